@@ -1,0 +1,485 @@
+#!/usr/bin/env python
+"""Benchmark of the Algebraic-Transformer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload attn|swiglu|norm|softmax|lm_small|lm_xl]
+                    [--impl ours|reference]
+
+Default workload ``attn``: causal rational attention forward+backward, bf16, B=8, H=16, S=4096,
+D=128 with ALiBi — per GPU (weak scaling: every rank processes its own 128 (batch, head) units,
+no collective on the data path).  One JSON line is printed by rank 0.
+
+``--impl reference`` times the CPU restatement of the reference's PyTorch path (the oracle) on the
+host cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 2 ** 20
+
+
+# ------------------------------------------------------------------------------------------ helpers
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region is timed."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        return False
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def max_over_ranks(ms: float, world: int, device) -> float:
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def time_steps(step, steps: int, warmup: int, world: int, device):
+    """W untimed warm-ups, then exactly K steps between CUDA events on the launching stream; max over ranks."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(device)
+    barrier(world)
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(device)
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world, device) / steps
+
+
+# ------------------------------------------------------------------------------------------ workloads
+ATTN = dict(B=8, H=16, S=4096, D=128)
+
+
+def attn_flops(B, H, S, D):
+    """Causal-convention flops: forward 2 GEMMs, backward 5 GEMMs, each 2*S*S*D/2 per (b,h)."""
+    fwd = 2.0 * B * H * S * S * D
+    return fwd, 2.5 * fwd
+
+
+def make_attn_inputs(cfg, seed, device=None, pin=False):
+    g = torch.Generator().manual_seed(seed)
+    shape = (cfg["B"], cfg["H"], cfg["S"], cfg["D"])
+    ts = [torch.randn(*shape, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(4)]
+    if pin:
+        ts = [t.pin_memory() for t in ts]
+    if device is not None:
+        ts = [t.to(device) for t in ts]
+    slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / cfg["H"]) for i in range(cfg["H"])], dtype=torch.float32)
+    return ts, slopes
+
+
+def bench_attn(args, rank, world, device):
+    import fastalgebraictransformer_b200 as fat
+    from fastalgebraictransformer_b200 import _lib
+    cfg = ATTN
+    (q, k, v, go), slopes = make_attn_inputs(cfg, 1234 + 1 + rank, device)
+    slopes = slopes.to(device)
+    scale = 1.0 / math.sqrt(cfg["D"])
+    fwd_flops, bwd_flops = attn_flops(**cfg)
+    path = _lib.lib().fat_attn_select_path(cfg["S"], cfg["D"], _lib.BF16, 1)
+
+    state = {}
+
+    def fwd():
+        state["out"], state["L"] = fat.rational_attention_forward(q, k, v, slopes, scale)
+
+    def bwd():
+        state["grads"] = fat.rational_attention_backward(q, k, v, state["out"], state["L"], go, slopes, scale)
+
+    def step():
+        fwd(); bwd()
+
+    with ClockSampler(device.index) as clocks:
+        ms = time_steps(step, args.steps, args.warmup, world, device)
+    fat.check_device_status()
+    ms_fwd = time_steps(fwd, max(3, args.steps // 2), 1, world, device)
+    ms_bwd = time_steps(bwd, max(3, args.steps // 2), 1, world, device)
+
+    # end to end through the public autograd API with host buffers (pinned), copies inside the timed region
+    (hq, hk, hv, hgo), _ = make_attn_inputs(cfg, 1234 + 1 + rank, pin=True)
+    houts = [torch.empty_like(hq).pin_memory() for _ in range(4)]
+
+    def e2e_step():
+        dq, dk, dv, dgo = (t.to(device, non_blocking=True) for t in (hq, hk, hv, hgo))
+        dq.requires_grad_(True); dk.requires_grad_(True); dv.requires_grad_(True)
+        out = fat.rational_attention(dq, dk, dv, slopes, scale)
+        out.backward(dgo)
+        for h, d in zip(houts, (out.detach(), dq.grad, dk.grad, dv.grad)):
+            h.copy_(d, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    ms_e2e = time_steps(e2e_step, e2e_steps, 1, world, device)
+    nbytes = hq.numel() * hq.element_size()
+
+    peaks = measured_peaks()
+    launches_per_step = {1: 3, 2: 4}.get(path, 3)
+    tfl = (fwd_flops + bwd_flops) * world / (ms * 1e-3) / 1e12
+    bwd_tfl = bwd_flops / (ms_bwd * 1e-3) / 1e12
+    return {
+        "metric": "rational_attention_fwd_bwd_tflops", "value": tfl, "unit": "TFLOP/s",
+        "ms_per_step": ms, "dtype": "bf16",
+        "config": {"workload": "rational_attention fwd+bwd causal ALiBi bf16 B=8 H=16 S=4096 D=128 per GPU "
+                               "(BASELINE configs[1])", "units_per_gpu": cfg["B"] * cfg["H"], "shard": "batch x head",
+                   "kernel_path": "tcgen05" if path == 2 else "simt", "l2": "inputs (4 x 134 MB) exceed the 126 MB L2",
+                   "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
+                   "pct_of_bf16_peak": 100.0 * tfl / world / peaks["bf16_tflops"]},
+        "e2e": {"value": (fwd_flops + bwd_flops) * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "ms_per_step": ms_e2e},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "attention backward", "achieved": bwd_tfl,
+                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": bwd_tfl / peaks["bf16_tflops"],
+                     "traffic": None, "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                     "fwd_achieved": fwd_flops / (ms_fwd * 1e-3) / 1e12},
+        "clocks": clocks.summary(),
+    }
+
+
+FUSED = {
+    "swiglu": dict(rows=16384, cols=8192, bytes=2147483648),
+    "norm": dict(rows=16384, cols=4096, bytes=671088640),
+    "softmax": dict(rows=4096, cols=4096, bytes=150994944),   # backward reads d_out and x only (p is recomputed)
+}
+
+
+def bench_fused(args, rank, world, device, name):
+    import fastalgebraictransformer_b200 as fat
+    cfg = FUSED[name]
+    g = torch.Generator(device=device).manual_seed(1234 + 2 + rank)
+    shape = (cfg["rows"], cfg["cols"])
+    nset = 1 if name != "softmax" else 6        # softmax tensors (33.5 MB) fit in L2: rotate 6 sets (> 126 MB each pass)
+
+    def rnd(std=1.0):
+        return (torch.randn(*shape, generator=g, device=device) * std).to(torch.bfloat16)
+
+    sets = []
+    for _ in range(nset):
+        if name == "swiglu":
+            sets.append((rnd().requires_grad_(True), rnd().requires_grad_(True), rnd()))
+        elif name == "norm":
+            w = (1 + 0.1 * torch.randn(cfg["cols"], generator=g, device=device)).to(torch.bfloat16)
+            sets.append((rnd().requires_grad_(True), w.requires_grad_(True), rnd()))
+        else:
+            sets.append((rnd(math.sqrt(2.0)).requires_grad_(True), rnd()))
+    it = [0]
+    alg = torch.ops.algebraic
+
+    def step():
+        s = sets[it[0] % nset]; it[0] += 1
+        if name == "swiglu":
+            out = alg.swiglu_fwd(s[0].detach(), s[1].detach()); alg.swiglu_bwd(s[2], s[0].detach(), s[1].detach())
+        elif name == "norm":
+            y, mean = alg.norm_fwd(s[0].detach(), s[1].detach(), 1e-6)
+            alg.norm_bwd(s[2], s[0].detach(), s[1].detach(), mean, 1e-6)
+        else:
+            alg.softmax_fwd(s[0].detach(), 1e-6); alg.softmax_bwd(s[1], s[0].detach(), 1e-6)
+
+    with ClockSampler(device.index) as clocks:
+        ms = time_steps(step, args.steps, args.warmup, world, device)
+    peaks = measured_peaks()
+    gbs = cfg["bytes"] * world / (ms * 1e-3) / 1e9
+
+    # end to end: host (pinned) -> device -> forward+backward through the autograd API -> host
+    hs = [t.detach().cpu().pin_memory() for t in sets[0]]
+    houts = [torch.empty(shape, dtype=torch.bfloat16).pin_memory() for _ in range(3)]
+
+    def e2e_step():
+        d = [t.to(device, non_blocking=True) for t in hs]
+        if name == "swiglu":
+            a, b = d[0].requires_grad_(True), d[1].requires_grad_(True)
+            o = fat.rational_swiglu(a, b); o.backward(d[2]); res = (o.detach(), a.grad, b.grad)
+        elif name == "norm":
+            a, w = d[0].requires_grad_(True), d[1].requires_grad_(True)
+            o = fat.mean_error_norm(a, w); o.backward(d[2]); res = (o.detach(), a.grad)
+        else:
+            a = d[0].requires_grad_(True)
+            o = fat.rational_softmax(a); o.backward(d[1]); res = (o.detach(), a.grad)
+        for h, r in zip(houts, res):
+            h.copy_(r, non_blocking=True)
+        return len(res)
+
+    ms_e2e = time_steps(e2e_step, 3, 1, world, device)
+    n_out = {"swiglu": 3, "norm": 2, "softmax": 2}[name]
+    return {
+        "metric": f"rational_{name}_fwd_bwd_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "dtype": "bf16",
+        "config": {"workload": f"{name} fwd+bwd bf16 [{cfg['rows']},{cfg['cols']}] (BASELINE configs[2])",
+                   "algorithmic_bytes_per_step": cfg["bytes"],
+                   "l2": "tensors exceed L2" if nset == 1 else f"{nset} rotating input sets (each pass touches > 126 MB before reuse)"},
+        "e2e": {"value": cfg["bytes"] * world / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in hs),
+                "d2h_bytes_per_step": n_out * shape[0] * shape[1] * 2, "ms_per_step": ms_e2e},
+        "gpu_launches": (3 if name == "norm" else 2) * args.steps,
+        "roofline": {"bound": "hbm", "kernel": f"{name} fwd+bwd", "achieved": gbs / world, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": gbs / world / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": peaks["source"]},
+        "clocks": clocks.summary(),
+    }
+
+
+LM = {
+    "lm_small": dict(vocab_size=32000, d_model=768, n_head=12, n_layers=12, d_ffn=None, batch=8, seq=1024),
+    "lm_xl": dict(vocab_size=50000, d_model=2048, n_head=16, n_layers=24, d_ffn=5504, batch=4, seq=2048),
+}
+
+
+def bench_lm(args, rank, world, device, name):
+    from fastalgebraictransformer_b200 import AlgebraicTransformerLM
+    cfg = LM[name]
+    torch.manual_seed(1234 + 3)
+    model = AlgebraicTransformerLM(cfg["vocab_size"], cfg["d_model"], cfg["n_head"], cfg["n_layers"], d_ffn=cfg["d_ffn"],
+                                   block_size=cfg["seq"], dropout=0.0).to(device).to(torch.bfloat16).train()
+    n_params = sum(p.numel() for p in model.parameters())
+    net = model
+    if world > 1:
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        net = DDP(model, device_ids=[device.index], gradient_as_bucket_view=True, bucket_cap_mb=64)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+    g = torch.Generator().manual_seed(1234 + 3 + rank)
+    hids = torch.randint(0, cfg["vocab_size"], (cfg["batch"], cfg["seq"]), generator=g).pin_memory()
+    hlab = torch.randint(0, cfg["vocab_size"], (cfg["batch"], cfg["seq"]), generator=g).pin_memory()
+    ids, lab = hids.to(device), hlab.to(device)
+    last = {}
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        _, loss = net(ids, labels=lab)
+        loss.backward()
+        opt.step()
+        last["loss"] = loss
+
+    def e2e_step():
+        i, l = hids.to(device, non_blocking=True), hlab.to(device, non_blocking=True)
+        opt.zero_grad(set_to_none=True)
+        _, loss = net(i, labels=l)
+        loss.backward()
+        opt.step()
+        last["loss_host"] = loss.item()
+
+    with ClockSampler(device.index) as clocks:
+        ms = time_steps(step, args.steps, args.warmup, world, device)
+    ms_e2e = time_steps(e2e_step, max(2, args.steps // 2), 1, world, device)
+    tokens = cfg["batch"] * cfg["seq"] * world
+    peaks = measured_peaks()
+    d_head = cfg["d_model"] // cfg["n_head"]
+    attn = cfg["n_layers"] * 3.5 * 2 * cfg["batch"] * cfg["n_head"] * cfg["seq"] ** 2 * d_head
+    flops = 6.0 * (n_params) * cfg["batch"] * cfg["seq"] + attn
+    return {
+        "metric": "lm_train_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+        "dtype": "bf16",
+        "config": {"workload": f"AlgebraicTransformerLM {name} training step (fwd+loss+bwd+AdamW), bf16, "
+                               f"batch {cfg['batch']} x seq {cfg['seq']} per GPU", "params": n_params,
+                   "parallelism": f"dp{world}", "loss": float(last["loss"].item())},
+        "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * hids.numel() * 8,
+                "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e},
+        "gpu_launches": cfg["n_layers"] * 9 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "whole step (GEMMs in cuBLAS + this library's kernels)",
+                     "achieved": flops / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], "traffic": None,
+                     "peak_source": peaks["source"] + " (sustained cuBLAS bf16)"},
+        "clocks": clocks.summary(),
+    }
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_attention_sample(heads: int, repeats: int = 1):
+    """The oracle (CPU restatement of the reference's PyTorch path) on `heads` heads of one batch element of the
+    attention workload, float32, all host threads.  Returns (seconds per pass, flops per pass)."""
+    from oracle import oracle
+    cfg = dict(ATTN, B=1, H=heads)
+    (q, k, v, go), slopes = make_attn_inputs(cfg, 1234 + 1)
+    q, k, v, go = (t.float() for t in (q, k, v, go))
+    slopes = slopes[:heads]
+    scale = 1.0 / math.sqrt(cfg["D"])
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle.rational_attention_grads(q, k, v, go, slopes, scale)
+        best = min(best, time.perf_counter() - t0)
+    f, b = attn_flops(**cfg)
+    return best, f + b
+
+
+def cpu_baseline_attn():
+    heads = 2
+    sec, flops = cpu_attention_sample(heads, repeats=1)           # warm-up / sizing pass
+    total, n = 0.0, 0
+    while total < 10.0 and n < 8:
+        s, _ = cpu_attention_sample(heads)
+        total += s; n += 1
+    sec = total / n
+    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"oracle (PyTorch fp32, autograd) on {heads} of the 128 (batch, head) units, S=4096 D=128, "
+                      f"mean of {n} passes of {sec:.2f} s; flops counted with the same causal convention"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return None
+    if args.workload != "attn":
+        return {"impl": "reference", "unavailable": "the CPU arm is implemented for the attention workload only"}
+    heads = 1
+    cpu_attention_sample(heads)                                    # untimed
+    for _ in range(max(0, args.warmup - 1)):
+        cpu_attention_sample(heads)
+    times = []
+    flops = 0.0
+    for _ in range(args.steps):
+        s, flops = cpu_attention_sample(heads)
+        times.append(s)
+    sec = sum(times) / len(times)
+    val = flops / sec / 1e12
+    base = {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"each step = 1 of the 128 (batch, head) units (S=4096, D=128), oracle in float32 with autograd"}
+    return {
+        "impl": "reference", "metric": "rational_attention_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "rational_attention fwd+bwd causal ALiBi B=8 H=16 S=4096 D=128 (BASELINE configs[1]); "
+                               "CPU restatement of the reference's PyTorch path on a bounded sample"},
+        "cpu_baseline": base,
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+# ------------------------------------------------------------------------------------------ main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "lm_small", "lm_xl"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank, world, local = dist_env()
+
+    if args.impl == "reference":
+        line = run_reference(args, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU implementation of the product path)")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE", file=sys.stderr)
+
+    if args.workload == "attn":
+        res = bench_attn(args, rank, world, device)
+    elif args.workload in FUSED:
+        res = bench_fused(args, rank, world, device, args.workload)
+    else:
+        res = bench_lm(args, rank, world, device, args.workload)
+
+    if rank == 0:
+        line = {"metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": res["dtype"],
+                "data": "synthetic", "config": res["config"], "e2e": res["e2e"], "gpu_launches": res["gpu_launches"],
+                "roofline": res["roofline"], "clocks": res["clocks"]}
+        if world == 1 and not args.no_cpu_baseline and args.workload == "attn":
+            line["cpu_baseline"] = cpu_baseline_attn()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

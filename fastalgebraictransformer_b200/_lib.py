@@ -1,0 +1,124 @@
+"""ctypes binding of libfat_b200.so (the C ABI declared in include/fat_b200.h).
+
+The library is the only implementation: if it is missing or fails to load, every op raises.
+There is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libfat_b200.so")
+
+F32, BF16, F16, F64 = 0, 1, 2, 3
+PATH_AUTO, PATH_SIMT, PATH_TENSOR = 0, 1, 2
+DTYPE_TAG = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16, torch.float64: F64}
+
+_lock = threading.Lock()
+_lib = None
+
+_i64, _int, _dbl, _ptr, _sz = C.c_int64, C.c_int, C.c_double, C.c_void_p, C.c_size_t
+_p64 = C.POINTER(C.c_int64)
+
+# name -> (restype, argtypes); must list every symbol include/fat_b200.h declares
+PROTOTYPES = {
+    "fat_version": (_int, []),
+    "fat_error_string": (C.c_char_p, [_int]),
+    "fat_last_error": (C.c_char_p, []),
+    "fat_swiglu_fwd": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
+    "fat_swiglu_bwd": (_int, [_ptr] * 5 + [_i64] * 7 + [_int, _ptr]),
+    "fat_norm_fwd": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),
+    "fat_norm_bwd_workspace_bytes": (_sz, [_i64, _i64, _int]),
+    "fat_norm_bwd": (_int, [_ptr] * 7 + [_sz] + [_i64] * 5 + [_dbl, _int, _ptr]),
+    "fat_softmax_fwd": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),
+    "fat_softmax_bwd": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),
+    "fat_attn_fwd": (_int, [_ptr] * 6 + [_int] * 4 + [_p64] * 4 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
+    "fat_attn_bwd_workspace_bytes": (_sz, [_int] * 6),
+    "fat_attn_bwd": (_int, [_ptr] * 11 + [_sz] + [_int] * 4 + [_p64] * 8 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
+    "fat_attn_select_path": (_int, [_int] * 4),
+}
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise RuntimeError(
+                        f"{LIB_PATH} is missing: build it with `python -m fastalgebraictransformer_b200.build` "
+                        "(nvcc, sm_100a).  This package has no fallback implementation.")
+                handle = C.CDLL(LIB_PATH)
+                for name, (res, args) in PROTOTYPES.items():
+                    fn = getattr(handle, name)
+                    fn.restype, fn.argtypes = res, args
+                _lib = handle
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        l = lib()
+        raise RuntimeError(f"libfat_b200: {l.fat_error_string(rc).decode()} — {l.fat_last_error().decode()}")
+
+
+def dtype_tag(t: torch.Tensor) -> int:
+    try:
+        return DTYPE_TAG[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def strides3(t: torch.Tensor):
+    """(batch, head, token) element strides of a [B,H,T,D] tensor as a C array."""
+    return (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+_status = {}
+
+
+def device_status(device: torch.device) -> torch.Tensor:
+    """The int32 status word kernels of this device write when a bounded wait runs out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status[idx]
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if any kernel reported a timed-out wait since the last check."""
+    for idx, word in list(_status.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        v = int(word.item())
+        if v:
+            word.zero_()
+            raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x} "
+                               f"(code {v >> 24}: a bounded wait inside a kernel ran out, detail {v & 0xffffff})")
+
+
+class device_guard:
+    """Make ``device`` current for the duration of a launch (no-op when it already is)."""
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index
+        self.prev = None
+
+    def __enter__(self):
+        if self.idx is not None and self.idx != torch.cuda.current_device():
+            self.prev = torch.cuda.current_device()
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False

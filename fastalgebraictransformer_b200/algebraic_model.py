@@ -1,0 +1,179 @@
+"""Algebraic Transformer language model on the sm_100a operators.
+
+Host-side mirror of the reference's ``algebraic_model.py`` (RationalMR 26-39, RationalSwiGLU
+42-62, AlgebraicAttention 65-136, AlgebraicBlock 139-152, AlgebraicTransformerLM 155-265,
+factories 272-302): same module names, constructor arguments, parameter names (so state
+dicts are interchangeable) and forward signature.  The modules run on CUDA only.
+
+Differences that remove copies but not behaviour: q, k, v are handed to the attention kernels
+as strided views of the packed projection, the attention output is produced directly in
+[B, T, H*D] memory order, and the SwiGLU kernels read the gate/value halves in place.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from . import _lib
+from .backward import RationalAttentionFunction
+from .forward import compute_alibi_slopes
+from .fused_ops import EPS, mean_error_norm, rational_swiglu
+
+
+class RationalMR(nn.Module):
+    """Mean-error normalisation layer (reference algebraic_model.py:26-39)."""
+
+    def __init__(self, d_model: int, eps: float = EPS):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(d_model))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return mean_error_norm(x, self.weight, self.eps)
+
+
+class RationalSwiGLU(nn.Module):
+    """SwiGLU feed-forward block with the rational sigmoid (reference algebraic_model.py:42-62)."""
+
+    def __init__(self, d_model: int, d_ffn: int, dropout: float = 0.0):
+        super().__init__()
+        self.w_gate_val = nn.Linear(d_model, 2 * d_ffn, bias=False)
+        self.w_out = nn.Linear(d_ffn, d_model, bias=False)
+        self.dropout = nn.Dropout(dropout)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gate, val = self.w_gate_val(x).chunk(2, dim=-1)
+        return self.dropout(self.w_out(rational_swiglu(gate, val)))
+
+
+class AlgebraicAttention(nn.Module):
+    """Multi-head causal attention with rational softmax and ALiBi (reference algebraic_model.py:65-110).
+
+    ``mask`` is accepted for signature parity and ignored, as the reference's CUDA path does
+    (algebraic_model.py:93-104)."""
+
+    def __init__(self, d_model: int, n_head: int, dropout: float = 0.1):
+        super().__init__()
+        assert d_model % n_head == 0
+        self.d_model = d_model
+        self.n_head = n_head
+        self.d_head = d_model // n_head
+        self.scale = 1.0 / math.sqrt(self.d_head)
+        self.qkv = nn.Linear(d_model, 3 * d_model, bias=False)
+        self.out = nn.Linear(d_model, d_model, bias=False)
+        self.dropout = nn.Dropout(dropout)
+        self.register_buffer("alibi_slopes", compute_alibi_slopes(n_head))
+
+    def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        B, T, C = x.shape
+        qkv = self.qkv(x).view(B, T, 3, self.n_head, self.d_head).permute(2, 0, 3, 1, 4)   # [3,B,H,T,D] view
+        q, k, v = qkv.unbind(0)
+        out = RationalAttentionFunction.apply(q, k, v, self.alibi_slopes, self.scale, True, EPS,
+                                              _lib.PATH_AUTO, True)
+        out = out.transpose(1, 2).reshape(B, T, C)          # already [B,T,H,D] in memory: no copy
+        return self.dropout(self.out(out))
+
+
+class AlgebraicBlock(nn.Module):
+    """Pre-norm transformer block (reference algebraic_model.py:139-152)."""
+
+    def __init__(self, d_model: int, n_head: int, d_ffn: int, dropout: float):
+        super().__init__()
+        self.attn = AlgebraicAttention(d_model, n_head, dropout)
+        self.ffn = RationalSwiGLU(d_model, d_ffn, dropout)
+        self.norm1 = RationalMR(d_model)
+        self.norm2 = RationalMR(d_model)
+
+    def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = x + self.attn(self.norm1(x), mask)
+        return x + self.ffn(self.norm2(x))
+
+
+class AlgebraicTransformerLM(nn.Module):
+    """Algebraic Transformer language model (reference algebraic_model.py:155-265)."""
+
+    def __init__(self, vocab_size: int, d_model: int, n_head: int, n_layers: int, d_ffn: Optional[int] = None,
+                 block_size: int = 2048, dropout: float = 0.1, gradient_checkpointing: bool = False, **kwargs):
+        super().__init__()
+        if d_ffn is None:
+            d_ffn = int(d_model * 8 / 3)
+        self.block_size = block_size
+        self.gradient_checkpointing = gradient_checkpointing
+        self.n_layers = n_layers
+        self.embed = nn.Embedding(vocab_size, d_model)
+        self.blocks = nn.ModuleList([AlgebraicBlock(d_model, n_head, d_ffn, dropout) for _ in range(n_layers)])
+        self.norm = RationalMR(d_model)
+        self.head = nn.Linear(d_model, vocab_size, bias=False)
+        self.embed.weight = self.head.weight            # tied (reference algebraic_model.py:193)
+        self.apply(self._init_weights)
+
+    def _init_weights(self, module):
+        if isinstance(module, nn.Linear):
+            std = 0.02
+            if hasattr(module, "_scale_init"):
+                std = 0.02 / math.sqrt(2 * self.n_layers)
+            nn.init.normal_(module.weight, mean=0.0, std=std)
+            if module.bias is not None:
+                nn.init.zeros_(module.bias)
+        elif isinstance(module, nn.Embedding):
+            nn.init.normal_(module.weight, mean=0.0, std=0.02)
+
+    def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
+                attention_mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        x = self.embed(input_ids)
+        for block in self.blocks:
+            if self.gradient_checkpointing and self.training:
+                x = checkpoint(block, x, attention_mask, use_reentrant=False)
+            else:
+                x = block(x, attention_mask)
+        logits = self.head(self.norm(x))
+        loss = None
+        if labels is not None:
+            shift_logits = logits[..., :-1, :].contiguous()
+            shift_labels = labels[..., 1:].contiguous()
+            loss = F.cross_entropy(shift_logits.view(-1, shift_logits.size(-1)), shift_labels.view(-1),
+                                   ignore_index=-100)
+        return logits, loss
+
+    @torch.no_grad()
+    def generate(self, idx: torch.Tensor, max_new_tokens: int, temperature: float = 1.0,
+                 top_k: Optional[int] = None) -> torch.Tensor:
+        """Sampling loop (reference algebraic_model.py:239-265): re-runs the forward per token, no KV cache."""
+        for _ in range(max_new_tokens):
+            idx_cond = idx if idx.size(1) <= self.block_size else idx[:, -self.block_size:]
+            logits, _ = self.forward(idx_cond)
+            logits = logits[:, -1, :]
+            if temperature != 1.0:
+                logits = logits / temperature
+            if top_k is not None:
+                kth, _ = torch.topk(logits, min(top_k, logits.size(-1)))
+                logits[logits < kth[:, [-1]]] = float("-inf")
+            idx = torch.cat((idx, torch.multinomial(F.softmax(logits, dim=-1), num_samples=1)), dim=1)
+        return idx
+
+
+def create_small_model(vocab_size: int = 32000, **kwargs) -> AlgebraicTransformerLM:
+    """~125M parameters (reference algebraic_model.py:272-280)."""
+    return AlgebraicTransformerLM(vocab_size=vocab_size, d_model=768, n_head=12, n_layers=12, **kwargs)
+
+
+def create_medium_model(vocab_size: int = 32000, **kwargs) -> AlgebraicTransformerLM:
+    """~350M parameters (reference algebraic_model.py:283-291)."""
+    return AlgebraicTransformerLM(vocab_size=vocab_size, d_model=1024, n_head=16, n_layers=24, **kwargs)
+
+
+def create_large_model(vocab_size: int = 32000, **kwargs) -> AlgebraicTransformerLM:
+    """~760M parameters (reference algebraic_model.py:294-302)."""
+    return AlgebraicTransformerLM(vocab_size=vocab_size, d_model=1536, n_head=24, n_layers=24, **kwargs)
+
+
+def create_xl_model(vocab_size: int = 50000, **kwargs) -> AlgebraicTransformerLM:
+    """~1.3B parameters: d_model 2048, 16 heads, 24 layers, FFN hidden 5504 (the reference's README
+    advertises this factory without defining it)."""
+    kwargs.setdefault("d_ffn", 5504)
+    return AlgebraicTransformerLM(vocab_size=vocab_size, d_model=2048, n_head=16, n_layers=24, **kwargs)

@@ -1,0 +1,33 @@
+// Argument block shared by the attention kernel families (SIMT and tcgen05).
+#pragma once
+
+#include "common.cuh"
+
+namespace fat {
+
+// Everything a rational-attention launch needs, passed by value to the kernels.
+// Strides are in elements, {batch, head, token}; the head dimension has unit stride.
+struct AttnParams {
+  const void* q; const void* k; const void* v; const float* slopes;
+  void* out; float* L;                        // forward outputs / backward inputs
+  const void* d_out; void* d_q; void* d_k; void* d_v;
+  float* delta;                               // workspace: Delta_i = d_out_i . out_i, [B,H,T]
+  float* dq_acc;                              // workspace: float32 d_q accumulator (tensor path)
+  int B, H, T, D;
+  int64_t qs[3], ks[3], vs[3], os[3], dos[3], dqs[3], dks[3], dvs[3];
+  float scale, eps;
+  int causal;
+  int* status;
+};
+
+// SIMT family (attn_simt.cu)
+int attn_fwd_simt(const AttnParams& p, int dtype, cudaStream_t st);
+int attn_bwd_simt(const AttnParams& p, int dtype, cudaStream_t st);
+
+// tcgen05 family (attn_tc_fwd.cu / attn_tc_bwd.cu)
+bool   attn_tc_eligible(int T, int D, int dtype, bool aligned);
+int    attn_fwd_tc(const AttnParams& p, int dtype, cudaStream_t st);
+int    attn_bwd_tc(const AttnParams& p, int dtype, cudaStream_t st);
+size_t attn_bwd_tc_workspace_bytes(int B, int H, int T, int D);
+
+}  // namespace fat

@@ -1,0 +1,675 @@
+// Bandwidth-bound kernels of the Algebraic-Transformer hot path for sm_100a:
+// rational SwiGLU, mean-error normalisation and rational softmax, forward and backward.
+//
+// Design: every tensor is touched exactly once per kernel.  Rows are held in registers
+// (16-byte packs, VPT packs per thread, G threads per row, 256/G rows per block) so the
+// row statistics and the output come from a single read; reductions are warp shuffles
+// plus one shared-memory hop when a row spans several warps.  Loads and stores carry
+// streaming hints (read-once / write-once data should not displace L2 contents).
+// Shapes or alignments that do not fit the register-resident scheme go through "slow"
+// kernels (one block per row, two passes, scalar accesses) that accept anything.
+#include <initializer_list>
+
+#include "common.cuh"
+
+namespace fat {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxVPT = 8;
+constexpr int kNormBwdMaxBlocks = 4 * kNumSM;   // rows of the d_weight partial-sum scratch
+
+// ------------------------------------------------------------------ group reduction
+// Sums NV values over the G threads (G = 32..256, power of two) that share a row.
+// `buf` is shared memory of 2*8*NV values; `phase` alternates the half in use so that one
+// __syncthreads per call suffices.  Every thread of the block must call it.
+template <typename C, int NV>
+__device__ __forceinline__ void group_sum(C (&v)[NV], int G, C* buf, int& phase) {
+#pragma unroll
+  for (int n = 0; n < NV; ++n) v[n] = warp_sum(v[n]);
+  if (G > 32) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    C* b = buf + phase * (kThreads / 32) * NV;
+    if (lane == 0) {
+#pragma unroll
+      for (int n = 0; n < NV; ++n) b[warp * NV + n] = v[n];
+    }
+    __syncthreads();
+    const int wpg = G >> 5, w0 = (warp / wpg) * wpg;
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      C s = C(0);
+      for (int w = 0; w < wpg; ++w) s += b[(w0 + w) * NV + n];
+      v[n] = s;
+    }
+    phase ^= 1;
+  }
+}
+
+// =====================================================================================
+// SwiGLU
+// =====================================================================================
+template <typename T, int W>
+__global__ void __launch_bounds__(kThreads)
+swiglu_fwd_kernel(const T* __restrict__ gate, const T* __restrict__ value, T* __restrict__ out,
+                  int64_t n_rows, int64_t packs_per_row, int64_t gs, int64_t vs, int64_t os) {
+  using C = typename Elem<T>::C;
+  const int64_t step = int64_t(gridDim.x) * kThreads;
+  for (int64_t row = blockIdx.y; row < n_rows; row += gridDim.y) {
+    const T* g = gate + row * gs; const T* v = value + row * vs; T* o = out + row * os;
+#pragma unroll 4
+    for (int64_t pk = int64_t(blockIdx.x) * kThreads + threadIdx.x; pk < packs_per_row; pk += step) {
+      C a[W], b[W], r[W];
+      load_pack<T, W>(g + pk * W, a);
+      load_pack<T, W>(v + pk * W, b);
+#pragma unroll
+      for (int i = 0; i < W; ++i) r[i] = a[i] * rsigmoid(a[i], rcp1p_abs(a[i])) * b[i];
+      store_pack<T, W>(o + pk * W, r);
+    }
+  }
+}
+
+template <typename T, int W>
+__global__ void __launch_bounds__(kThreads)
+swiglu_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ gate, const T* __restrict__ value,
+                  T* __restrict__ d_gate, T* __restrict__ d_value,
+                  int64_t n_rows, int64_t packs_per_row,
+                  int64_t dos, int64_t gs, int64_t vs, int64_t dgs, int64_t dvs) {
+  using C = typename Elem<T>::C;
+  const int64_t step = int64_t(gridDim.x) * kThreads;
+  for (int64_t row = blockIdx.y; row < n_rows; row += gridDim.y) {
+    const T* go = d_out + row * dos; const T* g = gate + row * gs; const T* v = value + row * vs;
+    T* dg = d_gate + row * dgs; T* dv = d_value + row * dvs;
+#pragma unroll 2
+    for (int64_t pk = int64_t(blockIdx.x) * kThreads + threadIdx.x; pk < packs_per_row; pk += step) {
+      C o[W], a[W], b[W], ra[W], rb[W];
+      load_pack<T, W>(go + pk * W, o);
+      load_pack<T, W>(g + pk * W, a);
+      load_pack<T, W>(v + pk * W, b);
+#pragma unroll
+      for (int i = 0; i < W; ++i) {
+        const C r = rcp1p_abs(a[i]);
+        const C s = rsigmoid(a[i], r);
+        rb[i] = o[i] * a[i] * s;                              // d_value = d_out * gate * sigma
+        ra[i] = o[i] * b[i] * (s + a[i] * C(0.5) * r * r);    // d_gate  = d_out * value * (sigma + gate sigma')
+      }
+      store_pack<T, W>(dg + pk * W, ra);
+      store_pack<T, W>(dv + pk * W, rb);
+    }
+  }
+}
+
+// =====================================================================================
+// Register-resident row kernels (fast path)
+// =====================================================================================
+template <typename T, int W, int VPT>
+struct RowRegs {
+  using C = typename Elem<T>::C;
+  C v[VPT][W];
+  __device__ __forceinline__ void load(const T* row, int t, int G, int npk, bool ok) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int pk = t + i * G;
+      if (ok && pk < npk) load_pack<T, W>(row + int64_t(pk) * W, v[i]);
+      else {
+#pragma unroll
+        for (int j = 0; j < W; ++j) v[i][j] = C(0);
+      }
+    }
+  }
+};
+
+template <typename T, int W, int VPT>
+__global__ void __launch_bounds__(kThreads)
+norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ weight, T* __restrict__ y,
+                float* __restrict__ mean, int64_t n_rows, int n_cols, int64_t xs, int64_t ys,
+                double eps_d, int G) {
+  using C = typename Elem<T>::C;
+  __shared__ C red[2 * (kThreads / 32)];
+  int phase = 0;
+  const int npk = n_cols / W, rpc = kThreads / G, g = threadIdx.x / G, t = threadIdx.x % G;
+  const C eps = C(eps_d);
+  C w[VPT][W];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int pk = t + i * G;
+    if (pk < npk) load_pack_cached<T, W>(weight + int64_t(pk) * W, w[i]);
+  }
+  for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += int64_t(gridDim.x) * rpc) {
+    const int64_t row = row0 + g;
+    const bool ok = row < n_rows;
+    RowRegs<T, W, VPT> xr;
+    xr.load(x + row * xs, t, G, npk, ok);
+    C s[1] = {C(0)};
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < W; ++j) s[0] += fabs(xr.v[i][j]);
+    group_sum<C, 1>(s, G, red, phase);
+    const C m = s[0] / C(n_cols);
+    const C inv = C(1) / (m + eps);
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int pk = t + i * G;
+        if (pk < npk) {
+          C o[W];
+#pragma unroll
+          for (int j = 0; j < W; ++j) o[j] = xr.v[i][j] * inv * w[i][j];
+          store_pack<T, W>(y + row * ys + int64_t(pk) * W, o);
+        }
+      }
+      if (t == 0) mean[row] = float(m);
+    }
+  }
+}
+
+// d_x for every row, plus this block's partial column sums of d_out * x / mu into
+// partial[blockIdx.x][0..n_cols) (compute type).  dyn smem: (256/G) * n_cols values when
+// several rows share a block.
+template <typename T, int W, int VPT>
+__global__ void __launch_bounds__(kThreads)
+norm_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ x, const T* __restrict__ weight,
+                const float* __restrict__ mean, T* __restrict__ d_x,
+                typename Elem<T>::C* __restrict__ partial,
+                int64_t n_rows, int n_cols, int64_t dos, int64_t xs, int64_t dxs,
+                double eps_d, int G) {
+  using C = typename Elem<T>::C;
+  __shared__ C red[2 * (kThreads / 32)];
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  int phase = 0;
+  const int npk = n_cols / W, rpc = kThreads / G, g = threadIdx.x / G, t = threadIdx.x % G;
+  const C eps = C(eps_d);
+  C w[VPT][W], acc[VPT][W];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int pk = t + i * G;
+    if (pk < npk) load_pack_cached<T, W>(weight + int64_t(pk) * W, w[i]);
+#pragma unroll
+    for (int j = 0; j < W; ++j) acc[i][j] = C(0);
+  }
+  for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += int64_t(gridDim.x) * rpc) {
+    const int64_t row = row0 + g;
+    const bool ok = row < n_rows;
+    RowRegs<T, W, VPT> xr, gr;
+    xr.load(x + row * xs, t, G, npk, ok);
+    gr.load(d_out + row * dos, t, G, npk, ok);
+    const C inv = ok ? C(1) / (C(mean[row]) + eps) : C(0);
+    C s[1] = {C(0)};
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      if (t + i * G < npk) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+          const C gxn = gr.v[i][j] * (xr.v[i][j] * inv);      // d_out * x / mu
+          acc[i][j] += gxn;
+          s[0] += gxn * w[i][j];
+        }
+      }
+    }
+    group_sum<C, 1>(s, G, red, phase);
+    const C corr = s[0] / C(n_cols) * inv;
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int pk = t + i * G;
+        if (pk < npk) {
+          C o[W];
+#pragma unroll
+          for (int j = 0; j < W; ++j)
+            o[j] = gr.v[i][j] * w[i][j] * inv - sgn(xr.v[i][j]) * corr;
+          store_pack<T, W>(d_x + row * dxs + int64_t(pk) * W, o);
+        }
+      }
+    }
+  }
+  // fold the row groups of this block, then publish the block's partial sums
+  C* prow = partial + int64_t(blockIdx.x) * n_cols;
+  if (rpc == 1) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int pk = t + i * G;
+      if (pk < npk) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) prow[pk * W + j] = acc[i][j];
+      }
+    }
+  } else {
+    C* sm = reinterpret_cast<C*>(dyn_smem);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int pk = t + i * G;
+      if (pk < npk) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) sm[g * n_cols + pk * W + j] = acc[i][j];
+      }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < n_cols; c += kThreads) {
+      C s = C(0);
+      for (int r = 0; r < rpc; ++r) s += sm[r * n_cols + c];
+      prow[c] = s;
+    }
+  }
+}
+
+// d_weight[c] = sum over the n_part partial rows.  Block = 32 columns x 8 slices.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+norm_bwd_reduce_kernel(const typename Elem<T>::C* __restrict__ partial, T* __restrict__ d_weight,
+                       int n_part, int n_cols) {
+  using C = typename Elem<T>::C;
+  __shared__ C sm[8][33];
+  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  C s = C(0);
+  if (c < n_cols)
+    for (int r = slice; r < n_part; r += 8) s += partial[int64_t(r) * n_cols + c];
+  sm[slice][lane] = s;
+  __syncthreads();
+  if (slice == 0 && c < n_cols) {
+#pragma unroll
+    for (int r = 1; r < 8; ++r) s += sm[r][lane];
+    d_weight[c] = Elem<T>::from_c(s);
+  }
+}
+
+template <typename T, int W, int VPT>
+__global__ void __launch_bounds__(kThreads)
+softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ p, int64_t n_rows, int n_cols,
+                   int64_t xs, int64_t ps, double eps_d, int G) {
+  using C = typename Elem<T>::C;
+  __shared__ C red[2 * (kThreads / 32)];
+  int phase = 0;
+  const int npk = n_cols / W, rpc = kThreads / G, g = threadIdx.x / G, t = threadIdx.x % G;
+  const C eps = C(eps_d);
+  for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += int64_t(gridDim.x) * rpc) {
+    const int64_t row = row0 + g;
+    const bool ok = row < n_rows;
+    RowRegs<T, W, VPT> xr;
+    xr.load(x + row * xs, t, G, npk, ok);
+    C s[1] = {C(0)};
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const bool live = t + i * G < npk;
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        const C v = xr.v[i][j];
+        C f = rsigmoid(v, rcp1p_abs(v));
+        f *= f; f *= f;
+        f = live ? f : C(0);
+        xr.v[i][j] = f;                 // the row now holds sigma^4
+        s[0] += f;
+      }
+    }
+    group_sum<C, 1>(s, G, red, phase);
+    const C inv = C(1) / (s[0] + eps);
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int pk = t + i * G;
+        if (pk < npk) {
+          C o[W];
+#pragma unroll
+          for (int j = 0; j < W; ++j) o[j] = xr.v[i][j] * inv;
+          store_pack<T, W>(p + row * ps + int64_t(pk) * W, o);
+        }
+      }
+    }
+  }
+}
+
+template <typename T, int W, int VPT>
+__global__ void __launch_bounds__(kThreads)
+softmax_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ x, T* __restrict__ d_x,
+                   int64_t n_rows, int n_cols, int64_t dos, int64_t xs, int64_t dxs,
+                   double eps_d, int G) {
+  using C = typename Elem<T>::C;
+  __shared__ C red[2 * (kThreads / 32) * 2];
+  int phase = 0;
+  const int npk = n_cols / W, rpc = kThreads / G, g = threadIdx.x / G, t = threadIdx.x % G;
+  const C eps = C(eps_d);
+  for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += int64_t(gridDim.x) * rpc) {
+    const int64_t row = row0 + g;
+    const bool ok = row < n_rows;
+    RowRegs<T, W, VPT> xr, gr;
+    xr.load(x + row * xs, t, G, npk, ok);
+    gr.load(d_out + row * dos, t, G, npk, ok);
+    // after this loop xr holds k = 2 sigma^3 r^2 (the un-normalised derivative factor)
+    C s[2] = {C(0), C(0)};                 // Z = sum sigma^4 ; sum d_out * sigma^4
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const bool live = t + i * G < npk;
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        const C v = xr.v[i][j];
+        const C r = rcp1p_abs(v);
+        const C sg = rsigmoid(v, r);
+        const C s2 = sg * sg;
+        const C f = live ? s2 * s2 : C(0);
+        s[0] += f;
+        s[1] += gr.v[i][j] * f;
+        xr.v[i][j] = C(2) * s2 * sg * r * r;
+      }
+    }
+    group_sum<C, 2>(s, G, red, phase);
+    const C inv = C(1) / (s[0] + eps);
+    const C dot = s[1] * inv;
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int pk = t + i * G;
+        if (pk < npk) {
+          C o[W];
+#pragma unroll
+          for (int j = 0; j < W; ++j) o[j] = xr.v[i][j] * inv * (gr.v[i][j] - dot);
+          store_pack<T, W>(d_x + row * dxs + int64_t(pk) * W, o);
+        }
+      }
+    }
+  }
+}
+
+// =====================================================================================
+// Slow path: one block per row, two passes, scalar accesses, any n_cols / alignment
+// =====================================================================================
+enum RowOp { kNormFwd, kNormBwd, kSoftmaxFwd, kSoftmaxBwd };
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads)
+row_slow_kernel(const T* __restrict__ a,      // x
+                const T* __restrict__ b,      // d_out (bwd ops) or unused
+                const T* __restrict__ weight, // norm ops
+                float* __restrict__ mean_out, const float* __restrict__ mean_in,
+                T* __restrict__ out, typename Elem<T>::C* __restrict__ partial,
+                int64_t n_rows, int64_t n_cols, int64_t as, int64_t bs, int64_t os, double eps_d) {
+  using C = typename Elem<T>::C;
+  __shared__ C red[2 * (kThreads / 32) * 2];
+  int phase = 0;
+  const C eps = C(eps_d);
+  if (OP == kNormBwd)
+    for (int64_t c = threadIdx.x; c < n_cols; c += kThreads) partial[int64_t(blockIdx.x) * n_cols + c] = C(0);
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    const T* x = a + row * as;
+    const T* go = b ? b + row * bs : nullptr;
+    T* o = out + row * os;
+    C s[2] = {C(0), C(0)};
+    C inv = C(0);
+    if (OP == kNormBwd) inv = C(1) / (C(mean_in[row]) + eps);
+    for (int64_t c = threadIdx.x; c < n_cols; c += kThreads) {
+      const C v = Elem<T>::to_c(x[c]);
+      if (OP == kNormFwd) s[0] += fabs(v);
+      if (OP == kNormBwd) s[0] += Elem<T>::to_c(go[c]) * (v * inv) * Elem<T>::to_c(weight[c]);
+      if (OP == kSoftmaxFwd || OP == kSoftmaxBwd) {
+        C f = rsigmoid(v, rcp1p_abs(v)); f *= f; f *= f;
+        s[0] += f;
+        if (OP == kSoftmaxBwd) s[1] += Elem<T>::to_c(go[c]) * f;
+      }
+    }
+    group_sum<C, 2>(s, kThreads, red, phase);
+    if (OP == kNormFwd) {
+      const C m = s[0] / C(n_cols);
+      inv = C(1) / (m + eps);
+      if (threadIdx.x == 0) mean_out[row] = float(m);
+    }
+    if (OP == kSoftmaxFwd || OP == kSoftmaxBwd) inv = C(1) / (s[0] + eps);
+    for (int64_t c = threadIdx.x; c < n_cols; c += kThreads) {
+      const C v = Elem<T>::to_c(x[c]);
+      C r;
+      if (OP == kNormFwd) r = v * inv * Elem<T>::to_c(weight[c]);
+      if (OP == kNormBwd) {
+        const C g = Elem<T>::to_c(go[c]);
+        r = g * Elem<T>::to_c(weight[c]) * inv - sgn(v) * (s[0] / C(n_cols) * inv);
+        partial[int64_t(blockIdx.x) * n_cols + c] += g * (v * inv);
+      }
+      if (OP == kSoftmaxFwd) { C f = rsigmoid(v, rcp1p_abs(v)); f *= f; f *= f; r = f * inv; }
+      if (OP == kSoftmaxBwd) {
+        const C rr = rcp1p_abs(v); const C sg = rsigmoid(v, rr);
+        r = C(2) * sg * sg * sg * rr * rr * inv * (Elem<T>::to_c(go[c]) - s[1] * inv);
+      }
+      o[c] = Elem<T>::from_c(r);
+    }
+  }
+}
+
+// =====================================================================================
+// Host-side dispatch
+// =====================================================================================
+struct RowPlan { bool fast; int G; int vpt; int grid; };
+
+// Fast path: all pointers 16-byte aligned, n_cols and the row strides multiples of the pack
+// width, and the row fits in registers (<= 256 * 8 packs).
+template <typename T>
+RowPlan plan_rows(int64_t n_rows, int64_t n_cols, std::initializer_list<const void*> ptrs,
+                  std::initializer_list<int64_t> strides, int blocks_per_sm) {
+  constexpr int W = 16 / sizeof(T);
+  RowPlan p{true, 32, 1, 1};
+  for (const void* q : ptrs) if (q && !aligned16(q)) p.fast = false;
+  for (int64_t s : strides) if (s % W) p.fast = false;
+  if (n_cols % W || n_cols / W > int64_t(kThreads) * kMaxVPT) p.fast = false;
+  if (p.fast) {
+    const int npk = int(n_cols / W);
+    int G = 32;
+    while (G < kThreads && (npk + G - 1) / G > 2) G <<= 1;      // aim for <= 2 packs per thread
+    p.G = G;
+    const int need = (npk + G - 1) / G;
+    p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+    const int rpc = kThreads / G;
+    const int64_t blocks = (n_rows + rpc - 1) / rpc;
+    p.grid = int(blocks < int64_t(blocks_per_sm) * kNumSM ? blocks : int64_t(blocks_per_sm) * kNumSM);
+  } else {
+    p.grid = int(n_rows < int64_t(blocks_per_sm) * kNumSM ? n_rows : int64_t(blocks_per_sm) * kNumSM);
+  }
+  if (p.grid < 1) p.grid = 1;
+  return p;
+}
+
+#define FAT_VPT_SWITCH(vpt, ...)                                  \
+  switch (vpt) {                                                  \
+    case 1: { constexpr int VPT = 1; __VA_ARGS__; } break;        \
+    case 2: { constexpr int VPT = 2; __VA_ARGS__; } break;        \
+    case 4: { constexpr int VPT = 4; __VA_ARGS__; } break;        \
+    default: { constexpr int VPT = 8; __VA_ARGS__; } break;       \
+  }
+
+template <typename T>
+int swiglu_fwd_t(const void* gate, const void* value, void* out, int64_t n_rows, int64_t n_cols,
+                 int64_t gs, int64_t vs, int64_t os, cudaStream_t st) {
+  constexpr int W = 16 / sizeof(T);
+  if (gs == n_cols && vs == n_cols && os == n_cols) { n_cols *= n_rows; n_rows = 1; gs = vs = os = n_cols; }
+  const bool vec = aligned16(gate) && aligned16(value) && aligned16(out) && n_cols % W == 0 &&
+                   gs % W == 0 && vs % W == 0 && os % W == 0;
+  const int64_t ppr = vec ? n_cols / W : n_cols;
+  int64_t gx = (ppr + kThreads - 1) / kThreads;
+  const int64_t cap = 8 * kNumSM;
+  if (gx > cap) gx = cap;
+  int64_t gy = n_rows < (cap + gx - 1) / gx ? n_rows : (cap + gx - 1) / gx;
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  if (vec) swiglu_fwd_kernel<T, W><<<grid, kThreads, 0, st>>>((const T*)gate, (const T*)value, (T*)out, n_rows, ppr, gs, vs, os);
+  else     swiglu_fwd_kernel<T, 1><<<grid, kThreads, 0, st>>>((const T*)gate, (const T*)value, (T*)out, n_rows, ppr, gs, vs, os);
+  return check_launch("swiglu_fwd");
+}
+
+template <typename T>
+int swiglu_bwd_t(const void* d_out, const void* gate, const void* value, void* d_gate, void* d_value,
+                 int64_t n_rows, int64_t n_cols, int64_t dos, int64_t gs, int64_t vs, int64_t dgs, int64_t dvs,
+                 cudaStream_t st) {
+  constexpr int W = 16 / sizeof(T);
+  if (dos == n_cols && gs == n_cols && vs == n_cols && dgs == n_cols && dvs == n_cols) {
+    n_cols *= n_rows; n_rows = 1; dos = gs = vs = dgs = dvs = n_cols;
+  }
+  const bool vec = aligned16(d_out) && aligned16(gate) && aligned16(value) && aligned16(d_gate) && aligned16(d_value) &&
+                   n_cols % W == 0 && dos % W == 0 && gs % W == 0 && vs % W == 0 && dgs % W == 0 && dvs % W == 0;
+  const int64_t ppr = vec ? n_cols / W : n_cols;
+  int64_t gx = (ppr + kThreads - 1) / kThreads;
+  const int64_t cap = 8 * kNumSM;
+  if (gx > cap) gx = cap;
+  int64_t gy = n_rows < (cap + gx - 1) / gx ? n_rows : (cap + gx - 1) / gx;
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  if (vec) swiglu_bwd_kernel<T, W><<<grid, kThreads, 0, st>>>((const T*)d_out, (const T*)gate, (const T*)value, (T*)d_gate, (T*)d_value, n_rows, ppr, dos, gs, vs, dgs, dvs);
+  else     swiglu_bwd_kernel<T, 1><<<grid, kThreads, 0, st>>>((const T*)d_out, (const T*)gate, (const T*)value, (T*)d_gate, (T*)d_value, n_rows, ppr, dos, gs, vs, dgs, dvs);
+  return check_launch("swiglu_bwd");
+}
+
+template <typename T>
+int norm_fwd_t(const void* x, const void* w, void* y, float* mean, int64_t n_rows, int64_t n_cols,
+               int64_t xs, int64_t ys, double eps, cudaStream_t st) {
+  constexpr int W = 16 / sizeof(T);
+  RowPlan p = plan_rows<T>(n_rows, n_cols, {x, w, y}, {xs, ys}, 8);
+  if (p.fast) {
+    FAT_VPT_SWITCH(p.vpt, (norm_fwd_kernel<T, W, VPT><<<p.grid, kThreads, 0, st>>>(
+        (const T*)x, (const T*)w, (T*)y, mean, n_rows, int(n_cols), xs, ys, eps, p.G)));
+  } else {
+    row_slow_kernel<T, kNormFwd><<<p.grid, kThreads, 0, st>>>((const T*)x, nullptr, (const T*)w, mean, nullptr,
+                                                               (T*)y, nullptr, n_rows, n_cols, xs, 0, ys, eps);
+  }
+  return check_launch("norm_fwd");
+}
+
+template <typename T>
+int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mean, void* d_x, void* d_w,
+               void* ws, size_t ws_bytes, int64_t n_rows, int64_t n_cols, int64_t dos, int64_t xs, int64_t dxs,
+               double eps, cudaStream_t st) {
+  using C = typename Elem<T>::C;
+  constexpr int W = 16 / sizeof(T);
+  RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, w, d_x}, {dos, xs, dxs}, 2);
+  if (p.grid > kNormBwdMaxBlocks) p.grid = kNormBwdMaxBlocks;
+  if (size_t(p.grid) * size_t(n_cols) * sizeof(C) > ws_bytes) {
+    set_error("norm_bwd: workspace of %zu bytes is smaller than the %zu needed", ws_bytes,
+              size_t(p.grid) * size_t(n_cols) * sizeof(C));
+    return FAT_ERR_WORKSPACE;
+  }
+  C* partial = reinterpret_cast<C*>(ws);
+  if (p.fast) {
+    const int rpc = kThreads / p.G;
+    const size_t smem = rpc > 1 ? size_t(rpc) * n_cols * sizeof(C) : 0;
+    FAT_VPT_SWITCH(p.vpt, {
+      auto kern = norm_bwd_kernel<T, W, VPT>;
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      kern<<<p.grid, kThreads, smem, st>>>((const T*)d_out, (const T*)x, (const T*)w, mean, (T*)d_x, partial,
+                                          n_rows, int(n_cols), dos, xs, dxs, eps, p.G);
+    });
+  } else {
+    row_slow_kernel<T, kNormBwd><<<p.grid, kThreads, 0, st>>>((const T*)x, (const T*)d_out, (const T*)w, nullptr, mean,
+                                                               (T*)d_x, partial, n_rows, n_cols, xs, dos, dxs, eps);
+  }
+  int rc = check_launch("norm_bwd");
+  if (rc) return rc;
+  norm_bwd_reduce_kernel<T><<<unsigned((n_cols + 31) / 32), kThreads, 0, st>>>(partial, (T*)d_w, p.grid, int(n_cols));
+  return check_launch("norm_bwd_reduce");
+}
+
+template <typename T>
+int softmax_fwd_t(const void* x, void* pr, int64_t n_rows, int64_t n_cols, int64_t xs, int64_t ps, double eps,
+                  cudaStream_t st) {
+  constexpr int W = 16 / sizeof(T);
+  RowPlan p = plan_rows<T>(n_rows, n_cols, {x, pr}, {xs, ps}, 8);
+  if (p.fast) {
+    FAT_VPT_SWITCH(p.vpt, (softmax_fwd_kernel<T, W, VPT><<<p.grid, kThreads, 0, st>>>(
+        (const T*)x, (T*)pr, n_rows, int(n_cols), xs, ps, eps, p.G)));
+  } else {
+    row_slow_kernel<T, kSoftmaxFwd><<<p.grid, kThreads, 0, st>>>((const T*)x, nullptr, nullptr, nullptr, nullptr,
+                                                                  (T*)pr, nullptr, n_rows, n_cols, xs, 0, ps, eps);
+  }
+  return check_launch("softmax_fwd");
+}
+
+template <typename T>
+int softmax_bwd_t(const void* d_out, const void* x, void* d_x, int64_t n_rows, int64_t n_cols, int64_t dos,
+                  int64_t xs, int64_t dxs, double eps, cudaStream_t st) {
+  constexpr int W = 16 / sizeof(T);
+  RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, d_x}, {dos, xs, dxs}, 8);
+  if (p.fast) {
+    FAT_VPT_SWITCH(p.vpt, (softmax_bwd_kernel<T, W, VPT><<<p.grid, kThreads, 0, st>>>(
+        (const T*)d_out, (const T*)x, (T*)d_x, n_rows, int(n_cols), dos, xs, dxs, eps, p.G)));
+  } else {
+    row_slow_kernel<T, kSoftmaxBwd><<<p.grid, kThreads, 0, st>>>((const T*)x, (const T*)d_out, nullptr, nullptr, nullptr,
+                                                                  (T*)d_x, nullptr, n_rows, n_cols, xs, dos, dxs, eps);
+  }
+  return check_launch("softmax_bwd");
+}
+
+#define FAT_DTYPE_SWITCH(dtype, ...)                                                    \
+  switch (dtype) {                                                                      \
+    case FAT_F32:  { using T = float;          return __VA_ARGS__; }                    \
+    case FAT_BF16: { using T = __nv_bfloat16;  return __VA_ARGS__; }                    \
+    case FAT_F16:  { using T = __half;         return __VA_ARGS__; }                    \
+    case FAT_F64:  { using T = double;         return __VA_ARGS__; }                    \
+    default: set_error("unsupported dtype tag %d", dtype); return FAT_ERR_DTYPE;        \
+  }
+
+int check_2d(const char* what, int64_t n_rows, int64_t n_cols) {
+  if (n_rows < 0 || n_cols <= 0 || n_cols > (int64_t(1) << 30)) {
+    set_error("%s: bad shape [%lld, %lld]", what, (long long)n_rows, (long long)n_cols);
+    return FAT_ERR_SHAPE;
+  }
+  return FAT_OK;
+}
+
+}  // namespace
+}  // namespace fat
+
+using namespace fat;
+
+extern "C" {
+
+int fat_swiglu_fwd(const void* gate, const void* value, void* out, int64_t n_rows, int64_t n_cols,
+                   int64_t gs, int64_t vs, int64_t os, int dtype, void* stream) {
+  if (int rc = check_2d("swiglu_fwd", n_rows, n_cols)) return rc;
+  if (n_rows == 0) return FAT_OK;
+  if (!gate || !value || !out) { set_error("swiglu_fwd: null pointer"); return FAT_ERR_NULL; }
+  FAT_DTYPE_SWITCH(dtype, swiglu_fwd_t<T>(gate, value, out, n_rows, n_cols, gs, vs, os, (cudaStream_t)stream));
+}
+
+int fat_swiglu_bwd(const void* d_out, const void* gate, const void* value, void* d_gate, void* d_value,
+                   int64_t n_rows, int64_t n_cols, int64_t dos, int64_t gs, int64_t vs, int64_t dgs, int64_t dvs,
+                   int dtype, void* stream) {
+  if (int rc = check_2d("swiglu_bwd", n_rows, n_cols)) return rc;
+  if (n_rows == 0) return FAT_OK;
+  if (!d_out || !gate || !value || !d_gate || !d_value) { set_error("swiglu_bwd: null pointer"); return FAT_ERR_NULL; }
+  FAT_DTYPE_SWITCH(dtype, swiglu_bwd_t<T>(d_out, gate, value, d_gate, d_value, n_rows, n_cols, dos, gs, vs, dgs, dvs,
+                                          (cudaStream_t)stream));
+}
+
+int fat_norm_fwd(const void* x, const void* weight, void* y, float* mean, int64_t n_rows, int64_t n_cols,
+                 int64_t xs, int64_t ys, double eps, int dtype, void* stream) {
+  if (int rc = check_2d("norm_fwd", n_rows, n_cols)) return rc;
+  if (n_rows == 0) return FAT_OK;
+  if (!x || !weight || !y || !mean) { set_error("norm_fwd: null pointer"); return FAT_ERR_NULL; }
+  FAT_DTYPE_SWITCH(dtype, norm_fwd_t<T>(x, weight, y, mean, n_rows, n_cols, xs, ys, eps, (cudaStream_t)stream));
+}
+
+size_t fat_norm_bwd_workspace_bytes(int64_t n_rows, int64_t n_cols, int dtype) {
+  (void)n_rows;
+  if (n_cols <= 0) return 0;
+  return size_t(kNormBwdMaxBlocks) * size_t(n_cols) * (dtype == FAT_F64 ? 8 : 4);
+}
+
+int fat_norm_bwd(const void* d_out, const void* x, const void* weight, const float* mean, void* d_x, void* d_weight,
+                 void* workspace, size_t workspace_bytes, int64_t n_rows, int64_t n_cols,
+                 int64_t dos, int64_t xs, int64_t dxs, double eps, int dtype, void* stream) {
+  if (int rc = check_2d("norm_bwd", n_rows, n_cols)) return rc;
+  if (!d_weight || !weight) { set_error("norm_bwd: null pointer"); return FAT_ERR_NULL; }
+  if (n_rows > 0 && (!d_out || !x || !mean || !d_x)) { set_error("norm_bwd: null pointer"); return FAT_ERR_NULL; }
+  if (!workspace) { set_error("norm_bwd: null workspace"); return FAT_ERR_WORKSPACE; }
+  FAT_DTYPE_SWITCH(dtype, norm_bwd_t<T>(d_out, x, weight, mean, d_x, d_weight, workspace, workspace_bytes, n_rows, n_cols,
+                                        dos, xs, dxs, eps, (cudaStream_t)stream));
+}
+
+int fat_softmax_fwd(const void* x, void* p, int64_t n_rows, int64_t n_cols, int64_t xs, int64_t ps,
+                    double eps, int dtype, void* stream) {
+  if (int rc = check_2d("softmax_fwd", n_rows, n_cols)) return rc;
+  if (n_rows == 0) return FAT_OK;
+  if (!x || !p) { set_error("softmax_fwd: null pointer"); return FAT_ERR_NULL; }
+  FAT_DTYPE_SWITCH(dtype, softmax_fwd_t<T>(x, p, n_rows, n_cols, xs, ps, eps, (cudaStream_t)stream));
+}
+
+int fat_softmax_bwd(const void* d_out, const void* x, void* d_x, int64_t n_rows, int64_t n_cols,
+                    int64_t dos, int64_t xs, int64_t dxs, double eps, int dtype, void* stream) {
+  if (int rc = check_2d("softmax_bwd", n_rows, n_cols)) return rc;
+  if (n_rows == 0) return FAT_OK;
+  if (!d_out || !x || !d_x) { set_error("softmax_bwd: null pointer"); return FAT_ERR_NULL; }
+  FAT_DTYPE_SWITCH(dtype, softmax_bwd_t<T>(d_out, x, d_x, n_rows, n_cols, dos, xs, dxs, eps, (cudaStream_t)stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,91 @@
+"""Fused element-wise / row operators: rational softmax, rational SwiGLU, mean-error norm.
+
+Host-side mirror of the reference's ``fused_ops.py`` (autograd Functions 435-599 and the
+convenience functions 606-636): same names, argument meaning and assertion behaviour.  The
+work is done by the sm_100a kernels behind ``torch.ops.algebraic.*``; CPU tensors are
+rejected (this package carries no fallback implementation).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops  # noqa: F401  (registers torch.ops.algebraic)
+
+EPS = 1e-6      # added to sums / means, never inside sigma (reference fused_ops.py:20)
+NEG_INF = -1e4  # kept for API parity (reference fused_ops.py:21); the kernels skip masked keys instead
+
+_alg = torch.ops.algebraic
+
+
+class RationalSoftmax(torch.autograd.Function):
+    """p = sigma(x)^4 / (sum sigma(x)^4 + eps) over the last dimension (reference fused_ops.py:435-487)."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, eps: float = EPS) -> torch.Tensor:
+        assert x.is_cuda, "Input must be on CUDA"
+        out = _alg.softmax_fwd(x, eps)
+        ctx.save_for_backward(x)
+        ctx.eps = eps
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        (x,) = ctx.saved_tensors
+        return _alg.softmax_bwd(grad_output, x, ctx.eps), None
+
+
+class RationalSwiGLU(torch.autograd.Function):
+    """out = gate * sigma(gate) * value (reference fused_ops.py:490-539)."""
+
+    @staticmethod
+    def forward(ctx, gate: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
+        assert gate.is_cuda and value.is_cuda, "Inputs must be on CUDA"
+        out = _alg.swiglu_fwd(gate, value)
+        ctx.save_for_backward(gate, value)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        gate, value = ctx.saved_tensors
+        return _alg.swiglu_bwd(grad_output, gate, value)
+
+
+class MeanErrorNorm(torch.autograd.Function):
+    """y = x / (mean|x| + eps) * weight (reference fused_ops.py:542-599); returns (d_x, d_weight, None)."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, weight: torch.Tensor, eps: float = EPS) -> torch.Tensor:
+        assert x.is_cuda, "Input must be on CUDA"
+        y, mean = _alg.norm_fwd(x, weight, eps)
+        ctx.save_for_backward(x, weight, mean)
+        ctx.eps = eps
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        x, weight, mean = ctx.saved_tensors
+        d_x, d_w = _alg.norm_bwd(grad_output, x, weight, mean, ctx.eps)
+        return d_x, d_w, None
+
+
+def _require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: CUDA tensor required — this build has no CPU fallback")
+
+
+def rational_softmax(x: torch.Tensor, eps: float = EPS) -> torch.Tensor:
+    """Apply rational softmax to the last dimension (reference fused_ops.py:606-615)."""
+    _require_cuda(x, "rational_softmax")
+    return RationalSoftmax.apply(x, eps)
+
+
+def rational_swiglu(gate: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
+    """Apply the rational SwiGLU activation (reference fused_ops.py:618-626)."""
+    _require_cuda(gate, "rational_swiglu")
+    return RationalSwiGLU.apply(gate, value)
+
+
+def mean_error_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = EPS) -> torch.Tensor:
+    """Apply mean-error normalisation (reference fused_ops.py:629-636)."""
+    _require_cuda(x, "mean_error_norm")
+    return MeanErrorNorm.apply(x, weight, eps)

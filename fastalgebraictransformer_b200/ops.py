@@ -1,0 +1,324 @@
+"""``torch.library`` operators of the ``algebraic`` namespace, implemented by the C ABI.
+
+Each operator allocates its outputs with torch, passes raw pointers / strides / the current
+CUDA stream to libfat_b200.so and turns a non-zero return code into ``RuntimeError``.
+Autograd formulas are registered on the forward operators, so they compose with
+``torch.utils.checkpoint`` (non-reentrant), DDP hooks and ``torch.autograd.grad``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+_NS = "algebraic"
+_libdef = torch.library.Library(_NS, "DEF")
+_libdef.define("swiglu_fwd(Tensor gate, Tensor value) -> Tensor")
+_libdef.define("swiglu_bwd(Tensor d_out, Tensor gate, Tensor value) -> (Tensor, Tensor)")
+_libdef.define("norm_fwd(Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)")
+_libdef.define("norm_bwd(Tensor d_out, Tensor x, Tensor weight, Tensor mean, float eps) -> (Tensor, Tensor)")
+_libdef.define("softmax_fwd(Tensor x, float eps) -> Tensor")
+_libdef.define("softmax_bwd(Tensor d_out, Tensor x, float eps) -> Tensor")
+_libdef.define("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor slopes, float scale, bool causal, float eps, "
+               "int path, bool token_major_out) -> (Tensor, Tensor)")
+_libdef.define("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor L, Tensor d_out, Tensor slopes, "
+               "float scale, bool causal, float eps, int path) -> (Tensor, Tensor, Tensor)")
+
+
+def _p(t: Tensor) -> int:
+    return t.data_ptr()
+
+
+def _rows(t: Tensor) -> Tensor:
+    """View ``t`` as [n_rows, n_cols] with unit column stride, copying only when it must."""
+    n = t.shape[-1]
+    if t.dim() == 2 and t.stride(1) == 1:
+        return t
+    if t.stride(-1) == 1 or n == 1:
+        try:
+            return t.view(-1, n)           # fails for views that cannot be flattened
+        except RuntimeError:
+            pass
+        # a slice of the last dimension of a dense tensor (e.g. one half of chunk(2,-1)): rows are
+        # equally spaced, so (n_rows, row_stride) describes it without a copy
+        st = t.stride(-2) if t.dim() >= 2 else n
+        ok, expect = True, st
+        for d in range(t.dim() - 2, -1, -1):
+            if t.shape[d] != 1 and t.stride(d) != expect:
+                ok = False
+                break
+            expect = t.stride(d) * t.shape[d]
+        if ok:
+            return t.as_strided((t.numel() // n, n), (st, 1), t.storage_offset())
+    return t.contiguous().view(-1, n)
+
+
+def _cuda_check(*ts: Tensor) -> None:
+    dev = ts[0].device
+    for t in ts:
+        if not t.is_cuda:
+            raise RuntimeError("algebraic ops run on CUDA tensors only (there is no CPU fallback)")
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+
+
+# ----------------------------------------------------------------------------- SwiGLU
+def _swiglu_fwd(gate: Tensor, value: Tensor) -> Tensor:
+    _cuda_check(gate, value)
+    assert gate.shape == value.shape and gate.dtype == value.dtype
+    out = torch.empty(gate.shape, dtype=gate.dtype, device=gate.device)
+    if gate.numel() == 0:
+        return out
+    g, v, o = _rows(gate), _rows(value), out.view(-1, gate.shape[-1])
+    with _lib.device_guard(gate.device):
+        _lib.check(_lib.lib().fat_swiglu_fwd(_p(g), _p(v), _p(o), g.shape[0], g.shape[1], g.stride(0), v.stride(0),
+                                             o.stride(0), _lib.dtype_tag(gate), _lib.stream_ptr(gate.device)))
+    return out
+
+
+def _swiglu_bwd(d_out: Tensor, gate: Tensor, value: Tensor) -> Tuple[Tensor, Tensor]:
+    _cuda_check(d_out, gate, value)
+    n = gate.shape[-1]
+    # both gradients live in one [rows, 2n] buffer: when gate/value were the two halves of a packed
+    # projection, autograd's concatenation of the halves becomes a no-op copy target of the same layout
+    packed = torch.empty(gate.shape[:-1] + (2 * n,), dtype=gate.dtype, device=gate.device)
+    d_gate, d_value = packed[..., :n], packed[..., n:]
+    if gate.numel() == 0:
+        return d_gate, d_value
+    go, g, v = _rows(d_out), _rows(gate), _rows(value)
+    dg, dv = _rows(d_gate), _rows(d_value)
+    with _lib.device_guard(gate.device):
+        _lib.check(_lib.lib().fat_swiglu_bwd(_p(go), _p(g), _p(v), _p(dg), _p(dv), g.shape[0], n, go.stride(0),
+                                             g.stride(0), v.stride(0), dg.stride(0), dv.stride(0),
+                                             _lib.dtype_tag(gate), _lib.stream_ptr(gate.device)))
+    return d_gate, d_value
+
+
+# ----------------------------------------------------------------------------- mean-error norm
+def _norm_fwd(x: Tensor, weight: Tensor, eps: float) -> Tuple[Tensor, Tensor]:
+    _cuda_check(x, weight)
+    n = x.shape[-1]
+    assert weight.shape == (n,), "weight must be [n_cols]"
+    w = weight.to(x.dtype).contiguous()
+    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    xr = _rows(x)
+    mean = torch.empty(xr.shape[0], dtype=torch.float32, device=x.device)
+    if x.numel():
+        yr = y.view(-1, n)
+        with _lib.device_guard(x.device):
+            _lib.check(_lib.lib().fat_norm_fwd(_p(xr), _p(w), _p(yr), _p(mean), xr.shape[0], n, xr.stride(0),
+                                               yr.stride(0), eps, _lib.dtype_tag(x), _lib.stream_ptr(x.device)))
+    return y, mean
+
+
+def _norm_bwd(d_out: Tensor, x: Tensor, weight: Tensor, mean: Tensor, eps: float) -> Tuple[Tensor, Tensor]:
+    _cuda_check(d_out, x, weight, mean)
+    n = x.shape[-1]
+    w = weight.to(x.dtype).contiguous()
+    d_x = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    d_w = torch.empty(n, dtype=x.dtype, device=x.device)
+    go, xr, dxr = _rows(d_out), _rows(x), d_x.view(-1, n)
+    tag = _lib.dtype_tag(x)
+    L = _lib.lib()
+    ws_bytes = L.fat_norm_bwd_workspace_bytes(xr.shape[0], n, tag)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    with _lib.device_guard(x.device):
+        _lib.check(L.fat_norm_bwd(_p(go), _p(xr), _p(w), _p(mean), _p(dxr), _p(d_w), _p(ws), ws_bytes, xr.shape[0], n,
+                                  go.stride(0) if go.numel() else n, xr.stride(0) if xr.numel() else n, n,
+                                  eps, tag, _lib.stream_ptr(x.device)))
+    return d_x, d_w.to(weight.dtype)
+
+
+# ----------------------------------------------------------------------------- rational softmax
+def _softmax_fwd(x: Tensor, eps: float) -> Tensor:
+    _cuda_check(x)
+    n = x.shape[-1]
+    p = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    if x.numel():
+        xr, pr = _rows(x), p.view(-1, n)
+        with _lib.device_guard(x.device):
+            _lib.check(_lib.lib().fat_softmax_fwd(_p(xr), _p(pr), xr.shape[0], n, xr.stride(0), pr.stride(0), eps,
+                                                  _lib.dtype_tag(x), _lib.stream_ptr(x.device)))
+    return p
+
+
+def _softmax_bwd(d_out: Tensor, x: Tensor, eps: float) -> Tensor:
+    _cuda_check(d_out, x)
+    n = x.shape[-1]
+    d_x = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    if x.numel():
+        go, xr, dxr = _rows(d_out), _rows(x), d_x.view(-1, n)
+        with _lib.device_guard(x.device):
+            _lib.check(_lib.lib().fat_softmax_bwd(_p(go), _p(xr), _p(dxr), xr.shape[0], n, go.stride(0), xr.stride(0),
+                                                  dxr.stride(0), eps, _lib.dtype_tag(x), _lib.stream_ptr(x.device)))
+    return d_x
+
+
+# ----------------------------------------------------------------------------- rational attention
+def _unit_d(t: Tensor) -> Tensor:
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def _is_token_major(t: Tensor) -> bool:
+    """[B,H,T,D] view whose memory order is (B,T,H,D), e.g. a slice of a packed QKV projection."""
+    return t.dim() == 4 and t.shape[1] > 1 and t.shape[2] > 1 and t.stride(1) < t.stride(2)
+
+
+def _alloc_bhtd(like: Tensor, token_major: bool) -> Tensor:
+    B, H, T, D = like.shape
+    if token_major:
+        return torch.empty((B, T, H, D), dtype=like.dtype, device=like.device).permute(0, 2, 1, 3)
+    return torch.empty((B, H, T, D), dtype=like.dtype, device=like.device)
+
+
+def _attn_fwd(q: Tensor, k: Tensor, v: Tensor, slopes: Tensor, scale: float, causal: bool, eps: float,
+              path: int, token_major_out: bool) -> Tuple[Tensor, Tensor]:
+    _cuda_check(q, k, v, slopes)
+    assert q.dim() == 4 and q.shape == k.shape == v.shape and q.dtype == k.dtype == v.dtype
+    B, H, T, D = q.shape
+    q, k, v = _unit_d(q), _unit_d(k), _unit_d(v)
+    sl = slopes.to(torch.float32).contiguous()
+    assert sl.numel() == H, "alibi_slopes must hold one slope per head"
+    out = _alloc_bhtd(q, token_major_out)
+    L = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+    if q.numel():
+        with _lib.device_guard(q.device):
+            _lib.check(_lib.lib().fat_attn_fwd(
+                _p(q), _p(k), _p(v), _p(sl), _p(out), _p(L), B, H, T, D,
+                _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out),
+                scale, eps, int(causal), _lib.dtype_tag(q), path,
+                _p(_lib.device_status(q.device)), _lib.stream_ptr(q.device)))
+    return out, L
+
+
+def _attn_bwd(q: Tensor, k: Tensor, v: Tensor, out: Tensor, L: Tensor, d_out: Tensor, slopes: Tensor,
+              scale: float, causal: bool, eps: float, path: int) -> Tuple[Tensor, Tensor, Tensor]:
+    _cuda_check(q, k, v, out, L, d_out, slopes)
+    B, H, T, D = q.shape
+    q, k, v, out, d_out = _unit_d(q), _unit_d(k), _unit_d(v), _unit_d(out), _unit_d(d_out)
+    sl = slopes.to(torch.float32).contiguous()
+    Lc = L.contiguous()
+    if _is_token_major(q):
+        # gradients of the three slices of a packed projection go into one [B,T,3,H,D] buffer
+        packed = torch.empty((B, T, 3, H, D), dtype=q.dtype, device=q.device)
+        d_q, d_k, d_v = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    else:
+        d_q, d_k, d_v = (torch.empty((B, H, T, D), dtype=q.dtype, device=q.device) for _ in range(3))
+    if q.numel():
+        lib = _lib.lib()
+        tag = _lib.dtype_tag(q)
+        ws_bytes = lib.fat_attn_bwd_workspace_bytes(B, H, T, D, tag, path)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        with _lib.device_guard(q.device):
+            _lib.check(lib.fat_attn_bwd(
+                _p(q), _p(k), _p(v), _p(out), _p(Lc), _p(d_out), _p(sl), _p(d_q), _p(d_k), _p(d_v),
+                _p(ws), ws_bytes, B, H, T, D,
+                _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out), _lib.strides3(d_out),
+                _lib.strides3(d_q), _lib.strides3(d_k), _lib.strides3(d_v),
+                scale, eps, int(causal), tag, path, _p(_lib.device_status(q.device)), _lib.stream_ptr(q.device)))
+    return d_q, d_k, d_v
+
+
+for _name, _fn in (("swiglu_fwd", _swiglu_fwd), ("swiglu_bwd", _swiglu_bwd), ("norm_fwd", _norm_fwd),
+                   ("norm_bwd", _norm_bwd), ("softmax_fwd", _softmax_fwd), ("softmax_bwd", _softmax_bwd),
+                   ("attn_fwd", _attn_fwd), ("attn_bwd", _attn_bwd)):
+    _libdef.impl(_name, _fn, "CUDA")
+
+
+# ----------------------------------------------------------------------------- shape functions (meta)
+@torch.library.register_fake(f"{_NS}::swiglu_fwd")
+def _(gate, value):
+    return torch.empty_like(gate, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{_NS}::swiglu_bwd")
+def _(d_out, gate, value):
+    n = gate.shape[-1]
+    packed = gate.new_empty(gate.shape[:-1] + (2 * n,))
+    return packed[..., :n], packed[..., n:]
+
+
+@torch.library.register_fake(f"{_NS}::norm_fwd")
+def _(x, weight, eps):
+    return torch.empty_like(x, memory_format=torch.contiguous_format), x.new_empty(x.numel() // x.shape[-1], dtype=torch.float32)
+
+
+@torch.library.register_fake(f"{_NS}::norm_bwd")
+def _(d_out, x, weight, mean, eps):
+    return torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(weight)
+
+
+@torch.library.register_fake(f"{_NS}::softmax_fwd")
+def _(x, eps):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{_NS}::softmax_bwd")
+def _(d_out, x, eps):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{_NS}::attn_fwd")
+def _(q, k, v, slopes, scale, causal, eps, path, token_major_out):
+    B, H, T, D = q.shape
+    out = q.new_empty((B, T, H, D)).permute(0, 2, 1, 3) if token_major_out else q.new_empty((B, H, T, D))
+    return out, q.new_empty((B, H, T), dtype=torch.float32)
+
+
+@torch.library.register_fake(f"{_NS}::attn_bwd")
+def _(q, k, v, out, L, d_out, slopes, scale, causal, eps, path):
+    return tuple(q.new_empty(q.shape) for _ in range(3))
+
+
+# ----------------------------------------------------------------------------- autograd formulas
+def _swiglu_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs)
+
+
+def _swiglu_backward(ctx, d_out):
+    gate, value = ctx.saved_tensors
+    return torch.ops.algebraic.swiglu_bwd(d_out, gate, value)
+
+
+def _norm_setup(ctx, inputs, output):
+    x, weight, eps = inputs
+    ctx.save_for_backward(x, weight, output[1])
+    ctx.eps = eps
+
+
+def _norm_backward(ctx, d_y, d_mean):
+    x, weight, mean = ctx.saved_tensors
+    d_x, d_w = torch.ops.algebraic.norm_bwd(d_y, x, weight, mean, ctx.eps)
+    return d_x, d_w, None
+
+
+def _softmax_setup(ctx, inputs, output):
+    ctx.save_for_backward(inputs[0])
+    ctx.eps = inputs[1]
+
+
+def _softmax_backward(ctx, d_out):
+    (x,) = ctx.saved_tensors
+    return torch.ops.algebraic.softmax_bwd(d_out, x, ctx.eps), None
+
+
+def _attn_setup(ctx, inputs, output):
+    q, k, v, slopes, scale, causal, eps, path, _ = inputs
+    ctx.save_for_backward(q, k, v, output[0], output[1], slopes)
+    ctx.args = (scale, causal, eps, path)
+
+
+def _attn_backward(ctx, d_out, d_L):
+    q, k, v, out, L, slopes = ctx.saved_tensors
+    d_q, d_k, d_v = torch.ops.algebraic.attn_bwd(q, k, v, out, L, d_out, slopes, *ctx.args)
+    return d_q, d_k, d_v, None, None, None, None, None, None
+
+
+torch.library.register_autograd(f"{_NS}::swiglu_fwd", _swiglu_backward, setup_context=_swiglu_setup)
+torch.library.register_autograd(f"{_NS}::norm_fwd", _norm_backward, setup_context=_norm_setup)
+torch.library.register_autograd(f"{_NS}::softmax_fwd", _softmax_backward, setup_context=_softmax_setup)
+torch.library.register_autograd(f"{_NS}::attn_fwd", _attn_backward, setup_context=_attn_setup)

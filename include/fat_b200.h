@@ -1,0 +1,170 @@
+/*
+ * fat_b200.h — C ABI of the B200 (sm_100a) Algebraic-Transformer hot path.
+ *
+ * One shared library (libfat_b200.so) exports these entry points.  They take raw device
+ * pointers, sizes, element strides, a dtype tag, scalars and a CUDA stream (passed as
+ * void* so that no CUDA header is needed to bind them).  They never allocate device
+ * memory, never synchronise, never throw: each returns FAT_OK or one of the error codes
+ * below, and a human-readable detail is available from fat_last_error().  All launches
+ * are asynchronous on the given stream.  The caller owns every buffer, including scratch
+ * ("workspace") whose size is reported by the matching *_workspace_bytes function.
+ *
+ * Each entry point replaces one launcher of the reference implementation
+ * (SkyeGunasekaran/fastAlgebraicTransformer); the citation names the reference file and
+ * lines whose behaviour it reproduces.
+ */
+#ifndef FAT_B200_H
+#define FAT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define FAT_API __attribute__((visibility("default")))
+#else
+#define FAT_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of tensor arguments */
+enum fat_dtype { FAT_F32 = 0, FAT_BF16 = 1, FAT_F16 = 2, FAT_F64 = 3 };
+
+/* return codes */
+enum fat_status {
+  FAT_OK = 0,
+  FAT_ERR_DTYPE = 1,        /* dtype tag not supported by this entry point              */
+  FAT_ERR_SHAPE = 2,        /* negative / zero / inconsistent sizes                     */
+  FAT_ERR_UNSUPPORTED = 3,  /* valid request outside what the kernels implement         */
+  FAT_ERR_ALIGNMENT = 4,    /* a forced fast path needs aligned pointers / strides      */
+  FAT_ERR_WORKSPACE = 5,    /* workspace pointer null or too small                      */
+  FAT_ERR_LAUNCH = 6,       /* the CUDA runtime rejected a launch (see fat_last_error)  */
+  FAT_ERR_NULL = 7          /* a required pointer is null                               */
+};
+
+/* attention kernel family selector */
+enum fat_attn_path {
+  FAT_PATH_AUTO = 0,        /* tensor-core kernels when eligible, else the SIMT kernels */
+  FAT_PATH_SIMT = 1,        /* fp32-accumulating CUDA-core kernels (any dtype, D<=128)  */
+  FAT_PATH_TENSOR = 2       /* tcgen05/TMEM kernels (bf16/f16, D in {64,128}); error if not eligible */
+};
+
+/* Device-side status word written by kernels whose bounded waits ran out.  Bit layout:
+ * 0 = never written; otherwise (code << 24) | detail.  The caller allocates one int32 per
+ * device, zeroes it, passes it to the attention entry points and reads it back when it
+ * wants to know (reading needs a synchronise, so it is left to the caller). */
+enum fat_device_status { FAT_DEV_OK = 0, FAT_DEV_WAIT_TIMEOUT = 1 };
+
+FAT_API int fat_version(void);
+FAT_API const char* fat_error_string(int code);
+FAT_API const char* fat_last_error(void);   /* thread-local detail of the last non-zero return */
+
+/* ------------------------------------------------------------------------------------
+ * Rational SwiGLU.  out = gate * sigma(gate) * value, sigma(x) = (x/(|x|+1)+1)/2.
+ * Tensors are [n_rows, n_cols] with unit column stride and the given row strides (in
+ * elements), so the two halves of a packed [rows, 2*ffn] projection can be passed in place.
+ * Replaces RationalSwiGLU.forward / swiglu_fwd_kernel   (fused_ops.py:196-229, 490-516)
+ * and      RationalSwiGLU.backward / swiglu_bwd_kernel  (fused_ops.py:236-288, 518-539).
+ * dtypes: F32, BF16, F16, F64.
+ * ---------------------------------------------------------------------------------- */
+FAT_API int fat_swiglu_fwd(const void* gate, const void* value, void* out,
+                   int64_t n_rows, int64_t n_cols,
+                   int64_t gate_row_stride, int64_t value_row_stride, int64_t out_row_stride,
+                   int dtype, void* stream);
+
+FAT_API int fat_swiglu_bwd(const void* d_out, const void* gate, const void* value,
+                   void* d_gate, void* d_value,
+                   int64_t n_rows, int64_t n_cols,
+                   int64_t d_out_row_stride, int64_t gate_row_stride, int64_t value_row_stride,
+                   int64_t d_gate_row_stride, int64_t d_value_row_stride,
+                   int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Mean-error normalisation.  mean_r = mean_c |x_rc| (float32, [n_rows], saved for the
+ * backward), y = x / (mean + eps) * weight.
+ * Replaces MeanErrorNorm.forward / mean_error_norm_fwd_kernel (fused_ops.py:295-342, 542-569).
+ * The backward produces d_x AND d_weight (the reference computes d_weight with two extra
+ * PyTorch passes, fused_ops.py:593-597; here it comes from per-block partial sums held in
+ * the workspace and a second small reduction kernel).  sign(0) = 0.
+ * Replaces MeanErrorNorm.backward / mean_error_norm_bwd_kernel (fused_ops.py:349-423, 572-599).
+ * d_weight has the dtype of x.  dtypes: F32, BF16, F16, F64.
+ * ---------------------------------------------------------------------------------- */
+FAT_API int fat_norm_fwd(const void* x, const void* weight, void* y, float* mean,
+                 int64_t n_rows, int64_t n_cols, int64_t x_row_stride, int64_t y_row_stride,
+                 double eps, int dtype, void* stream);
+
+FAT_API size_t fat_norm_bwd_workspace_bytes(int64_t n_rows, int64_t n_cols, int dtype);
+
+FAT_API int fat_norm_bwd(const void* d_out, const void* x, const void* weight, const float* mean,
+                 void* d_x, void* d_weight, void* workspace, size_t workspace_bytes,
+                 int64_t n_rows, int64_t n_cols,
+                 int64_t d_out_row_stride, int64_t x_row_stride, int64_t d_x_row_stride,
+                 double eps, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Rational softmax over the last dimension.  p = sigma(x)^4 / (sum_c sigma(x)^4 + eps).
+ * Replaces RationalSoftmax.forward / rational_softmax_fwd_kernel (fused_ops.py:52-106, 435-462).
+ * The backward recomputes p from x (the row is held in registers), so it reads only d_out
+ * and x:  d_x = 2 sigma^3 r^2 / (Z+eps) * (d_out - sum_c d_out p),  r = 1/(|x|+1).
+ * Replaces RationalSoftmax.backward / rational_softmax_bwd_kernel (fused_ops.py:113-189, 464-487).
+ * dtypes: F32, BF16, F16, F64.
+ * ---------------------------------------------------------------------------------- */
+FAT_API int fat_softmax_fwd(const void* x, void* p, int64_t n_rows, int64_t n_cols,
+                    int64_t x_row_stride, int64_t p_row_stride,
+                    double eps, int dtype, void* stream);
+
+FAT_API int fat_softmax_bwd(const void* d_out, const void* x, void* d_x,
+                    int64_t n_rows, int64_t n_cols,
+                    int64_t d_out_row_stride, int64_t x_row_stride, int64_t d_x_row_stride,
+                    double eps, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Rational attention with ALiBi.  For head h, query i, key j (j <= i when causal):
+ *     s_ij = scale * q_i.k_j - slope_h * |i-j|,   f_ij = sigma(s_ij)^4,
+ *     L_i  = sum_j f_ij  (float32 [B,H,T], contiguous, WITHOUT eps),
+ *     O_i  = sum_j f_ij v_j / (L_i + eps).
+ * q, k, v, out are [B,H,T,D] with unit stride along D; *_strides point to three element
+ * strides {batch, head, token}, so views of a packed [B,T,3,H,D] projection are consumed
+ * in place.  slopes is float32 [H].  status may be null.
+ * Replaces rational_attention_forward / rational_attention_fwd_kernel (forward.py:49-159, 267-319).
+ * dtypes: F32, BF16, F16.  D <= 128.
+ * ---------------------------------------------------------------------------------- */
+FAT_API int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slopes,
+                 void* out, float* L,
+                 int B, int H, int T, int D,
+                 const int64_t* q_strides, const int64_t* k_strides,
+                 const int64_t* v_strides, const int64_t* out_strides,
+                 double scale, double eps, int causal, int dtype, int path,
+                 int* status, void* stream);
+
+/* Backward: given d_out, the saved out and L, produces d_q, d_k, d_v (same dtype as q):
+ *     Delta_i = d_out_i . out_i,   dP_ij = d_out_i . v_j,   r = 1/(|s|+1),
+ *     dS_ij = 2 sigma^3 r^2 (dP_ij - Delta_i) / (L_i + eps),
+ *     d_q = scale dS k,  d_k = scale dS^T q,  d_v = P^T d_out.
+ * The workspace holds Delta (and, for the tensor-core path, a float32 d_q accumulator).
+ * Replaces rational_attention_backward / rational_attention_bwd_dq_kernel /
+ * rational_attention_bwd_dkv_kernel (backward.py:62-158, 165-266, 273-341).
+ * ---------------------------------------------------------------------------------- */
+FAT_API size_t fat_attn_bwd_workspace_bytes(int B, int H, int T, int D, int dtype, int path);
+
+FAT_API int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, const float* L,
+                 const void* d_out, const float* slopes,
+                 void* d_q, void* d_k, void* d_v,
+                 void* workspace, size_t workspace_bytes,
+                 int B, int H, int T, int D,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const int64_t* out_strides, const int64_t* d_out_strides,
+                 const int64_t* d_q_strides, const int64_t* d_k_strides, const int64_t* d_v_strides,
+                 double scale, double eps, int causal, int dtype, int path,
+                 int* status, void* stream);
+
+/* Which kernel family FAT_PATH_AUTO would pick for these arguments (FAT_PATH_SIMT or
+ * FAT_PATH_TENSOR).  Host-only, no launch. */
+FAT_API int fat_attn_select_path(int T, int D, int dtype, int aligned16);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FAT_B200_H */

@@ -1,0 +1,172 @@
+"""Parity of the rational-attention kernels with the CPU oracle and the golden vectors (B200)."""
+import math
+
+import pytest
+import torch
+
+from conftest import bf16_violations, load_golden, norm_max_err
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+FP32_TOL = 1e-5
+
+
+def fat():
+    import fastalgebraictransformer_b200 as m
+    return m
+
+
+def run_attention(q, k, v, go, slopes, scale, causal=True, path=0, eps=1e-6):
+    from fastalgebraictransformer_b200.backward import RationalAttentionFunction
+    leaves = [t.detach().to(DEV).requires_grad_(True) for t in (q, k, v)]
+    out = RationalAttentionFunction.apply(*leaves, slopes.to(DEV), scale, causal, eps, path, False)
+    out.backward(go.to(DEV))
+    fat().check_device_status()
+    return out.detach(), leaves[0].grad, leaves[1].grad, leaves[2].grad
+
+
+def gen_qkv(seed, B, H, T, D, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(B, H, T, D, generator=g).to(dtype) for _ in range(4)]
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c", "d", "e"])
+@pytest.mark.parametrize("path", [1])
+def test_golden_fp32(tag, path):
+    g = load_golden(f"attention_{tag}")
+    out, dq, dk, dv = run_attention(g["q"], g["k"], g["v"], g["d_out"], g["slopes"], g["scale"], path=path)
+    for got, key in ((out, "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert norm_max_err(got, g[key]) < FP32_TOL, f"{key}: {norm_max_err(got, g[key]):.2e}"
+        # the reference's own thresholds (tests.py:210-211): fwd < 1e-3, grads < 1e-2 max abs
+        assert (got.cpu() - g[key]).abs().max() < (1e-3 if key == "out" else 1e-2)
+
+
+SHAPES = [(1, 1, 1, 8), (1, 2, 2, 16), (2, 3, 17, 32), (1, 2, 63, 64), (1, 2, 64, 64), (1, 2, 65, 64), (1, 4, 127, 32),
+          (1, 2, 129, 128), (2, 2, 200, 40), (1, 1, 300, 100), (1, 12, 256, 64)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_fp32_vs_oracle(shape):
+    B, H, T, D = shape
+    q, k, v, go = gen_qkv(21, B, H, T, D)
+    slopes = oracle.compute_alibi_slopes(H)
+    scale = 1.0 / math.sqrt(D)
+    out, dq, dk, dv = run_attention(q, k, v, go, slopes, scale, path=1)
+    want = oracle.rational_attention_grads(q, k, v, go, slopes, scale)
+    for got, w, name in zip((out, dq, dk, dv), want, ("out", "dq", "dk", "dv")):
+        assert norm_max_err(got, w) < FP32_TOL, f"{name}: {norm_max_err(got, w):.2e}"
+
+
+def test_config1_fp32_closed_form_slopes():
+    """BASELINE config 1: B=2,H=12,S=512,D=64 float32, slopes 2^(-8(i+1)/12)."""
+    B, H, T, D = 2, 12, 512, 64
+    g = torch.Generator().manual_seed(1234 + 0)
+    q, k, v, go = (torch.randn(B, H, T, D, generator=g) for _ in range(4))
+    slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / H) for i in range(H)])
+    out, dq, dk, dv = run_attention(q, k, v, go, slopes, 0.125)
+    want = oracle.rational_attention_grads(q, k, v, go, slopes, 0.125)
+    for got, w, name in zip((out, dq, dk, dv), want, ("out", "dq", "dk", "dv")):
+        assert norm_max_err(got, w) < FP32_TOL, f"{name}: {norm_max_err(got, w):.2e}"
+    # and once with the library's own slopes for 12 heads (not a power of two)
+    slopes = fat().compute_alibi_slopes(12)
+    out = run_attention(q, k, v, go, slopes, 0.125)[0]
+    assert norm_max_err(out, oracle.rational_attention(q, k, v, slopes, 0.125)) < FP32_TOL
+
+
+def test_forward_returns_row_sums_without_eps():
+    B, H, T, D = 1, 2, 70, 32
+    q, k, v, _ = gen_qkv(22, B, H, T, D)
+    slopes = oracle.compute_alibi_slopes(H)
+    out, L = fat().rational_attention_forward(q.to(DEV), k.to(DEV), v.to(DEV), slopes.to(DEV), 0.2)
+    assert L.dtype == torch.float32 and L.shape == (B, H, T)
+    assert norm_max_err(L, oracle.rational_attention_rowsum(q, k, slopes, 0.2)) < FP32_TOL
+    assert norm_max_err(out, oracle.rational_attention(q, k, v, slopes, 0.2)) < FP32_TOL
+
+
+def test_explicit_backward_entry_point():
+    B, H, T, D = 1, 2, 50, 32
+    q, k, v, go = gen_qkv(23, B, H, T, D)
+    slopes = oracle.compute_alibi_slopes(H)
+    f = fat()
+    qd, kd, vd, god, sd = (t.to(DEV) for t in (q, k, v, go, slopes))
+    out, L = f.rational_attention_forward(qd, kd, vd, sd, 0.3)
+    dq, dk, dv = f.rational_attention_backward(qd, kd, vd, out, L, god, sd, 0.3)
+    want = oracle.rational_attention_grads(q, k, v, go, slopes, 0.3)
+    for got, w in zip((dq, dk, dv), want[1:]):
+        assert norm_max_err(got, w) < FP32_TOL
+
+
+def test_non_causal_extension():
+    """causal=False has no reference behaviour; checked against the oracle with its mask line removed."""
+    B, H, T, D = 1, 2, 90, 32
+    q, k, v, go = gen_qkv(24, B, H, T, D)
+    slopes = oracle.compute_alibi_slopes(H)
+    out, dq, dk, dv = run_attention(q, k, v, go, slopes, 0.2, causal=False, path=1)
+    want = oracle.rational_attention_grads(q, k, v, go, slopes, 0.2, causal=False)
+    for got, w in zip((out, dq, dk, dv), want):
+        assert norm_max_err(got, w) < FP32_TOL
+
+
+def test_strided_views_of_packed_projection():
+    """q, k, v as the model passes them: permuted views of one [B,T,3,H,D] buffer (algebraic_model.py:89-91)."""
+    B, H, T, D = 2, 4, 96, 32
+    g = torch.Generator().manual_seed(25)
+    packed = torch.randn(B, T, 3, H, D, generator=g)
+    go = torch.randn(B, H, T, D, generator=g)
+    slopes = oracle.compute_alibi_slopes(H)
+    pd = packed.to(DEV).requires_grad_(True)
+    q, k, v = pd.permute(2, 0, 3, 1, 4).unbind(0)
+    assert not q.is_contiguous()
+    out = fat().rational_attention(q, k, v, slopes.to(DEV), 0.2)
+    out.backward(go.to(DEV))
+    pr = packed.clone().requires_grad_(True)
+    qr, kr, vr = pr.permute(2, 0, 3, 1, 4).unbind(0)
+    ref = oracle.rational_attention(qr, kr, vr, slopes, 0.2)
+    ref.backward(go)
+    assert norm_max_err(out, ref) < FP32_TOL and norm_max_err(pd.grad, pr.grad) < FP32_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 2, 64, 64), (2, 4, 200, 64), (1, 2, 333, 128), (1, 3, 100, 32), (1, 16, 512, 128)])
+@pytest.mark.parametrize("path", [0, 1])
+def test_low_precision_vs_oracle(shape, dtype, path):
+    """bf16 / fp16: inputs rounded, oracle in float32 on the rounded values, bar rel 2e-2 / abs 1e-2."""
+    B, H, T, D = shape
+    q, k, v, go = gen_qkv(26, B, H, T, D, dtype)
+    slopes = oracle.compute_alibi_slopes(H)
+    scale = 1.0 / math.sqrt(D)
+    out, dq, dk, dv = run_attention(q, k, v, go, slopes, scale, path=path)
+    want = oracle.rational_attention_grads(q.float(), k.float(), v.float(), go.float(), slopes, scale)
+    for got, w, name in zip((out, dq, dk, dv), want, ("out", "dq", "dk", "dv")):
+        bad, nme = bf16_violations(got.float(), w)
+        assert bad == 0.0, f"{name}: {bad:.2e} of elements outside the bar (norm max err {nme:.2e})"
+
+
+def test_deterministic():
+    B, H, T, D = 1, 4, 300, 64
+    q, k, v, go = gen_qkv(27, B, H, T, D, torch.bfloat16)
+    slopes = oracle.compute_alibi_slopes(H)
+    a = run_attention(q, k, v, go, slopes, 0.125)
+    b = run_attention(q, k, v, go, slopes, 0.125)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[3], b[3])
+
+
+def test_config2_slice_bf16():
+    """BASELINE config 2 (B=8,H=16,S=4096,D=128 bf16), one batch element against the oracle, the rest through
+    a property: heads and batch elements are independent, so batch element b of the full run equals a run on it alone."""
+    H, T, D = 16, 4096, 128
+    g = torch.Generator().manual_seed(1234 + 1)
+    q, k, v, go = (torch.randn(2, H, T, D, generator=g).to(torch.bfloat16) for _ in range(4))
+    slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / H) for i in range(H)])
+    scale = 1.0 / math.sqrt(D)
+    full = run_attention(q, k, v, go, slopes, scale)
+    one = run_attention(q[1:], k[1:], v[1:], go[1:], slopes, scale)
+    for a, b in zip(full, one):
+        assert torch.equal(a[1:], b)
+    want = oracle.rational_attention_grads(q[:1, :2].float(), k[:1, :2].float(), v[:1, :2].float(), go[:1, :2].float(),
+                                           slopes[:2], scale)
+    got = run_attention(q[:1, :2], k[:1, :2], v[:1, :2], go[:1, :2], slopes[:2], scale)
+    for a, w, name in zip(got, want, ("out", "dq", "dk", "dv")):
+        bad, nme = bf16_violations(a.float(), w)
+        assert bad == 0.0, f"{name}: {bad:.2e} outside the bar (norm max err {nme:.2e})"

@@ -1,0 +1,202 @@
+"""Parity of the SwiGLU / mean-error-norm / rational-softmax kernels with the CPU oracle (B200)."""
+import pytest
+import torch
+
+from conftest import bf16_violations, load_golden, norm_max_err
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+FP32_TOL = 1e-5      # max|a-b| / max|b|, the bar for float32
+DEV = "cuda"
+
+
+def fat():
+    import fastalgebraictransformer_b200 as m
+    return m
+
+
+def run(fn, inputs, d_out):
+    leaves = [t.detach().to(DEV).requires_grad_(True) for t in inputs]
+    out = fn(*leaves)
+    out.backward(d_out.to(DEV))
+    return out.detach(), [t.grad for t in leaves]
+
+
+def gen(seed, *shapes, std=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return [(torch.randn(*s, generator=g) * std).to(dtype) for s in shapes]
+
+
+def compare(got, want, dtype, what):
+    if dtype in (torch.float32, torch.float64):
+        tol = FP32_TOL if dtype == torch.float32 else 1e-12
+        assert norm_max_err(got, want) < tol, f"{what}: {norm_max_err(got, want):.3e}"
+    else:   # bf16 / fp16: |a-b| <= 1e-2 + 2e-2 |b| on every element
+        bad, nme = bf16_violations(got.float(), want)
+        assert bad == 0.0, f"{what}: {bad:.2e} of elements outside rel 2e-2 / abs 1e-2 (norm max err {nme:.2e})"
+
+
+def oracle_inputs(ts, dtype):
+    """Low-precision inputs are rounded first, then the oracle runs in float32 on the rounded values."""
+    up = torch.float64 if dtype == torch.float64 else torch.float32
+    return [t.to(dtype).to(up) for t in ts]
+
+
+# ----------------------------------------------------------------------------- golden vectors
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_softmax_golden(tag):
+    g = load_golden(f"softmax_{tag}")
+    out, (dx,) = run(fat().rational_softmax, [g["x"]], g["d_out"])
+    assert norm_max_err(out, g["out"]) < FP32_TOL and norm_max_err(dx, g["dx"]) < FP32_TOL
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_swiglu_golden(tag):
+    g = load_golden(f"swiglu_{tag}")
+    out, (dg, dv) = run(fat().rational_swiglu, [g["gate"], g["value"]], g["d_out"])
+    assert norm_max_err(out, g["out"]) < FP32_TOL
+    assert norm_max_err(dg, g["dgate"]) < FP32_TOL and norm_max_err(dv, g["dvalue"]) < FP32_TOL
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_norm_golden(tag):
+    g = load_golden(f"norm_{tag}")
+    out, (dx, dw) = run(fat().mean_error_norm, [g["x"], g["weight"]], g["d_out"])
+    assert norm_max_err(out, g["out"]) < FP32_TOL
+    assert norm_max_err(dx, g["dx"]) < FP32_TOL and norm_max_err(dw, g["dweight"]) < FP32_TOL
+
+
+# ----------------------------------------------------------------------------- seeded sweeps vs the oracle
+SOFTMAX_SHAPES = [(2, 8, 64, 64), (4, 12, 128, 128), (2, 16, 256, 256),          # the reference's test shapes
+                  (1, 1), (3, 1), (5, 7), (4, 37), (33, 1000), (3, 2048), (2, 4096), (2, 16384), (1, 20000), (2, 40000)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+@pytest.mark.parametrize("shape", SOFTMAX_SHAPES)
+def test_softmax_vs_oracle(shape, dtype):
+    x, go = gen(11, shape, shape, dtype=dtype)
+    x = x * 2
+    out, (dx,) = run(fat().rational_softmax, [x], go)
+    xo, goo = oracle_inputs([x, go], dtype)
+    want, (wdx,) = oracle.autograd_grads(oracle.rational_softmax, [xo], goo)
+    compare(out, want, dtype, "softmax out")
+    compare(dx, wdx, dtype, "softmax dx")
+    if dtype == torch.float32:
+        assert (out.sum(-1) - 1).abs().max().item() < 1e-5
+
+
+SWIGLU_SHAPES = [(2, 512, 768), (4, 1024, 1024), (1, 1), (3, 5), (7, 33), (129, 2048), (2, 3, 1000)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+@pytest.mark.parametrize("shape", SWIGLU_SHAPES)
+def test_swiglu_vs_oracle(shape, dtype):
+    gate, val, go = gen(12, shape, shape, shape, dtype=dtype)
+    out, (dg, dv) = run(fat().rational_swiglu, [gate, val], go)
+    a, b, c = oracle_inputs([gate, val, go], dtype)
+    want, (wdg, wdv) = oracle.autograd_grads(oracle.rational_swiglu, [a, b], c)
+    compare(out, want, dtype, "swiglu out")
+    compare(dg, wdg, dtype, "swiglu dgate")
+    compare(dv, wdv, dtype, "swiglu dvalue")
+
+
+def test_swiglu_reads_packed_halves_in_place():
+    """gate / value as the two halves of one [rows, 2*ffn] projection (the model's layout)."""
+    (gv, go) = gen(13, (4, 96, 2 * 344), (4, 96, 344))
+    gv_d = gv.to(DEV).requires_grad_(True)
+    gate, val = gv_d.chunk(2, dim=-1)
+    out = fat().rational_swiglu(gate, val)
+    out.backward(go.to(DEV))
+    ref = gv.clone().requires_grad_(True)
+    a, b = ref.chunk(2, dim=-1)
+    oracle.rational_swiglu(a, b).backward(go)
+    assert norm_max_err(out, oracle.rational_swiglu(a, b)) < FP32_TOL
+    assert norm_max_err(gv_d.grad, ref.grad) < FP32_TOL
+
+
+NORM_SHAPES = [(2, 512, 768), (4, 1024, 1024), (1, 1), (2, 3), (7, 50), (300, 2048), (64, 4096), (5, 8192), (3, 20000)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+@pytest.mark.parametrize("shape", NORM_SHAPES)
+def test_norm_vs_oracle(shape, dtype):
+    x, go = gen(14, shape, shape, dtype=dtype)
+    (w,) = gen(15, (shape[-1],), dtype=dtype)
+    w = (1 + 0.1 * w.float()).to(dtype)
+    out, (dx, dw) = run(fat().mean_error_norm, [x, w], go)
+    a, b, c = oracle_inputs([x, w, go], dtype)
+    want, (wdx, wdw) = oracle.autograd_grads(oracle.mean_error_norm, [a, b], c)
+    compare(out, want, dtype, "norm out")
+    compare(dx, wdx, dtype, "norm dx")
+    if dtype in (torch.float32, torch.float64):
+        compare(dw, wdw, dtype, "norm dweight")
+    else:   # a column sum over many rows, rounded once to 16 bits at the end
+        assert norm_max_err(dw.float(), wdw) < 1e-2
+
+
+def test_norm_weight_randn_like_reference_test():
+    """tests.py:141-173 draws the weight from randn; thresholds fwd 1e-4, grads 1e-3 (max abs)."""
+    x, go = gen(16, (4, 1024, 1024), (4, 1024, 1024))
+    (w,) = gen(17, (1024,))
+    out, (dx, dw) = run(fat().mean_error_norm, [x, w], go)
+    want, (wdx, wdw) = oracle.autograd_grads(oracle.mean_error_norm, [x, w], go)
+    assert (out.cpu() - want).abs().max() < 1e-4
+    assert (dx.cpu() - wdx).abs().max() < 1e-3 and ((dw.cpu() - wdw).abs().max() / wdw.abs().max()) < 1e-5
+
+
+def test_norm_sign_of_zero_is_zero():
+    x = torch.zeros(2, 64); x[:, ::2] = 1.5
+    go = torch.ones(2, 64)
+    w = torch.full((64,), 2.0)
+    _, (dx, _) = run(fat().mean_error_norm, [x, w], go)
+    _, (wdx, _) = oracle.autograd_grads(oracle.mean_error_norm, [x, w], go)
+    assert norm_max_err(dx, wdx) < FP32_TOL
+
+
+def test_empty_inputs():
+    f = fat()
+    e = torch.empty(0, 16, device=DEV)
+    assert f.rational_softmax(e).shape == (0, 16)
+    assert f.rational_swiglu(e, e).shape == (0, 16)
+    assert f.mean_error_norm(e, torch.ones(16, device=DEV)).shape == (0, 16)
+
+
+def test_gradcheck_float64():
+    """The reference's gradcheck settings (tests.py:219-270): eps 1e-6, atol 1e-4, rtol 1e-3."""
+    f = fat()
+    g = torch.Generator().manual_seed(18)
+    kw = dict(eps=1e-6, atol=1e-4, rtol=1e-3)
+    x = torch.randn(2, 4, 16, 16, generator=g, dtype=torch.float64).to(DEV).requires_grad_(True)
+    assert torch.autograd.gradcheck(lambda t: f.RationalSoftmax.apply(t, 1e-6), (x,), **kw)
+    gate = torch.randn(2, 16, 32, generator=g, dtype=torch.float64).to(DEV).requires_grad_(True)
+    val = torch.randn(2, 16, 32, generator=g, dtype=torch.float64).to(DEV).requires_grad_(True)
+    assert torch.autograd.gradcheck(f.RationalSwiGLU.apply, (gate, val), **kw)
+    x = torch.randn(2, 16, 32, generator=g, dtype=torch.float64).to(DEV).requires_grad_(True)
+    w = torch.randn(32, generator=g, dtype=torch.float64).to(DEV).requires_grad_(True)
+    assert torch.autograd.gradcheck(lambda a, b: f.MeanErrorNorm.apply(a, b, 1e-6), (x, w), **kw)
+
+
+def test_torch_library_ops_have_autograd():
+    x = torch.randn(8, 64, device=DEV, requires_grad=True)
+    y = torch.ops.algebraic.softmax_fwd(x, 1e-6)
+    y.sum().backward()
+    assert x.grad is not None and x.grad.shape == x.shape
+
+
+def test_full_size_properties():
+    """BASELINE sizes, checked through size-independent properties instead of the (slow) oracle."""
+    f = fat()
+    g = torch.Generator(device=DEV).manual_seed(19)
+    x = (torch.randn(4096, 4096, generator=g, device=DEV) * 1.4142).to(torch.bfloat16)
+    p = f.rational_softmax(x)
+    assert (p.float().sum(-1) - 1).abs().max().item() < 2e-2 and (p >= 0).all()
+    xn = torch.randn(16384, 4096, generator=g, device=DEV).to(torch.bfloat16)
+    w = torch.ones(4096, device=DEV, dtype=torch.bfloat16)
+    y = f.mean_error_norm(xn, w)
+    assert (y.float().abs().mean(-1) - 1).abs().max().item() < 1e-2            # rows have unit mean |y|
+    assert torch.equal(f.mean_error_norm(2 * xn, w), y)                          # scale invariance (exact: power of 2)
+    gate = torch.randn(2048, 8192, generator=g, device=DEV).to(torch.bfloat16)
+    val = torch.randn(2048, 8192, generator=g, device=DEV).to(torch.bfloat16)
+    o1 = f.rational_swiglu(gate, val)
+    assert torch.equal(f.rational_swiglu(gate, 2 * val), 2 * o1)                 # linear in value
+    assert torch.equal(f.rational_swiglu(gate, val), o1)                         # deterministic
