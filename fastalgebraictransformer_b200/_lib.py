@@ -36,9 +36,9 @@ PROTOTYPES = {
     "fat_norm_bwd": (_int, [_ptr] * 7 + [_sz] + [_i64] * 5 + [_dbl, _int, _ptr]),
     "fat_softmax_fwd": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),
     "fat_softmax_bwd": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),
-    "fat_attn_fwd": (_int, [_ptr] * 6 + [_int] * 4 + [_p64] * 4 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
+    "fat_attn_fwd": (_int, [_ptr] * 7 + [_int] * 4 + [_p64] * 4 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
     "fat_attn_bwd_workspace_bytes": (_sz, [_int] * 6),
-    "fat_attn_bwd": (_int, [_ptr] * 11 + [_sz] + [_int] * 4 + [_p64] * 8 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
+    "fat_attn_bwd": (_int, [_ptr] * 12 + [_sz] + [_int] * 4 + [_p64] * 8 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
     "fat_attn_select_path": (_int, [_int] * 4),
 }
 

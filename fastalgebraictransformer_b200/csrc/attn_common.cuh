@@ -10,6 +10,7 @@ namespace fat {
 struct AttnParams {
   const void* q; const void* k; const void* v; const float* slopes;
   void* out; float* L;                        // forward outputs / backward inputs
+  void* out_lo;                               // optional rounding residual of out (same strides), may be null
   const void* d_out; void* d_q; void* d_k; void* d_v;
   float* delta;                               // workspace: Delta_i = d_out_i . out_i, [B,H,T]
   float* dq_acc;                              // workspace: float32 d_q accumulator (tensor path)

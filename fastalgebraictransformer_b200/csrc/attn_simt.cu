@@ -111,9 +111,11 @@ __device__ __forceinline__ void gemm_nn(float (&o)[4][DP / 16], const float* __r
   }
 }
 
+// Writes o*mul to `base`; when `lo` is given also writes the rounding residual round(o*mul - stored).
 template <typename T, int DP>
 __device__ __forceinline__ void store_rows(T* __restrict__ base, int64_t row_stride, int row0, int T_len, int D,
-                                           const float (&o)[4][DP / 16], const float (&mul)[4], int ty, int tx) {
+                                           const float (&o)[4][DP / 16], const float (&mul)[4], int ty, int tx,
+                                           T* __restrict__ lo = nullptr) {
   using OC = OutCols<DP>;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -124,7 +126,12 @@ __device__ __forceinline__ void store_rows(T* __restrict__ base, int64_t row_str
 #pragma unroll
       for (int e = 0; e < OC::VW; ++e) {
         const int col = OC::col(tx, c, e);
-        if (col < D) base[int64_t(row) * row_stride + col] = Elem<T>::from_c(o[i][c * OC::VW + e] * mul[i]);
+        if (col < D) {
+          const float val = o[i][c * OC::VW + e] * mul[i];
+          const T hi = Elem<T>::from_c(val);
+          base[int64_t(row) * row_stride + col] = hi;
+          if (lo) lo[int64_t(row) * row_stride + col] = Elem<T>::from_c(val - Elem<T>::to_c(hi));
+        }
       }
   }
 }
@@ -190,7 +197,8 @@ __global__ void __launch_bounds__(NT) attn_fwd_simt_kernel(AttnParams p, bool ve
     const int row = q0 + ty + 16 * i;
     if (tx == 0 && row < p.T) p.L[(int64_t(b) * p.H + h) * p.T + row] = l[i];
   }
-  store_rows<T, DP>(ob, p.os[2], q0, p.T, p.D, o, inv, ty, tx);
+  T* olo = p.out_lo ? static_cast<T*>(p.out_lo) + b * p.os[0] + h * p.os[1] : nullptr;
+  store_rows<T, DP>(ob, p.os[2], q0, p.T, p.D, o, inv, ty, tx, olo);
 }
 
 // ------------------------------------------------------------------ backward, query-major: Delta and d_q
@@ -216,10 +224,12 @@ __global__ void __launch_bounds__(NT) attn_bwd_dq_simt_kernel(AttnParams p, bool
   load_tile<T, DP>(Qs, qb, p.qs[2], q0, p.T, p.D, vec);
   load_tile<T, DP>(dOs, dob, p.dos[2], q0, p.T, p.D, vec);
   load_tile<T, DP>(Ks, ob, p.os[2], q0, p.T, p.D, vec);          // the O tile, parked in the K buffer
+  const bool has_lo = p.out_lo != nullptr;                        // and its rounding residual in the V buffer
+  if (has_lo) load_tile<T, DP>(Vs, static_cast<const T*>(p.out_lo) + b * p.os[0] + h * p.os[1], p.os[2], q0, p.T, p.D, vec);
   __syncthreads();
   for (int r = warp * 8; r < warp * 8 + 8; ++r) {
     float s = 0.f;
-    for (int d = lane; d < DP; d += 32) s = fmaf(dOs[r * LD + d], Ks[r * LD + d], s);
+    for (int d = lane; d < DP; d += 32) s = fmaf(dOs[r * LD + d], has_lo ? Ks[r * LD + d] + Vs[r * LD + d] : Ks[r * LD + d], s);
     s = warp_sum(s);
     if (lane == 0) {
       const int row = q0 + r;

@@ -86,7 +86,7 @@ int fat_attn_select_path(int T, int D, int dtype, int aligned) {
   return attn_tc_eligible(T, D, dtype, aligned != 0) ? FAT_PATH_TENSOR : FAT_PATH_SIMT;
 }
 
-int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slopes, void* out, float* L,
+int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slopes, void* out, void* out_lo, float* L,
                  int B, int H, int T, int D,
                  const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os,
                  double scale, double eps, int causal, int dtype, int path, int* status, void* stream) {
@@ -95,12 +95,12 @@ int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slope
   if (B == 0 || T == 0) return FAT_OK;
   if (!q || !k || !v || !slopes || !out || !L || !qs || !ks || !vs || !os) { set_error("attn_fwd: null pointer"); return FAT_ERR_NULL; }
   const int w = dtype == FAT_F32 ? 4 : 8;
-  const bool aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
+  const bool aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(out_lo) &&
                        strides_aligned(qs, w) && strides_aligned(ks, w) && strides_aligned(vs, w) && strides_aligned(os, w);
   const int sel = resolve_path("attn_fwd", path, T, D, dtype, aligned);
   if (sel < 0) return -sel;
   AttnParams p{};
-  p.q = q; p.k = k; p.v = v; p.slopes = slopes; p.out = out; p.L = L;
+  p.q = q; p.k = k; p.v = v; p.slopes = slopes; p.out = out; p.out_lo = out_lo; p.L = L;
   p.B = B; p.H = H; p.T = T; p.D = D;
   copy3(p.qs, qs); copy3(p.ks, ks); copy3(p.vs, vs); copy3(p.os, os);
   p.scale = float(scale); p.eps = float(eps); p.causal = causal != 0; p.status = status;
@@ -114,7 +114,7 @@ size_t fat_attn_bwd_workspace_bytes(int B, int H, int T, int D, int dtype, int p
   return tc ? attn_bwd_tc_workspace_bytes(B, H, T, D) : delta;
 }
 
-int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, const float* L,
+int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* out_lo, const float* L,
                  const void* d_out, const float* slopes, void* d_q, void* d_k, void* d_v,
                  void* workspace, size_t workspace_bytes, int B, int H, int T, int D,
                  const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, const int64_t* dos,
@@ -126,7 +126,7 @@ int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, c
   if (!q || !k || !v || !out || !L || !d_out || !slopes || !d_q || !d_k || !d_v ||
       !qs || !ks || !vs || !os || !dos || !dqs || !dks || !dvs) { set_error("attn_bwd: null pointer"); return FAT_ERR_NULL; }
   const int w = dtype == FAT_F32 ? 4 : 8;
-  const bool aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(d_out) &&
+  const bool aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(out_lo) && aligned16(d_out) &&
                        aligned16(d_q) && aligned16(d_k) && aligned16(d_v) &&
                        strides_aligned(qs, w) && strides_aligned(ks, w) && strides_aligned(vs, w) && strides_aligned(os, w) &&
                        strides_aligned(dos, w) && strides_aligned(dqs, w) && strides_aligned(dks, w) && strides_aligned(dvs, w);
@@ -138,7 +138,7 @@ int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, c
     return FAT_ERR_WORKSPACE;
   }
   AttnParams p{};
-  p.q = q; p.k = k; p.v = v; p.slopes = slopes; p.out = const_cast<void*>(out); p.L = const_cast<float*>(L);
+  p.q = q; p.k = k; p.v = v; p.slopes = slopes; p.out = const_cast<void*>(out); p.out_lo = const_cast<void*>(out_lo); p.L = const_cast<float*>(L);
   p.d_out = d_out; p.d_q = d_q; p.d_k = d_k; p.d_v = d_v;
   p.delta = static_cast<float*>(workspace);
   p.dq_acc = static_cast<float*>(workspace) + ((size_t(B) * H * T + 3) / 4) * 4;

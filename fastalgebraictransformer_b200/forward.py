@@ -41,5 +41,6 @@ def rational_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     """
     assert q.is_cuda and k.is_cuda and v.is_cuda
     assert q.shape == k.shape == v.shape
-    return torch.ops.algebraic.attn_fwd(q.detach(), k.detach(), v.detach(), alibi_slopes, float(scale), bool(causal),
-                                        float(eps), int(path), False)
+    out, L, _ = torch.ops.algebraic.attn_fwd(q.detach(), k.detach(), v.detach(), alibi_slopes, float(scale),
+                                             bool(causal), float(eps), int(path), False)
+    return out, L

@@ -24,8 +24,8 @@ _libdef.define("norm_bwd(Tensor d_out, Tensor x, Tensor weight, Tensor mean, flo
 _libdef.define("softmax_fwd(Tensor x, float eps) -> Tensor")
 _libdef.define("softmax_bwd(Tensor d_out, Tensor x, float eps) -> Tensor")
 _libdef.define("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor slopes, float scale, bool causal, float eps, "
-               "int path, bool token_major_out) -> (Tensor, Tensor)")
-_libdef.define("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor L, Tensor d_out, Tensor slopes, "
+               "int path, bool token_major_out) -> (Tensor, Tensor, Tensor)")
+_libdef.define("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor out_lo, Tensor L, Tensor d_out, Tensor slopes, "
                "float scale, bool causal, float eps, int path) -> (Tensor, Tensor, Tensor)")
 
 
@@ -176,7 +176,7 @@ def _alloc_bhtd(like: Tensor, token_major: bool) -> Tensor:
 
 
 def _attn_fwd(q: Tensor, k: Tensor, v: Tensor, slopes: Tensor, scale: float, causal: bool, eps: float,
-              path: int, token_major_out: bool) -> Tuple[Tensor, Tensor]:
+              path: int, token_major_out: bool) -> Tuple[Tensor, Tensor, Tensor]:
     _cuda_check(q, k, v, slopes)
     assert q.dim() == 4 and q.shape == k.shape == v.shape and q.dtype == k.dtype == v.dtype
     B, H, T, D = q.shape
@@ -184,22 +184,29 @@ def _attn_fwd(q: Tensor, k: Tensor, v: Tensor, slopes: Tensor, scale: float, cau
     sl = slopes.to(torch.float32).contiguous()
     assert sl.numel() == H, "alibi_slopes must hold one slope per head"
     out = _alloc_bhtd(q, token_major_out)
+    # 16-bit outputs also keep their rounding residual, so the backward can form Delta = dO.O accurately
+    out_lo = _alloc_bhtd(q, token_major_out) if q.element_size() == 2 else q.new_empty(0)
     L = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
     if q.numel():
         with _lib.device_guard(q.device):
             _lib.check(_lib.lib().fat_attn_fwd(
-                _p(q), _p(k), _p(v), _p(sl), _p(out), _p(L), B, H, T, D,
+                _p(q), _p(k), _p(v), _p(sl), _p(out), _p(out_lo) if out_lo.numel() else None, _p(L), B, H, T, D,
                 _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out),
                 scale, eps, int(causal), _lib.dtype_tag(q), path,
                 _p(_lib.device_status(q.device)), _lib.stream_ptr(q.device)))
-    return out, L
+    return out, L, out_lo
 
 
-def _attn_bwd(q: Tensor, k: Tensor, v: Tensor, out: Tensor, L: Tensor, d_out: Tensor, slopes: Tensor,
+def _attn_bwd(q: Tensor, k: Tensor, v: Tensor, out: Tensor, out_lo: Tensor, L: Tensor, d_out: Tensor, slopes: Tensor,
               scale: float, causal: bool, eps: float, path: int) -> Tuple[Tensor, Tensor, Tensor]:
     _cuda_check(q, k, v, out, L, d_out, slopes)
     B, H, T, D = q.shape
     q, k, v, out, d_out = _unit_d(q), _unit_d(k), _unit_d(v), _unit_d(out), _unit_d(d_out)
+    lo_ptr = None
+    if out_lo.numel():
+        if out_lo.stride() != out.stride():       # the kernels address both with one set of strides
+            out, out_lo = out.contiguous(), out_lo.contiguous()
+        lo_ptr = _p(out_lo)
     sl = slopes.to(torch.float32).contiguous()
     Lc = L.contiguous()
     if _is_token_major(q):
@@ -215,7 +222,7 @@ def _attn_bwd(q: Tensor, k: Tensor, v: Tensor, out: Tensor, L: Tensor, d_out: Te
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
         with _lib.device_guard(q.device):
             _lib.check(lib.fat_attn_bwd(
-                _p(q), _p(k), _p(v), _p(out), _p(Lc), _p(d_out), _p(sl), _p(d_q), _p(d_k), _p(d_v),
+                _p(q), _p(k), _p(v), _p(out), lo_ptr, _p(Lc), _p(d_out), _p(sl), _p(d_q), _p(d_k), _p(d_v),
                 _p(ws), ws_bytes, B, H, T, D,
                 _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out), _lib.strides3(d_out),
                 _lib.strides3(d_q), _lib.strides3(d_k), _lib.strides3(d_v),
@@ -266,11 +273,12 @@ def _(d_out, x, eps):
 def _(q, k, v, slopes, scale, causal, eps, path, token_major_out):
     B, H, T, D = q.shape
     out = q.new_empty((B, T, H, D)).permute(0, 2, 1, 3) if token_major_out else q.new_empty((B, H, T, D))
-    return out, q.new_empty((B, H, T), dtype=torch.float32)
+    lo = torch.empty_like(out) if q.element_size() == 2 else q.new_empty(0)
+    return out, q.new_empty((B, H, T), dtype=torch.float32), lo
 
 
 @torch.library.register_fake(f"{_NS}::attn_bwd")
-def _(q, k, v, out, L, d_out, slopes, scale, causal, eps, path):
+def _(q, k, v, out, out_lo, L, d_out, slopes, scale, causal, eps, path):
     return tuple(q.new_empty(q.shape) for _ in range(3))
 
 
@@ -308,13 +316,13 @@ def _softmax_backward(ctx, d_out):
 
 def _attn_setup(ctx, inputs, output):
     q, k, v, slopes, scale, causal, eps, path, _ = inputs
-    ctx.save_for_backward(q, k, v, output[0], output[1], slopes)
+    ctx.save_for_backward(q, k, v, output[0], output[1], output[2], slopes)
     ctx.args = (scale, causal, eps, path)
 
 
-def _attn_backward(ctx, d_out, d_L):
-    q, k, v, out, L, slopes = ctx.saved_tensors
-    d_q, d_k, d_v = torch.ops.algebraic.attn_bwd(q, k, v, out, L, d_out, slopes, *ctx.args)
+def _attn_backward(ctx, d_out, d_L, d_lo):
+    q, k, v, out, L, out_lo, slopes = ctx.saved_tensors
+    d_q, d_k, d_v = torch.ops.algebraic.attn_bwd(q, k, v, out, out_lo, L, d_out, slopes, *ctx.args)
     return d_q, d_k, d_v, None, None, None, None, None, None
 
 

@@ -128,11 +128,15 @@ FAT_API int fat_softmax_bwd(const void* d_out, const void* x, void* d_x,
  * q, k, v, out are [B,H,T,D] with unit stride along D; *_strides point to three element
  * strides {batch, head, token}, so views of a packed [B,T,3,H,D] projection are consumed
  * in place.  slopes is float32 [H].  status may be null.
+ * out_lo (optional, may be null; same dtype and strides as out) receives the rounding residual
+ * of the output, out_lo = round(O - out): with 16-bit tensors out + out_lo carries O to ~16
+ * significant bits, which the backward needs for Delta_i = d_out_i . O_i to stay inside the
+ * 16-bit tolerance.  The reference has no such tensor (it keeps only the rounded output).
  * Replaces rational_attention_forward / rational_attention_fwd_kernel (forward.py:49-159, 267-319).
  * dtypes: F32, BF16, F16.  D <= 128.
  * ---------------------------------------------------------------------------------- */
 FAT_API int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slopes,
-                 void* out, float* L,
+                 void* out, void* out_lo, float* L,
                  int B, int H, int T, int D,
                  const int64_t* q_strides, const int64_t* k_strides,
                  const int64_t* v_strides, const int64_t* out_strides,
@@ -143,13 +147,14 @@ FAT_API int fat_attn_fwd(const void* q, const void* k, const void* v, const floa
  *     Delta_i = d_out_i . out_i,   dP_ij = d_out_i . v_j,   r = 1/(|s|+1),
  *     dS_ij = 2 sigma^3 r^2 (dP_ij - Delta_i) / (L_i + eps),
  *     d_q = scale dS k,  d_k = scale dS^T q,  d_v = P^T d_out.
+ * out_lo is the optional residual written by the forward (null: Delta uses the rounded out).
  * The workspace holds Delta (and, for the tensor-core path, a float32 d_q accumulator).
  * Replaces rational_attention_backward / rational_attention_bwd_dq_kernel /
  * rational_attention_bwd_dkv_kernel (backward.py:62-158, 165-266, 273-341).
  * ---------------------------------------------------------------------------------- */
 FAT_API size_t fat_attn_bwd_workspace_bytes(int B, int H, int T, int D, int dtype, int path);
 
-FAT_API int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, const float* L,
+FAT_API int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* out_lo, const float* L,
                  const void* d_out, const float* slopes,
                  void* d_q, void* d_k, void* d_v,
                  void* workspace, size_t workspace_bytes,

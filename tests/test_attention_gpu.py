@@ -55,7 +55,11 @@ def test_fp32_vs_oracle(shape):
     out, dq, dk, dv = run_attention(q, k, v, go, slopes, scale, path=1)
     want = oracle.rational_attention_grads(q, k, v, go, slopes, scale)
     for got, w, name in zip((out, dq, dk, dv), want, ("out", "dq", "dk", "dv")):
-        assert norm_max_err(got, w) < FP32_TOL, f"{name}: {norm_max_err(got, w):.2e}"
+        if T == 1 and name in ("dq", "dk"):
+            # a single key: dS = k (dP - Delta) / (L+eps) is ~eps, the difference of two equal numbers
+            assert (got.cpu() - w).abs().max() < 1e-5
+        else:
+            assert norm_max_err(got, w) < FP32_TOL, f"{name}: {norm_max_err(got, w):.2e}"
 
 
 def test_config1_fp32_closed_form_slopes():
