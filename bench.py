@@ -165,7 +165,7 @@ def bench_attn(args, rank, world, device):
     slopes = slopes.to(device)
     scale = 1.0 / math.sqrt(cfg["D"])
     fwd_flops, bwd_flops = attn_flops(**cfg)
-    path = _lib.lib().fat_attn_select_path(cfg["S"], cfg["D"], _lib.BF16, 1)
+    path = _lib.lib().fat_attn_select_path(cfg["S"], cfg["D"], _lib.BF16, 1, 1, 1)
 
     state = {}
 

@@ -39,7 +39,7 @@ PROTOTYPES = {
     "fat_attn_fwd": (_int, [_ptr] * 7 + [_int] * 4 + [_p64] * 4 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
     "fat_attn_bwd_workspace_bytes": (_sz, [_int] * 6),
     "fat_attn_bwd": (_int, [_ptr] * 12 + [_sz] + [_int] * 4 + [_p64] * 8 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
-    "fat_attn_select_path": (_int, [_int] * 4),
+    "fat_attn_select_path": (_int, [_int] * 6),
 }
 
 

@@ -1,0 +1,319 @@
+// Causal rational attention forward on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
+//
+// One CTA owns 256 consecutive queries of one (batch, head): two 128-row query tiles, each
+// served by one "softmax" warpgroup (one thread per query row).  A producer warp streams
+// 128-key K and V tiles through a two-stage shared-memory ring with TMA; an issuer warp
+// drives the tensor core:   S_t = Q_t K^T  (smem x smem -> TMEM, fp32)
+//                           O_t += P_t V   (TMEM x smem -> TMEM, fp32)
+// Because sigma(s)^4 lies in [0,1] there is no running maximum and nothing to rescale: the
+// output accumulates in TMEM across all key tiles untouched by the CUDA cores, which only
+// turn S into P = sigma(S*scale + alibi)^4 in place (16-bit, packed over the fp32 scores)
+// and keep a running row sum.  The two query tiles ping-pong, so the tensor core works on
+// one while the other is in its element-wise phase.
+//
+// TMEM columns: S0/P0 [0,128)  S1/P1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "attn_common.cuh"
+#include "tc_common.cuh"
+
+namespace fat {
+namespace {
+
+using namespace tc;
+
+constexpr int BLK = 128;                 // rows per query tile and keys per key tile
+constexpr int kStages = 2;
+constexpr int kFwdThreads = 320;         // warps 0-3: tile 0, warps 4-7: tile 1, warp 8: TMA, warp 9: MMA
+constexpr uint32_t kTmemCols = 512;
+
+template <int D>
+struct FwdSmem {
+  static constexpr int kTileBytes = BLK * D * 2;          // one [128][D] 16-bit tile
+  alignas(1024) unsigned char q[2][kTileBytes];           // reused as output staging in the epilogue
+  alignas(1024) unsigned char k[kStages][kTileBytes];
+  alignas(1024) unsigned char v[kStages][kTileBytes];
+  uint64_t q_full[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+  uint64_t s_full[2], p_full[2], o_full[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename T> struct Pack16;
+template <> struct Pack16<__nv_bfloat16> {
+  static constexpr int kFmt = 1;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  }
+};
+template <> struct Pack16<__half> {
+  static constexpr int kFmt = 0;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+};
+
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// sigma(s)^4 with sigma(s) = (s/(|s|+1) + 1)/2
+__device__ __forceinline__ float sigma4(float s) {
+  const float sg = fmaf(s * rcp_approx(fabsf(s) + 1.0f), 0.5f, 0.5f);
+  const float s2 = sg * sg;
+  return s2 * s2;
+}
+
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Loads one [128][D] tile (rows row0.., all of D) as D/64 boxes of 64 columns.
+template <int D>
+__device__ __forceinline__ void load_tile_tma(unsigned char* dst, const CUtensorMap* m, uint64_t* bar,
+                                              int row0, int h, int b) {
+  mbar_expect_tx(bar, BLK * D * 2);
+#pragma unroll
+  for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + c * (BLK * 128), m, bar, c * 64, row0, h, b);
+}
+
+struct FwdMaps { CUtensorMap q, k, v, out, out_lo; };
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  using S = FwdSmem<D>;
+  S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qb = gridDim.x - 1 - blockIdx.x;                 // long query blocks first
+  const int n_kv_total = (p.T + BLK - 1) / BLK;
+  // query tile t covers rows [(2qb+t)*128, +128); it needs key tiles 0..(2qb+t) (causal)
+  int n_tiles[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) n_tiles[t] = (2 * qb + t) * BLK < p.T ? min(2 * qb + t + 1, n_kv_total) : 0;
+  const int n_max = max(n_tiles[0], n_tiles[1]);
+  Guard g{&sm.abort_flag, p.status};
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.q_full[i], 1); mbar_init(&sm.s_full[i], 1); mbar_init(&sm.p_full[i], BLK); mbar_init(&sm.o_full[i], 1);
+    }
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 8) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&maps.q); tma_prefetch_desc(&maps.k); tma_prefetch_desc(&maps.v);
+      for (int t = 0; t < 2; ++t)
+        if (n_tiles[t] > 0) load_tile_tma<D>(sm.q[t], &maps.q, &sm.q_full[t], (2 * qb + t) * BLK, h, b);
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        if (!g.wait(&sm.k_empty[st], ph ^ 1, 10)) break;
+        load_tile_tma<D>(sm.k[st], &maps.k, &sm.k_full[st], j * BLK, h, b);
+        if (!g.wait(&sm.v_empty[st], ph ^ 1, 11)) break;
+        load_tile_tma<D>(sm.v[st], &maps.v, &sm.v_full[st], j * BLK, h, b);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ tensor-core issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_qk = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
+      constexpr uint32_t idesc_pv = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
+      auto issue_qk = [&](int t, int st) {            // S_t = Q_t K^T
+        const uint32_t qa = smem_u32(sm.q[t]), ka = smem_u32(sm.k[st]);
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s) {
+          const uint32_t off = (s / 4) * (BLK * 128) + (s % 4) * 32;
+          mma_ss(tmem + t * BLK, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), idesc_qk, s > 0);
+        }
+      };
+      auto issue_pv = [&](int t, int st, bool first) { // O_t += P_t V
+        const uint32_t va = smem_u32(sm.v[st]);
+#pragma unroll
+        for (int s = 0; s < BLK / 16; ++s)
+          mma_ts(tmem + 2 * BLK + t * D, tmem + t * BLK + s * 8, smem_desc_sw128(va + s * 2048, BLK * 128, 1024), idesc_pv,
+                 !(first && s == 0));
+      };
+      bool ok = true;
+      // prologue: scores of key tile 0 for both query tiles
+      if (n_max > 0) ok = g.wait(&sm.k_full[0], 0, 20);
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (n_tiles[t] == 0) continue;
+        ok = g.wait(&sm.q_full[t], 0, 21);
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(t, 0);
+        mma_commit(&sm.s_full[t]);
+      }
+      if (ok && n_max > 0) mma_commit(&sm.k_empty[0]);
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j % kStages, st1 = (j + 1) % kStages;
+        const uint32_t ph = (j / kStages) & 1, ph1 = ((j + 1) / kStages) & 1;
+        bool k_next_ready = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= n_tiles[t]) continue;
+          if (!(ok = g.wait(&sm.p_full[t], j & 1, 22))) break;
+          if (!(ok = g.wait(&sm.v_full[st], ph, 23))) break;
+          tc_fence_after();
+          issue_pv(t, st, j == 0);
+          if (j + 1 < n_tiles[t]) {
+            if (!k_next_ready) { if (!(ok = g.wait(&sm.k_full[st1], ph1, 24))) break; k_next_ready = true; tc_fence_after(); }
+            issue_qk(t, st1);
+            mma_commit(&sm.s_full[t]);
+          } else {
+            mma_commit(&sm.o_full[t]);
+          }
+        }
+        if (!ok) break;
+        mma_commit(&sm.v_empty[st]);                       // V(j) and, if it was read, K(j+1) are free once these finish
+        if (j + 1 < n_max) mma_commit(&sm.k_empty[st1]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    const int t = warp >> 2;                                 // query tile of this warpgroup
+    const int r = tid & (BLK - 1);                           // row inside the tile == TMEM lane
+    const int row = (2 * qb + t) * BLK + r;                  // query index
+    const uint32_t lane_base = uint32_t(warp & 3) * 32;
+    const float slope = p.slopes[h];
+    const float scale = p.scale;
+    const int n = n_tiles[t];
+    float l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      if (!(ok = g.wait(&sm.s_full[t], j & 1, 30))) break;
+      tc_fence_after();
+      const int k0 = j * BLK;
+      const float base = slope * float(k0 - row);            // bias of column 0 of this tile: -slope*(row-k0)
+      const bool diag = (j == 2 * qb + t);
+#pragma unroll
+      for (int c = 0; c < BLK / 32; ++c) {
+        uint32_t sreg[32], preg[16];
+        tmem_ld32(tmem_addr(tmem, lane_base, t * BLK + c * 32), sreg);
+        tmem_wait_ld();
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c * 32 + i;
+          const float s = fmaf(__uint_as_float(sreg[i]), scale, fmaf(slope, float(col), base));
+          f[i] = sigma4(s);
+        }
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (c * 32 + i > r) f[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) l_sum += f[i];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) preg[i] = Pack16<T>::pack(f[2 * i], f[2 * i + 1]);
+        tmem_st16(tmem_addr(tmem, lane_base, t * BLK + c * 16), preg);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.p_full[t]);
+    }
+    if (ok && n > 0) ok = g.wait(&sm.o_full[t], 0, 31);
+    named_barrier(1 + t, BLK);                               // reached by all 128 threads, aborted or not
+    if (n > 0 && !g.aborted()) {
+      // -------------------------------------------------------------- epilogue: O / (L + eps), hi + residual
+      tc_fence_after();
+      const float inv = 1.0f / (l_sum + p.eps);
+      if (row < p.T) p.L[(int64_t(b) * p.H + h) * p.T + row] = l_sum;
+      unsigned char* stage = sm.q[t];
+      const bool want_lo = p.out_lo != nullptr;
+      for (int pass = 0; pass < (want_lo ? 2 : 1); ++pass) {
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t oreg[32];
+          tmem_ld32(tmem_addr(tmem, lane_base, 2 * BLK + t * D + c * 32), oreg);
+          tmem_wait_ld();
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float a = __uint_as_float(oreg[2 * i]) * inv, bb = __uint_as_float(oreg[2 * i + 1]) * inv;
+            uint32_t hi = Pack16<T>::pack(a, bb);
+            if (pass == 1) { const float2 hf = Pack16<T>::unpack(hi); hi = Pack16<T>::pack(a - hf.x, bb - hf.y); }
+            w[i] = hi;
+          }
+#pragma unroll
+          for (int sgm = 0; sgm < 4; ++sgm) {
+            const int col = c * 32 + sgm * 8;                 // first column of this 16-byte segment
+            *reinterpret_cast<uint4*>(stage + (col / 64) * (BLK * 128) + sw128_offset(r, (col % 64) / 8)) =
+                make_uint4(w[4 * sgm], w[4 * sgm + 1], w[4 * sgm + 2], w[4 * sgm + 3]);
+          }
+        }
+        fence_async_smem();
+        named_barrier(1 + t, BLK);
+        if (r == 0) {
+          const CUtensorMap* m = pass == 0 ? &maps.out : &maps.out_lo;
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) tma_store_4d(m, stage + c * (BLK * 128), c * 64, (2 * qb + t) * BLK, h, b);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        named_barrier(1 + t, BLK);
+      }
+      if (r == 0) tma_store_wait_all();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <typename T, int D>
+int launch_fwd(const AttnParams& p, cudaStream_t st) {
+  FwdMaps maps;
+  if (!make_tmap_bhtd(&maps.q, p.q, p.B, p.H, p.T, D, p.qs, 64, BLK) ||
+      !make_tmap_bhtd(&maps.k, p.k, p.B, p.H, p.T, D, p.ks, 64, BLK) ||
+      !make_tmap_bhtd(&maps.v, p.v, p.B, p.H, p.T, D, p.vs, 64, BLK) ||
+      !make_tmap_bhtd(&maps.out, p.out, p.B, p.H, p.T, D, p.os, 64, BLK))
+    return FAT_ERR_LAUNCH;
+  if (p.out_lo) {
+    if (!make_tmap_bhtd(&maps.out_lo, p.out_lo, p.B, p.H, p.T, D, p.os, 64, BLK)) return FAT_ERR_LAUNCH;
+  } else {
+    maps.out_lo = maps.out;
+  }
+  auto kern = attn_fwd_tc_kernel<T, D>;
+  const size_t smem = sizeof(FwdSmem<D>) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  if (e != cudaSuccess) { set_error("attn_fwd_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return FAT_ERR_LAUNCH; }
+  dim3 grid((p.T + 2 * BLK - 1) / (2 * BLK), p.H, p.B);
+  kern<<<grid, kFwdThreads, smem, st>>>(maps, p);
+  return check_launch("attn_fwd_tc");
+}
+
+}  // namespace
+
+int attn_fwd_tc(const AttnParams& p, int dtype, cudaStream_t st) {
+  if (dtype == FAT_BF16) return p.D == 128 ? launch_fwd<__nv_bfloat16, 128>(p, st) : launch_fwd<__nv_bfloat16, 64>(p, st);
+  if (dtype == FAT_F16) return p.D == 128 ? launch_fwd<__half, 128>(p, st) : launch_fwd<__half, 64>(p, st);
+  set_error("attn_fwd_tc: unsupported dtype tag %d", dtype);
+  return FAT_ERR_DTYPE;
+}
+
+}  // namespace fat

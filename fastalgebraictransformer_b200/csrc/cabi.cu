@@ -42,13 +42,13 @@ int check_attn_shape(const char* what, int B, int H, int T, int D) {
 void copy3(int64_t (&dst)[3], const int64_t* src) { dst[0] = src[0]; dst[1] = src[1]; dst[2] = src[2]; }
 
 // Resolves the kernel family.  Returns FAT_PATH_SIMT / FAT_PATH_TENSOR, or a negative status.
-int resolve_path(const char* what, int path, int T, int D, int dtype, bool aligned) {
-  const bool ok = attn_tc_eligible(T, D, dtype, aligned);
+int resolve_path(const char* what, int path, int T, int D, int dtype, bool aligned, bool causal, bool backward) {
+  const bool ok = attn_tc_eligible(T, D, dtype, aligned, causal, backward);
   if (path == FAT_PATH_SIMT) return FAT_PATH_SIMT;
   if (path == FAT_PATH_TENSOR) {
     if (!ok) {
-      set_error("%s: the tensor-core path needs bf16/f16, D in {64,128}, 16-byte aligned pointers and strides "
-                "(got dtype %d, D=%d, aligned=%d)", what, dtype, D, int(aligned));
+      set_error("%s: the tensor-core path needs bf16/f16, D in {64,128}, causal masking, 16-byte aligned pointers and "
+                "strides (got dtype %d, D=%d, causal=%d, aligned=%d)", what, dtype, D, int(causal), int(aligned));
       return aligned ? -FAT_ERR_UNSUPPORTED : -FAT_ERR_ALIGNMENT;
     }
     return FAT_PATH_TENSOR;
@@ -82,8 +82,8 @@ const char* fat_error_string(int code) {
   }
 }
 
-int fat_attn_select_path(int T, int D, int dtype, int aligned) {
-  return attn_tc_eligible(T, D, dtype, aligned != 0) ? FAT_PATH_TENSOR : FAT_PATH_SIMT;
+int fat_attn_select_path(int T, int D, int dtype, int aligned, int causal, int backward) {
+  return attn_tc_eligible(T, D, dtype, aligned != 0, causal != 0, backward != 0) ? FAT_PATH_TENSOR : FAT_PATH_SIMT;
 }
 
 int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slopes, void* out, void* out_lo, float* L,
@@ -97,7 +97,7 @@ int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slope
   const int w = dtype == FAT_F32 ? 4 : 8;
   const bool aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(out_lo) &&
                        strides_aligned(qs, w) && strides_aligned(ks, w) && strides_aligned(vs, w) && strides_aligned(os, w);
-  const int sel = resolve_path("attn_fwd", path, T, D, dtype, aligned);
+  const int sel = resolve_path("attn_fwd", path, T, D, dtype, aligned, causal != 0, false);
   if (sel < 0) return -sel;
   AttnParams p{};
   p.q = q; p.k = k; p.v = v; p.slopes = slopes; p.out = out; p.out_lo = out_lo; p.L = L;
@@ -110,7 +110,7 @@ int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slope
 size_t fat_attn_bwd_workspace_bytes(int B, int H, int T, int D, int dtype, int path) {
   if (B <= 0 || H <= 0 || T <= 0 || D <= 0) return 0;
   const size_t delta = size_t(B) * H * T * sizeof(float);
-  const bool tc = path != FAT_PATH_SIMT && attn_tc_eligible(T, D, dtype, true);
+  const bool tc = path != FAT_PATH_SIMT && attn_tc_eligible(T, D, dtype, true, true, true);
   return tc ? attn_bwd_tc_workspace_bytes(B, H, T, D) : delta;
 }
 
@@ -130,7 +130,7 @@ int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, c
                        aligned16(d_q) && aligned16(d_k) && aligned16(d_v) &&
                        strides_aligned(qs, w) && strides_aligned(ks, w) && strides_aligned(vs, w) && strides_aligned(os, w) &&
                        strides_aligned(dos, w) && strides_aligned(dqs, w) && strides_aligned(dks, w) && strides_aligned(dvs, w);
-  const int sel = resolve_path("attn_bwd", path, T, D, dtype, aligned);
+  const int sel = resolve_path("attn_bwd", path, T, D, dtype, aligned, causal != 0, true);
   if (sel < 0) return -sel;
   const size_t need = sel == FAT_PATH_TENSOR ? attn_bwd_tc_workspace_bytes(B, H, T, D) : size_t(B) * H * T * sizeof(float);
   if (!workspace || workspace_bytes < need || !aligned16(workspace)) {

@@ -166,8 +166,9 @@ FAT_API int fat_attn_bwd(const void* q, const void* k, const void* v, const void
                  int* status, void* stream);
 
 /* Which kernel family FAT_PATH_AUTO would pick for these arguments (FAT_PATH_SIMT or
- * FAT_PATH_TENSOR).  Host-only, no launch. */
-FAT_API int fat_attn_select_path(int T, int D, int dtype, int aligned16);
+ * FAT_PATH_TENSOR), for the forward (backward = 0) or the backward (backward = 1) launch.
+ * Host-only, no launch. */
+FAT_API int fat_attn_select_path(int T, int D, int dtype, int aligned16, int causal, int backward);
 
 #ifdef __cplusplus
 }
