@@ -1,0 +1,585 @@
+// Causal rational attention backward on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
+//
+// Three launches, no atomics, bit-reproducible:
+//   1. prepare:  per query row  inv = 1/(L+eps) and Delta = dO . O  (two padded float32 arrays)
+//   2. d_q kernel, query-major (one 128-query tile per CTA, key tiles streamed):
+//                S = Q K^T, dP = dO V^T -> dS = g inv (dP - Delta) (16-bit, packed into TMEM over dP)
+//                -> dQ += dS K                      with F = sigma^4, g = 2 sigma^3 r^2
+//   3. d_k/d_v kernel, key-major (one 128-key tile per CTA, query tiles streamed), transposed:
+//                S^T = K Q^T, dP^T = V dO^T -> P^T = F inv, dS^T (TMEM) -> dV += P^T dO, dK += dS^T Q
+// In both main kernels the element-wise work is split in two phases so that the tensor core
+// never waits for it: phase A needs only the scores (sigma, F, g), phase B only dP'.
+// Eight element-wise warps share a tile: warpgroup w owns score columns [64w, 64w+64).
+#include "attn_tc_common.cuh"
+
+namespace fat {
+namespace {
+
+using namespace tc;
+using namespace tcattn;
+
+// The element-wise results that feed the tensor core from TMEM (P^T, dS, dS^T) carry the tensor
+// dtype: tcgen05.mma kind::f16 wants both operands in one format (an f16 A with a bf16 B is an
+// illegal instruction on this hardware).  Power-of-two pre-scales keep small values out of the
+// fp16 subnormals; they are undone exactly in the epilogue multipliers.
+constexpr float kPScale = 1024.0f;       // p = sigma^4/(L+eps) in [0,1]
+constexpr float kDsScale = 256.0f;       // |dS| stays far below 65504/256
+
+constexpr int kBwdThreads = 320;         // warps 0-7: element-wise (2 warpgroups), warp 8: TMA, warp 9: MMA
+constexpr int kBwdStages = 2;
+
+__host__ __device__ inline int64_t pad_rows(int T) { return int64_t((T + BLK - 1) / BLK) * BLK; }
+
+// ------------------------------------------------------------------------------------- 1. prepare
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out) {
+  constexpr int LPR = D / 8;                      // lanes per row, 16 bytes each
+  constexpr int RPW = 32 / LPR;                   // rows per warp
+  const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
+  const int64_t Tp = pad_rows(p.T);
+  const int64_t n_rows = int64_t(p.B) * p.H * Tp;
+  const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+  const T* ob = static_cast<const T*>(p.out);
+  const T* lob = static_cast<const T*>(p.out_lo);
+  const T* dob = static_cast<const T*>(p.d_out);
+  for (int64_t r0 = warp_global * RPW; r0 < n_rows; r0 += n_warps * RPW) {
+    const int64_t row = r0 + sub;
+    const int64_t bh = row / Tp;
+    const int t = int(row - bh * Tp);
+    const int b = int(bh / p.H), h = int(bh % p.H);
+    const bool live = row < n_rows && t < p.T;
+    float g[8] = {}, o[8] = {};
+    if (live) {
+      load_pack_cached<T, 8>(dob + b * p.dos[0] + h * p.dos[1] + int64_t(t) * p.dos[2] + l * 8, g);
+      load_pack_cached<T, 8>(ob + b * p.os[0] + h * p.os[1] + int64_t(t) * p.os[2] + l * 8, o);
+      if (lob) {
+        float lo[8];
+        load_pack_cached<T, 8>(lob + b * p.os[0] + h * p.os[1] + int64_t(t) * p.os[2] + l * 8, lo);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += lo[i];
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dot = fmaf(g[i], o[i], dot);
+#pragma unroll
+    for (int m = LPR / 2; m > 0; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
+    if (row < n_rows) {
+      const float inv = live ? 1.0f / (p.L[(int64_t(b) * p.H + h) * p.T + t] + p.eps) : 0.f;
+      if (l == 0) { p.delta[row] = dot; inv_out[row] = inv; }           // rows in the padding get 0
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------- element-wise math
+// For a raw score accumulator `acc`: s = acc*scale + bias, r = 1/(|s|+1), sigma = (s r + 1)/2.
+// Returns F = sigma^4 and g = sigma^3 r^2 (the factor 2 of the derivative is applied in the epilogues).
+__device__ __forceinline__ void score_fg(float acc, float scale, float bias, float& F, float& g) {
+  const float s = fmaf(acc, scale, bias);
+  const float r = rcp_approx(fabsf(s) + 1.0f);
+  const float sg = fmaf(s * r, 0.5f, 0.5f);
+  const float s2 = sg * sg;
+  F = s2 * s2;
+  g = (s2 * sg) * (r * r);
+}
+
+// TMEM column (relative to the start of a 128-column region) where warpgroup w keeps its packed
+// 16-bit results: elements [64w, 64w+64) live in columns [64w, 64w+32), inside the fp32 columns
+// that only this warpgroup reads.
+__device__ __forceinline__ uint32_t packed_col(int w, int chunk16) { return uint32_t(64 * w + 16 * chunk16); }
+// TMEM column of the A operand of K-step s (16 elements = 8 packed columns) for such a region.
+__device__ __forceinline__ uint32_t packed_kstep_col(int s) { return uint32_t((s / 4) * 64 + (s % 4) * 8); }
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// Tile load that adds its bytes to a barrier whose expect_tx was posted separately.
+template <int D>
+__device__ __forceinline__ void load_tile_tma_noexpect(unsigned char* dst, const CUtensorMap* m, uint64_t* bar,
+                                                       int row0, int h, int b) {
+#pragma unroll
+  for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + c * (BLK * 128), m, bar, c * 64, row0, h, b);
+}
+
+// Converts one thread's 32 fp32 values to 16-bit pairs and stores them into its row of a
+// 128-byte-swizzled [128][D] staging tile, columns [col0, col0+32).
+template <typename T>
+__device__ __forceinline__ void stage_row32(unsigned char* stage, int r, int col0, const uint32_t (&v)[32], float mul) {
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = Pack16<T>::pack(__uint_as_float(v[2 * i]) * mul, __uint_as_float(v[2 * i + 1]) * mul);
+#pragma unroll
+  for (int sgm = 0; sgm < 4; ++sgm) {
+    const int col = col0 + sgm * 8;
+    *reinterpret_cast<uint4*>(stage + (col / 64) * (BLK * 128) + sw128_offset(r, (col % 64) / 8)) =
+        make_uint4(w[4 * sgm], w[4 * sgm + 1], w[4 * sgm + 2], w[4 * sgm + 3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------- 2. d_q kernel
+template <int D>
+struct DqSmem {
+  static constexpr int kTileBytes = BLK * D * 2;
+  alignas(1024) unsigned char q[kTileBytes];               // reused as d_q staging in the epilogue
+  alignas(1024) unsigned char dout[kTileBytes];
+  alignas(1024) unsigned char k[kBwdStages][kTileBytes];
+  alignas(1024) unsigned char v[kBwdStages][kTileBytes];
+  uint64_t qdo_full, k_full[kBwdStages], k_empty[kBwdStages], v_full[kBwdStages], v_empty[kBwdStages];
+  uint64_t s_full, s_free, dp_full, ds_full, dq_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct DqMaps { CUtensorMap q, dout, k, v, dq; };
+
+// TMEM columns: S [0,128)   dP' / packed dS [128,256)   dQ [256,256+D)
+template <typename T, int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  using S = DqSmem<D>;
+  S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qt = gridDim.x - 1 - blockIdx.x;                 // long rows first
+  const int n = qt + 1;                                      // key tiles 0..qt (causal)
+  Guard g{&sm.abort_flag, p.status};
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.qdo_full, 1); mbar_init(&sm.s_full, 1); mbar_init(&sm.s_free, 256);
+    mbar_init(&sm.dp_full, 1); mbar_init(&sm.ds_full, 256); mbar_init(&sm.dq_full, 1);
+    for (int i = 0; i < kBwdStages; ++i) {
+      mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 8) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tS = tmem, tP = tmem + BLK, tQ = tmem + 2 * BLK;
+
+  if (warp == 8) {
+    if (elect_one()) {
+      mbar_expect_tx(&sm.qdo_full, 2 * S::kTileBytes);
+      load_tile_tma_noexpect<D>(sm.q, &maps.q, &sm.qdo_full, qt * BLK, h, b);
+      load_tile_tma_noexpect<D>(sm.dout, &maps.dout, &sm.qdo_full, qt * BLK, h, b);
+      for (int j = 0; j < n; ++j) {
+        const int st = j % kBwdStages;
+        const uint32_t ph = (j / kBwdStages) & 1;
+        if (!g.wait(&sm.k_empty[st], ph ^ 1, 40)) break;
+        load_tile_tma<D>(sm.k[st], &maps.k, &sm.k_full[st], j * BLK, h, b);
+        if (!g.wait(&sm.v_empty[st], ph ^ 1, 41)) break;
+        load_tile_tma<D>(sm.v[st], &maps.v, &sm.v_full[st], j * BLK, h, b);
+      }
+    }
+  } else if (warp == 9) {
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
+      constexpr uint32_t idesc_dq = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
+      auto issue_nt = [&](uint32_t d_tmem, const unsigned char* a, const unsigned char* bm) {   // D = A B^T over head dim
+        const uint32_t aa = smem_u32(a), ba = smem_u32(bm);
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s) {
+          const uint32_t off = (s / 4) * (BLK * 128) + (s % 4) * 32;
+          mma_ss(d_tmem, smem_desc_sw128(aa + off, 16, 1024), smem_desc_sw128(ba + off, 16, 1024), idesc_s, s > 0);
+        }
+      };
+      bool ok = g.wait(&sm.qdo_full, 0, 50) && g.wait(&sm.k_full[0], 0, 51);
+      if (ok) { tc_fence_after(); issue_nt(tS, sm.q, sm.k[0]); mma_commit(&sm.s_full); }
+      ok = ok && g.wait(&sm.v_full[0], 0, 52);
+      if (ok) { tc_fence_after(); issue_nt(tP, sm.dout, sm.v[0]); mma_commit(&sm.dp_full); mma_commit(&sm.v_empty[0]); }
+      for (int j = 0; j < n && ok; ++j) {
+        const int st = j % kBwdStages, st1 = (j + 1) % kBwdStages;
+        const uint32_t ph1 = ((j + 1) / kBwdStages) & 1;
+        if (j + 1 < n) {
+          if (!(ok = g.wait(&sm.s_free, j & 1, 53))) break;
+          if (!(ok = g.wait(&sm.k_full[st1], ph1, 54))) break;
+          tc_fence_after();
+          issue_nt(tS, sm.q, sm.k[st1]);
+          mma_commit(&sm.s_full);
+        }
+        if (!(ok = g.wait(&sm.ds_full, j & 1, 55))) break;
+        tc_fence_after();
+        {
+          const uint32_t ka = smem_u32(sm.k[st]);
+#pragma unroll
+          for (int s = 0; s < BLK / 16; ++s)
+            mma_ts(tQ, tP + packed_kstep_col(s), smem_desc_sw128(ka + s * 2048, BLK * 128, 1024), idesc_dq, !(j == 0 && s == 0));
+        }
+        mma_commit(&sm.k_empty[st]);
+        if (j + 1 < n) {
+          if (!(ok = g.wait(&sm.v_full[st1], ph1, 56))) break;
+          tc_fence_after();
+          issue_nt(tP, sm.dout, sm.v[st1]);
+          mma_commit(&sm.dp_full);
+          mma_commit(&sm.v_empty[st1]);
+        }
+      }
+      if (ok) mma_commit(&sm.dq_full);
+    }
+  } else {
+    const int w = warp >> 2;                                 // column half of this warpgroup
+    const int r = tid & (BLK - 1);                           // query row inside the tile == TMEM lane
+    const int row = qt * BLK + r;
+    const uint32_t lane_base = uint32_t(warp & 3) * 32;
+    const float slope = p.slopes[h], scale = p.scale;
+    const int64_t srow = (int64_t(b) * p.H + h) * pad_rows(p.T) + row;
+    const float dlt = p.delta[srow];                                               // Delta of this query
+    const float ginv = p.delta[int64_t(p.B) * p.H * pad_rows(p.T) + srow] * kDsScale;   // 1/(L+eps), pre-scaled
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      float gq[64];
+      // ---- phase A: g = sigma^3 r^2 from the scores
+      if (!(ok = g.wait(&sm.s_full, j & 1, 60))) break;
+      tc_fence_after();
+      const float base = slope * float(j * BLK - row);       // bias of key column 0 of this tile
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sreg[32];
+        tmem_ld32(tmem_addr(tS, lane_base, 64 * w + 32 * c), sreg);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float F;
+          score_fg(__uint_as_float(sreg[i]), scale, fmaf(slope, float(64 * w + 32 * c + i), base), F, gq[32 * c + i]);
+          gq[32 * c + i] *= ginv;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&sm.s_free);
+      // ---- phase B: dS = g (dP' - Delta'), packed over dP'
+      if (!(ok = g.wait(&sm.dp_full, j & 1, 61))) break;
+      tc_fence_after();
+      const bool diag = (j == qt);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t dreg[32], preg[16];
+        tmem_ld32(tmem_addr(tP, lane_base, 64 * w + 32 * c), dreg);
+        tmem_wait_ld();
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          ds[i] = gq[32 * c + i] * (__uint_as_float(dreg[i]) - dlt);
+          if (diag && 64 * w + 32 * c + i > r) ds[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) preg[i] = Pack16<T>::pack(ds[2 * i], ds[2 * i + 1]);
+        tmem_st16(tmem_addr(tP, lane_base, packed_col(w, c)), preg);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.ds_full);
+    }
+    if (ok) ok = g.wait(&sm.dq_full, 0, 62);
+    named_barrier(1, 256);
+    if (!g.aborted()) {
+      tc_fence_after();
+      const float mul = 2.0f * scale / kDsScale;
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {                     // warpgroup w stores columns [w*D/2, (w+1)*D/2)
+        uint32_t oreg[32];
+        const int col0 = w * (D / 2) + c * 32;
+        tmem_ld32(tmem_addr(tQ, lane_base, col0), oreg);
+        tmem_wait_ld();
+        stage_row32<T>(sm.q, r, col0, oreg, mul);
+      }
+      fence_async_smem();
+      named_barrier(1, 256);
+      if (tid == 0) {
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_store_4d(&maps.dq, sm.q + c * (BLK * 128), c * 64, qt * BLK, h, b);
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------- 3. d_k / d_v kernel
+template <int D>
+struct DkvSmem {
+  static constexpr int kTileBytes = BLK * D * 2;
+  alignas(1024) unsigned char k[kTileBytes];
+  alignas(1024) unsigned char v[kTileBytes];
+  alignas(1024) unsigned char q[kBwdStages][kTileBytes];     // reused as d_v / d_k staging in the epilogue
+  alignas(1024) unsigned char dout[kBwdStages][kTileBytes];
+  alignas(16) float delta[kBwdStages][BLK];                  // Delta and 1/(L+eps) of the staged query tile
+  alignas(16) float inv[kBwdStages][BLK];
+  uint64_t kv_full, q_full[kBwdStages], q_empty[kBwdStages], do_full[kBwdStages], do_empty[kBwdStages];
+  uint64_t s_full, p_full, dp_full, ds_full, acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct DkvMaps { CUtensorMap q, dout, k, v, dk, dv; };
+
+// TMEM columns: S^T / packed P^T [0,128)   dP'^T / packed dS^T [128,256)   dV [256,256+D)   dK [256+D,256+2D)
+template <typename T, int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  using S = DkvSmem<D>;
+  S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int kt = blockIdx.x;                                 // early key tiles see the most queries: first
+  const int n_q_total = (p.T + BLK - 1) / BLK;
+  const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
+  Guard g{&sm.abort_flag, p.status};
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.kv_full, 1); mbar_init(&sm.s_full, 1); mbar_init(&sm.p_full, 256);
+    mbar_init(&sm.dp_full, 1); mbar_init(&sm.ds_full, 256); mbar_init(&sm.acc_full, 1);
+    for (int i = 0; i < kBwdStages; ++i) {
+      mbar_init(&sm.q_full[i], 1); mbar_init(&sm.q_empty[i], 1); mbar_init(&sm.do_full[i], 1); mbar_init(&sm.do_empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 8) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tS = tmem, tP = tmem + BLK, tV = tmem + 2 * BLK, tK = tmem + 2 * BLK + D;
+
+  if (warp == 8) {
+    if (elect_one()) {
+      mbar_expect_tx(&sm.kv_full, 2 * S::kTileBytes);
+      load_tile_tma_noexpect<D>(sm.k, &maps.k, &sm.kv_full, kt * BLK, h, b);
+      load_tile_tma_noexpect<D>(sm.v, &maps.v, &sm.kv_full, kt * BLK, h, b);
+      const float* delta_bh = p.delta + (int64_t(b) * p.H + h) * pad_rows(p.T);
+      const float* inv_bh = delta_bh + int64_t(p.B) * p.H * pad_rows(p.T);
+      for (int it = 0; it < n; ++it) {
+        const int st = it % kBwdStages, qi = kt + it;
+        const uint32_t ph = (it / kBwdStages) & 1;
+        if (!g.wait(&sm.q_empty[st], ph ^ 1, 70)) break;
+        mbar_expect_tx(&sm.q_full[st], S::kTileBytes + 2 * BLK * 4);
+        load_tile_tma_noexpect<D>(sm.q[st], &maps.q, &sm.q_full[st], qi * BLK, h, b);
+        bulk_load(sm.delta[st], delta_bh + qi * BLK, BLK * 4, &sm.q_full[st]);
+        bulk_load(sm.inv[st], inv_bh + qi * BLK, BLK * 4, &sm.q_full[st]);
+        if (!g.wait(&sm.do_empty[st], ph ^ 1, 71)) break;
+        load_tile_tma<D>(sm.dout[st], &maps.dout, &sm.do_full[st], qi * BLK, h, b);
+      }
+    }
+  } else if (warp == 9) {
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
+      constexpr uint32_t idesc_acc = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
+      auto issue_nt = [&](uint32_t d_tmem, const unsigned char* a, const unsigned char* bm) {
+        const uint32_t aa = smem_u32(a), ba = smem_u32(bm);
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s) {
+          const uint32_t off = (s / 4) * (BLK * 128) + (s % 4) * 32;
+          mma_ss(d_tmem, smem_desc_sw128(aa + off, 16, 1024), smem_desc_sw128(ba + off, 16, 1024), idesc_s, s > 0);
+        }
+      };
+      auto issue_acc = [&](uint32_t d_tmem, uint32_t a_tmem, const unsigned char* bm, bool first) {   // D += A(tmem) B, B MN-major
+        const uint32_t ba = smem_u32(bm);
+#pragma unroll
+        for (int s = 0; s < BLK / 16; ++s)
+          mma_ts(d_tmem, a_tmem + packed_kstep_col(s), smem_desc_sw128(ba + s * 2048, BLK * 128, 1024), idesc_acc, !(first && s == 0));
+      };
+      bool ok = g.wait(&sm.kv_full, 0, 80) && g.wait(&sm.q_full[0], 0, 81);
+      if (ok) { tc_fence_after(); issue_nt(tS, sm.k, sm.q[0]); mma_commit(&sm.s_full); }
+      ok = ok && g.wait(&sm.do_full[0], 0, 82);
+      if (ok) { tc_fence_after(); issue_nt(tP, sm.v, sm.dout[0]); mma_commit(&sm.dp_full); }
+      for (int it = 0; it < n && ok; ++it) {
+        const int st = it % kBwdStages, st1 = (it + 1) % kBwdStages;
+        const uint32_t ph1 = ((it + 1) / kBwdStages) & 1;
+        if (!(ok = g.wait(&sm.p_full, it & 1, 83))) break;
+        tc_fence_after();
+        issue_acc(tV, tS, sm.dout[st], it == 0);             // dV += P^T dO'
+        mma_commit(&sm.do_empty[st]);
+        if (it + 1 < n) {
+          if (!(ok = g.wait(&sm.q_full[st1], ph1, 84))) break;
+          tc_fence_after();
+          issue_nt(tS, sm.k, sm.q[st1]);                     // S^T of the next query tile
+          mma_commit(&sm.s_full);
+        }
+        if (!(ok = g.wait(&sm.ds_full, it & 1, 85))) break;
+        tc_fence_after();
+        issue_acc(tK, tP, sm.q[st], it == 0);                // dK += dS^T Q
+        mma_commit(&sm.q_empty[st]);
+        if (it + 1 < n) {
+          if (!(ok = g.wait(&sm.do_full[st1], ph1, 86))) break;
+          tc_fence_after();
+          issue_nt(tP, sm.v, sm.dout[st1]);                  // dP'^T of the next query tile
+          mma_commit(&sm.dp_full);
+        }
+      }
+      if (ok) mma_commit(&sm.acc_full);
+    }
+  } else {
+    const int w = warp >> 2;                                 // query-column half of this warpgroup
+    const int r = tid & (BLK - 1);                           // key row inside the tile == TMEM lane
+    const int key = kt * BLK + r;
+    const uint32_t lane_base = uint32_t(warp & 3) * 32;
+    const float slope = p.slopes[h], scale = p.scale;
+    bool ok = true;
+    for (int it = 0; it < n; ++it) {
+      const int st = it % kBwdStages, qi = kt + it;
+      const bool diag = (it == 0);
+      float gq[64];
+      // ---- phase A: p = sigma^4 inv -> packed P^T over S^T; g inv kept in registers
+      if (!(ok = g.wait(&sm.q_full[st], (it / kBwdStages) & 1, 93))) break;       // Delta / inv arrived with the Q tile
+      if (!(ok = g.wait(&sm.s_full, it & 1, 90))) break;
+      tc_fence_after();
+      const float base = slope * float(key - qi * BLK);      // bias of query column 0: -slope*(q-key)
+      const float* iv = sm.inv[st];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sreg[32], preg[16];
+        tmem_ld32(tmem_addr(tS, lane_base, 64 * w + 32 * c), sreg);
+        tmem_wait_ld();
+        float F[32];
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 v4 = *reinterpret_cast<const float4*>(iv + 64 * w + 32 * c + 4 * i4);
+          const float invs[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = 4 * i4 + e, col = 64 * w + 32 * c + i;
+            float f, gg;
+            score_fg(__uint_as_float(sreg[i]), scale, fmaf(-slope, float(col), base), f, gg);
+            const bool dead = diag && col < r;
+            F[i] = dead ? 0.f : f * (invs[e] * kPScale);
+            gq[32 * c + i] = dead ? 0.f : gg * (invs[e] * kDsScale);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) preg[i] = Pack16<T>::pack(F[2 * i], F[2 * i + 1]);
+        tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.p_full);
+      // ---- phase B: dS^T = g inv (dP^T - Delta[q]) -> packed over dP^T
+      if (!(ok = g.wait(&sm.dp_full, it & 1, 91))) break;
+      tc_fence_after();
+      const float* dl = sm.delta[st];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t dreg[32], preg[16];
+        tmem_ld32(tmem_addr(tP, lane_base, 64 * w + 32 * c), dreg);
+        tmem_wait_ld();
+        float ds[32];
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(dl + 64 * w + 32 * c + 4 * i4);
+          ds[4 * i4 + 0] = gq[32 * c + 4 * i4 + 0] * (__uint_as_float(dreg[4 * i4 + 0]) - d4.x);
+          ds[4 * i4 + 1] = gq[32 * c + 4 * i4 + 1] * (__uint_as_float(dreg[4 * i4 + 1]) - d4.y);
+          ds[4 * i4 + 2] = gq[32 * c + 4 * i4 + 2] * (__uint_as_float(dreg[4 * i4 + 2]) - d4.z);
+          ds[4 * i4 + 3] = gq[32 * c + 4 * i4 + 3] * (__uint_as_float(dreg[4 * i4 + 3]) - d4.w);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) preg[i] = Pack16<T>::pack(ds[2 * i], ds[2 * i + 1]);
+        tmem_st16(tmem_addr(tP, lane_base, packed_col(w, c)), preg);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.ds_full);
+    }
+    if (ok) ok = g.wait(&sm.acc_full, 0, 92);
+    named_barrier(1, 256);
+    if (!g.aborted()) {
+      // warpgroup 0 stores d_v, warpgroup 1 stores d_k (scaled by 2*scale)
+      tc_fence_after();
+      unsigned char* stage = sm.q[w];
+      const float mul = w == 0 ? 1.0f / kPScale : 2.0f * scale / kDsScale;
+      const uint32_t src = w == 0 ? tV : tK;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t oreg[32];
+        tmem_ld32(tmem_addr(src, lane_base, c * 32), oreg);
+        tmem_wait_ld();
+        stage_row32<T>(stage, r, c * 32, oreg, mul);
+      }
+      fence_async_smem();
+      named_barrier(2 + w, BLK);
+      if (r == 0) {
+        const CUtensorMap* m = w == 0 ? &maps.dv : &maps.dk;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_store_4d(m, stage + c * (BLK * 128), c * 64, kt * BLK, h, b);
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, kTmemCols);
+}
+
+
+template <typename T, int D>
+int launch_bwd(const AttnParams& p, cudaStream_t st) {
+  float* inv_rows = p.delta + int64_t(p.B) * p.H * pad_rows(p.T);
+  DqMaps mq;
+  DkvMaps mk;
+  if (!make_tmap_bhtd(&mq.q, p.q, p.B, p.H, p.T, D, p.qs, 64, BLK) ||
+      !make_tmap_bhtd(&mq.dout, p.d_out, p.B, p.H, p.T, D, p.dos, 64, BLK) ||
+      !make_tmap_bhtd(&mq.k, p.k, p.B, p.H, p.T, D, p.ks, 64, BLK) ||
+      !make_tmap_bhtd(&mq.v, p.v, p.B, p.H, p.T, D, p.vs, 64, BLK) ||
+      !make_tmap_bhtd(&mq.dq, p.d_q, p.B, p.H, p.T, D, p.dqs, 64, BLK) ||
+      !make_tmap_bhtd(&mk.dk, p.d_k, p.B, p.H, p.T, D, p.dks, 64, BLK) ||
+      !make_tmap_bhtd(&mk.dv, p.d_v, p.B, p.H, p.T, D, p.dvs, 64, BLK))
+    return FAT_ERR_LAUNCH;
+  mk.q = mq.q; mk.dout = mq.dout; mk.k = mq.k; mk.v = mq.v;
+
+  {   // 1. prepare
+    constexpr int RPW = 32 / (D / 8);
+    const int64_t rows = int64_t(p.B) * p.H * pad_rows(p.T);
+    int64_t blocks = (rows + RPW * 8 - 1) / (RPW * 8);
+    if (blocks > 16 * kNumSM) blocks = 16 * kNumSM;
+    attn_bwd_prepare_kernel<T, D><<<unsigned(blocks), 256, 0, st>>>(p, inv_rows);
+    if (int rc = check_launch("attn_bwd_prepare")) return rc;
+  }
+  const int tiles = (p.T + BLK - 1) / BLK;
+  dim3 grid(tiles, p.H, p.B);
+  {   // 2. d_q
+    auto kern = attn_bwd_dq_tc_kernel<T, D>;
+    const size_t smem = sizeof(DqSmem<D>) + 1024;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+      set_error("attn_bwd_dq_tc: cannot reserve %zu bytes of shared memory", smem); return FAT_ERR_LAUNCH;
+    }
+    kern<<<grid, kBwdThreads, smem, st>>>(mq, p);
+    if (int rc = check_launch("attn_bwd_dq_tc")) return rc;
+  }
+  {   // 3. d_k, d_v
+    auto kern = attn_bwd_dkv_tc_kernel<T, D>;
+    const size_t smem = sizeof(DkvSmem<D>) + 1024;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+      set_error("attn_bwd_dkv_tc: cannot reserve %zu bytes of shared memory", smem); return FAT_ERR_LAUNCH;
+    }
+    kern<<<grid, kBwdThreads, smem, st>>>(mk, p);
+    if (int rc = check_launch("attn_bwd_dkv_tc")) return rc;
+  }
+  return FAT_OK;
+}
+
+}  // namespace
+
+size_t attn_bwd_tc_workspace_bytes(int B, int H, int T, int D) {
+  (void)D;
+  return 2 * size_t(B) * H * pad_rows(T) * sizeof(float);      // Delta and 1/(L+eps), rows padded to whole tiles
+}
+
+int attn_bwd_tc(const AttnParams& p, int dtype, cudaStream_t st) {
+  if (dtype == FAT_BF16) return p.D == 128 ? launch_bwd<__nv_bfloat16, 128>(p, st) : launch_bwd<__nv_bfloat16, 64>(p, st);
+  if (dtype == FAT_F16) return p.D == 128 ? launch_bwd<__half, 128>(p, st) : launch_bwd<__half, 64>(p, st);
+  set_error("attn_bwd_tc: unsupported dtype tag %d", dtype);
+  return FAT_ERR_DTYPE;
+}
+
+}  // namespace fat

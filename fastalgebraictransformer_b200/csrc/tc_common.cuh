@@ -151,10 +151,14 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
 }
 
 // Instruction descriptor of tcgen05.mma kind::f16 with float32 accumulation.
-//   ab_fmt: 0 = f16, 1 = bf16.  a_mn / b_mn: 1 when the operand is MN-major (transposed).
-__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int ab_fmt, int a_mn, int b_mn) {
-  return (1u << 4) | (uint32_t(ab_fmt) << 7) | (uint32_t(ab_fmt) << 10) | (uint32_t(a_mn) << 15) |
+//   a_fmt / b_fmt: 0 = f16, 1 = bf16 (the two operands may differ).
+//   a_mn / b_mn: 1 when the operand is MN-major (transposed).
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int a_fmt, int b_fmt, int a_mn, int b_mn) {
+  return (1u << 4) | (uint32_t(a_fmt) << 7) | (uint32_t(b_fmt) << 10) | (uint32_t(a_mn) << 15) |
          (uint32_t(b_mn) << 16) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int ab_fmt, int a_mn, int b_mn) {
+  return idesc_f16(M, N, ab_fmt, ab_fmt, a_mn, b_mn);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.

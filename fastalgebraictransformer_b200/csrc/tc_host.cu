@@ -29,6 +29,10 @@ EncodeFn encode_fn() {
 
 bool make_tmap_bhtd(CUtensorMap* out, const void* base, int B, int H, int T, int D,
                     const int64_t* s, int box_d, int box_t) {
+  // The encoder is a driver-API call: it needs the primary context bound to the calling thread,
+  // which a thread that has only been handed pointers (e.g. an autograd worker) may not have yet.
+  static thread_local bool bound = false;
+  if (!bound) { cudaFree(nullptr); bound = true; }
   EncodeFn fn = encode_fn();
   if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return false; }
   const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(T), cuuint64_t(H), cuuint64_t(B)};
