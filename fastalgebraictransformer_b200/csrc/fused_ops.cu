@@ -9,6 +9,7 @@
 // Shapes or alignments that do not fit the register-resident scheme go through "slow"
 // kernels (one block per row, two passes, scalar accesses) that accept anything.
 #include <initializer_list>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -18,6 +19,11 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kMaxVPT = 8;
 constexpr int kNormBwdMaxBlocks = 4 * kNumSM;   // rows of the d_weight partial-sum scratch
+
+// Scratch of fat_norm_bwd_static: a fixed array inside the library image.  Every GPU that loads
+// the library holds these 16 MiB until the process exits; all calls on a device share them.
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;
+constexpr int kMaxDevices = 64;
 
 // ------------------------------------------------------------------ group reduction
 // Sums NV values over the G threads (G = 32..256, power of two) that share a row.
@@ -609,6 +615,40 @@ int check_2d(const char* what, int64_t n_rows, int64_t n_cols) {
 }  // namespace
 }  // namespace fat
 
+static __device__ __align__(256) unsigned char g_norm_bwd_scratch[fat::kStaticScratchBytes];
+
+namespace fat {
+namespace {
+
+// Device address of g_norm_bwd_scratch on the current device.  In host code the array's name is
+// only a handle, not a device pointer, so the address is asked for once per device (with that
+// device current) and cached.
+int static_scratch(void** out) {
+  static std::mutex mu;
+  static void* cached[kMaxDevices] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("norm_bwd_static: cannot identify the current device (%s)", cudaGetErrorString(e));
+    return FAT_ERR_LAUNCH;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_norm_bwd_scratch);
+    if (e != cudaSuccess || !ptr) {
+      set_error("norm_bwd_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return FAT_ERR_LAUNCH;
+    }
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return FAT_OK;
+}
+
+}  // namespace
+}  // namespace fat
+
 using namespace fat;
 
 extern "C" {
@@ -654,6 +694,24 @@ int fat_norm_bwd(const void* d_out, const void* x, const void* weight, const flo
   if (!workspace) { set_error("norm_bwd: null workspace"); return FAT_ERR_WORKSPACE; }
   FAT_DTYPE_SWITCH(dtype, norm_bwd_t<T>(d_out, x, weight, mean, d_x, d_weight, workspace, workspace_bytes, n_rows, n_cols,
                                         dos, xs, dxs, eps, (cudaStream_t)stream));
+}
+
+size_t fat_norm_bwd_static_capacity(void) { return kStaticScratchBytes; }
+
+int fat_norm_bwd_static(const void* d_out, const void* x, const void* weight, const float* mean, void* d_x, void* d_weight,
+                        int64_t n_rows, int64_t n_cols, int64_t dos, int64_t xs, int64_t dxs, double eps, int dtype,
+                        void* stream) {
+  if (int rc = check_2d("norm_bwd_static", n_rows, n_cols)) return rc;
+  const size_t need = fat_norm_bwd_workspace_bytes(n_rows, n_cols, dtype);
+  if (need > kStaticScratchBytes) {
+    set_error("norm_bwd_static: %lld columns need %zu bytes of scratch, the built-in array holds %zu; "
+              "use fat_norm_bwd with a caller-owned workspace", (long long)n_cols, need, kStaticScratchBytes);
+    return FAT_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  return fat_norm_bwd(d_out, x, weight, mean, d_x, d_weight, scratch, kStaticScratchBytes, n_rows, n_cols, dos, xs, dxs,
+                      eps, dtype, stream);
 }
 
 int fat_softmax_fwd(const void* x, void* p, int64_t n_rows, int64_t n_cols, int64_t xs, int64_t ps,

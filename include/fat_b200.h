@@ -103,6 +103,34 @@ FAT_API int fat_norm_bwd(const void* d_out, const void* x, const void* weight, c
                  int64_t d_out_row_stride, int64_t x_row_stride, int64_t d_x_row_stride,
                  double eps, int dtype, void* stream);
 
+/* Mean-error-norm backward for callers that cannot provide scratch memory.
+ * (No counterpart in the reference: its backward lets PyTorch allocate whatever it needs.)
+ *
+ * Some hosts of this library may not allocate device memory when they call in: a plugin
+ * invoked from inside another framework's memory plan, a runtime whose arena is already carved
+ * up, a callback running where cudaMalloc is forbidden.  fat_norm_bwd needs a workspace for
+ * the per-block partial sums of d_weight; this variant keeps that workspace in a fixed 16 MiB
+ * array that is part of the library image, so the caller passes inputs and outputs only.  It
+ * calls no allocator of any kind.
+ *
+ *  - Limit: fat_norm_bwd_workspace_bytes(n_rows, n_cols, dtype) must not exceed
+ *    fat_norm_bwd_static_capacity() (16 MiB: up to 7084 columns for F32/BF16/F16, 3542 for
+ *    F64); larger requests return FAT_ERR_WORKSPACE and launch nothing.
+ *  - Every GPU on which the library is loaded holds the 16 MiB until the process exits.
+ *  - The first call on each device looks up the array's device address (one host-side
+ *    query, with that device current).  Make that first call before starting a stream capture.
+ *  - All calls on one device share the array.  It is fully rewritten by each call before it
+ *    is read, so nothing has to be cleared, but two calls that overlap on the GPU (different
+ *    streams) race on it: serialise them.
+ * Results are identical to fat_norm_bwd. */
+FAT_API size_t fat_norm_bwd_static_capacity(void);
+
+FAT_API int fat_norm_bwd_static(const void* d_out, const void* x, const void* weight, const float* mean,
+                 void* d_x, void* d_weight,
+                 int64_t n_rows, int64_t n_cols,
+                 int64_t d_out_row_stride, int64_t x_row_stride, int64_t d_x_row_stride,
+                 double eps, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Rational softmax over the last dimension.  p = sigma(x)^4 / (sum_c sigma(x)^4 + eps).
  * Replaces RationalSoftmax.forward / rational_softmax_fwd_kernel (fused_ops.py:52-106, 435-462).
