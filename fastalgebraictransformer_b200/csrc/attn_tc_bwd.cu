@@ -22,8 +22,8 @@ using namespace tcattn;
 // dtype: tcgen05.mma kind::f16 wants both operands in one format (an f16 A with a bf16 B is an
 // illegal instruction on this hardware).  Power-of-two pre-scales keep small values out of the
 // fp16 subnormals; they are undone exactly in the epilogue multipliers.
-constexpr float kPScale = 1024.0f;       // p = sigma^4/(L+eps) in [0,1]
-constexpr float kDsScale = 256.0f;       // |dS| stays far below 65504/256
+constexpr float kOpScale = 256.0f;       // applied to p (<= 1) and dS (|dS| stays far below 65504/256); the prepare
+                                         // kernel folds it into the per-row normaliser it writes
 
 constexpr int kBwdThreads = 320;         // warps 0-7: element-wise (2 warpgroups), warp 8: TMA, warp 9: MMA
 constexpr int kBwdStages = 2;
@@ -68,21 +68,24 @@ attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out) {
     for (int m = LPR / 2; m > 0; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
     if (row < n_rows) {
       const float inv = live ? 1.0f / (p.L[(int64_t(b) * p.H + h) * p.T + t] + p.eps) : 0.f;
-      if (l == 0) { p.delta[row] = dot; inv_out[row] = inv; }           // rows in the padding get 0
+      if (l == 0) { p.delta[row] = dot; inv_out[row] = inv * kOpScale; }   // rows in the padding get 0
     }
   }
 }
 
 // ------------------------------------------------------------------------------------- element-wise math
-// For a raw score accumulator `acc`: s = acc*scale + bias, r = 1/(|s|+1), sigma = (s r + 1)/2.
-// Returns F = sigma^4 and g = sigma^3 r^2 (the factor 2 of the derivative is applied in the epilogues).
-__device__ __forceinline__ void score_fg(float acc, float scale, float bias, float& F, float& g) {
-  const float s = fmaf(acc, scale, bias);
-  const float r = rcp_approx(fabsf(s) + 1.0f);
-  const float sg = fmaf(s * r, 0.5f, 0.5f);
-  const float s2 = sg * sg;
-  F = s2 * s2;
-  g = (s2 * sg) * (r * r);
+// Packed pair of raw score accumulators -> sigma-derived factors, in units that avoid every constant
+// multiply: with s = acc*scale + bias, r = 1/(|s|+1), w = 1 + s r = 2 sigma,
+//   g8  = w^3 r^2 = 8 sigma^3 r^2   (half of 8x the derivative of sigma^4; the constants go to the epilogues)
+//   F16 = w^4     = 16 sigma^4      (when WANT_F)
+template <bool WANT_F, bool SHARED>
+__device__ __forceinline__ void score_fg2(f32x2 acc2, f32x2 scale2, f32x2 bias2, f32x2 one2, f32x2& F2, f32x2& g2) {
+  const f32x2 s2 = fma2(acc2, scale2, bias2);
+  f32x2 r2, w2;
+  sigma_terms2<SHARED>(s2, one2, r2, w2);
+  const f32x2 u2 = mul2(w2, r2);
+  g2 = mul2(mul2(u2, u2), w2);
+  if (WANT_F) { const f32x2 q2 = mul2(w2, w2); F2 = mul2(q2, q2); }
 }
 
 // TMEM column (relative to the start of a 128-column region) where warpgroup w keeps its packed
@@ -148,6 +151,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
   const int qt = gridDim.x - 1 - blockIdx.x;                 // long rows first
   const int n = qt + 1;                                      // key tiles 0..qt (causal)
   Guard g{&sm.abort_flag, p.status};
+  FAT_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -183,18 +187,14 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
       constexpr uint32_t idesc_dq = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
-      auto issue_nt = [&](uint32_t d_tmem, const unsigned char* a, const unsigned char* bm) {   // D = A B^T over head dim
-        const uint32_t aa = smem_u32(a), ba = smem_u32(bm);
-#pragma unroll
-        for (int s = 0; s < D / 16; ++s) {
-          const uint32_t off = (s / 4) * (BLK * 128) + (s % 4) * 32;
-          mma_ss(d_tmem, smem_desc_sw128(aa + off, 16, 1024), smem_desc_sw128(ba + off, 16, 1024), idesc_s, s > 0);
-        }
-      };
+      const uint64_t qd = desc_kmajor(sm.q), dod = desc_kmajor(sm.dout);
+      const uint64_t kd[kBwdStages] = {desc_kmajor(sm.k[0]), desc_kmajor(sm.k[1])};
+      const uint64_t kd_mn[kBwdStages] = {desc_mnmajor(sm.k[0]), desc_mnmajor(sm.k[1])};
+      const uint64_t vd[kBwdStages] = {desc_kmajor(sm.v[0]), desc_kmajor(sm.v[1])};
       bool ok = g.wait(&sm.qdo_full, 0, 50) && g.wait(&sm.k_full[0], 0, 51);
-      if (ok) { tc_fence_after(); issue_nt(tS, sm.q, sm.k[0]); mma_commit(&sm.s_full); }
+      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tS, qd, kd[0], idesc_s); mma_commit(&sm.s_full); }
       ok = ok && g.wait(&sm.v_full[0], 0, 52);
-      if (ok) { tc_fence_after(); issue_nt(tP, sm.dout, sm.v[0]); mma_commit(&sm.dp_full); mma_commit(&sm.v_empty[0]); }
+      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tP, dod, vd[0], idesc_s); mma_commit(&sm.dp_full); mma_commit(&sm.v_empty[0]); }
       for (int j = 0; j < n && ok; ++j) {
         const int st = j % kBwdStages, st1 = (j + 1) % kBwdStages;
         const uint32_t ph1 = ((j + 1) / kBwdStages) & 1;
@@ -202,22 +202,17 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
           if (!(ok = g.wait(&sm.s_free, j & 1, 53))) break;
           if (!(ok = g.wait(&sm.k_full[st1], ph1, 54))) break;
           tc_fence_after();
-          issue_nt(tS, sm.q, sm.k[st1]);
+          issue_gemm_nt<D>(tS, qd, kd[st1], idesc_s);
           mma_commit(&sm.s_full);
         }
         if (!(ok = g.wait(&sm.ds_full, j & 1, 55))) break;
         tc_fence_after();
-        {
-          const uint32_t ka = smem_u32(sm.k[st]);
-#pragma unroll
-          for (int s = 0; s < BLK / 16; ++s)
-            mma_ts(tQ, tP + packed_kstep_col(s), smem_desc_sw128(ka + s * 2048, BLK * 128, 1024), idesc_dq, !(j == 0 && s == 0));
-        }
+        issue_gemm_tn<true>(tQ, tP, kd_mn[st], idesc_dq, j > 0);       // dQ += dS K
         mma_commit(&sm.k_empty[st]);
         if (j + 1 < n) {
           if (!(ok = g.wait(&sm.v_full[st1], ph1, 56))) break;
           tc_fence_after();
-          issue_nt(tP, sm.dout, sm.v[st1]);
+          issue_gemm_nt<D>(tP, dod, vd[st1], idesc_s);
           mma_commit(&sm.dp_full);
           mma_commit(&sm.v_empty[st1]);
         }
@@ -232,56 +227,74 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
     const float slope = p.slopes[h], scale = p.scale;
     const int64_t srow = (int64_t(b) * p.H + h) * pad_rows(p.T) + row;
     const float dlt = p.delta[srow];                                               // Delta of this query
-    const float ginv = p.delta[int64_t(p.B) * p.H * pad_rows(p.T) + srow] * kDsScale;   // 1/(L+eps), pre-scaled
+    const float ginv = p.delta[int64_t(p.B) * p.H * pad_rows(p.T) + srow] ;              // kOpScale/(L+eps)
+    const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(2.f * slope, 2.f * slope);
+    const f32x2 ndlt2 = pk2(-dlt, -dlt);
     bool ok = true;
     for (int j = 0; j < n; ++j) {
-      float gq[64];
-      // ---- phase A: g = sigma^3 r^2 from the scores
+      f32x2 gq[32];
+      // ---- phase A: g = sigma^3 r^2 / (L+eps) from the scores
+      TR_BEGIN();
       if (!(ok = g.wait(&sm.s_full, j & 1, 60))) break;
+      TR_WAITED();
       tc_fence_after();
       const float base = slope * float(j * BLK - row);       // bias of key column 0 of this tile
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t sreg[32];
         tmem_ld32(tmem_addr(tS, lane_base, 64 * w + 32 * c), sreg);
-        tmem_wait_ld();
+        tmem_wait_ld_regs(sreg);
+        const int col0 = 64 * w + 32 * c;
+        f32x2 bias2 = pk2(fmaf(slope, float(col0), base), fmaf(slope, float(col0 + 1), base));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float F;
-          score_fg(__uint_as_float(sreg[i]), scale, fmaf(slope, float(64 * w + 32 * c + i), base), F, gq[32 * c + i]);
-          gq[32 * c + i] *= ginv;
+        for (int i = 0; i < 16; ++i) {
+          f32x2 F2, g2;
+          const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+          if (i % 4 == 0) score_fg2<false, true>(acc2, scale2, bias2, half2, F2, g2);
+          else            score_fg2<false, false>(acc2, scale2, bias2, half2, F2, g2);
+          bias2 = add2(bias2, step2);
+          gq[16 * c + i] = g2;
         }
       }
       tc_fence_before();
       mbar_arrive(&sm.s_free);
-      // ---- phase B: dS = g (dP' - Delta'), packed over dP'
+      TR_WORKED();
+      // ---- phase B: dS = g (dP - Delta), packed over dP
       if (!(ok = g.wait(&sm.dp_full, j & 1, 61))) break;
+      TR_WAITED2();
       tc_fence_after();
       const bool diag = (j == qt);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t dreg[32], preg[16];
         tmem_ld32(tmem_addr(tP, lane_base, 64 * w + 32 * c), dreg);
-        tmem_wait_ld();
-        float ds[32];
+        tmem_wait_ld_regs(dreg);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          ds[i] = gq[32 * c + i] * (__uint_as_float(dreg[i]) - dlt);
-          if (diag && 64 * w + 32 * c + i > r) ds[i] = 0.f;
+        for (int i = 0; i < 16; ++i) {
+          const f32x2 ds2 = mul2(gq[16 * c + i], add2(pk2(__uint_as_float(dreg[2 * i]), __uint_as_float(dreg[2 * i + 1])), ndlt2));
+          float d0, d1;
+          upk2(ds2, d0, d1);
+          if (diag) {
+            if (64 * w + 32 * c + 2 * i > r) d0 = 0.f;
+            if (64 * w + 32 * c + 2 * i + 1 > r) d1 = 0.f;
+          }
+          preg[i] = Pack16<T>::pack(d0, d1);
         }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) preg[i] = Pack16<T>::pack(ds[2 * i], ds[2 * i + 1]);
         tmem_st16(tmem_addr(tP, lane_base, packed_col(w, c)), preg);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.ds_full);
+      TR_WORKED2();
     }
+#ifdef FAT_TRACE
+    if (traced && (tid & 127) == 0) { long long* o = trace + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
+#endif
     if (ok) ok = g.wait(&sm.dq_full, 0, 62);
     named_barrier(1, 256);
     if (!g.aborted()) {
       tc_fence_after();
-      const float mul = 2.0f * scale / kDsScale;
+      const float mul = 0.25f * scale * ginv / kOpScale;        // 2 (derivative) / 8 (g8 units) * scale / (L+eps)
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {                     // warpgroup w stores columns [w*D/2, (w+1)*D/2)
         uint32_t oreg[32];
@@ -336,6 +349,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
   const int n_q_total = (p.T + BLK - 1) / BLK;
   const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
   Guard g{&sm.abort_flag, p.status};
+  FAT_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -376,45 +390,36 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
     if (elect_one()) {
       constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
       constexpr uint32_t idesc_acc = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
-      auto issue_nt = [&](uint32_t d_tmem, const unsigned char* a, const unsigned char* bm) {
-        const uint32_t aa = smem_u32(a), ba = smem_u32(bm);
-#pragma unroll
-        for (int s = 0; s < D / 16; ++s) {
-          const uint32_t off = (s / 4) * (BLK * 128) + (s % 4) * 32;
-          mma_ss(d_tmem, smem_desc_sw128(aa + off, 16, 1024), smem_desc_sw128(ba + off, 16, 1024), idesc_s, s > 0);
-        }
-      };
-      auto issue_acc = [&](uint32_t d_tmem, uint32_t a_tmem, const unsigned char* bm, bool first) {   // D += A(tmem) B, B MN-major
-        const uint32_t ba = smem_u32(bm);
-#pragma unroll
-        for (int s = 0; s < BLK / 16; ++s)
-          mma_ts(d_tmem, a_tmem + packed_kstep_col(s), smem_desc_sw128(ba + s * 2048, BLK * 128, 1024), idesc_acc, !(first && s == 0));
-      };
+      const uint64_t kd = desc_kmajor(sm.k), vd = desc_kmajor(sm.v);
+      const uint64_t qd[kBwdStages] = {desc_kmajor(sm.q[0]), desc_kmajor(sm.q[1])};
+      const uint64_t qd_mn[kBwdStages] = {desc_mnmajor(sm.q[0]), desc_mnmajor(sm.q[1])};
+      const uint64_t dod[kBwdStages] = {desc_kmajor(sm.dout[0]), desc_kmajor(sm.dout[1])};
+      const uint64_t dod_mn[kBwdStages] = {desc_mnmajor(sm.dout[0]), desc_mnmajor(sm.dout[1])};
       bool ok = g.wait(&sm.kv_full, 0, 80) && g.wait(&sm.q_full[0], 0, 81);
-      if (ok) { tc_fence_after(); issue_nt(tS, sm.k, sm.q[0]); mma_commit(&sm.s_full); }
+      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tS, kd, qd[0], idesc_s); mma_commit(&sm.s_full); }
       ok = ok && g.wait(&sm.do_full[0], 0, 82);
-      if (ok) { tc_fence_after(); issue_nt(tP, sm.v, sm.dout[0]); mma_commit(&sm.dp_full); }
+      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tP, vd, dod[0], idesc_s); mma_commit(&sm.dp_full); }
       for (int it = 0; it < n && ok; ++it) {
         const int st = it % kBwdStages, st1 = (it + 1) % kBwdStages;
         const uint32_t ph1 = ((it + 1) / kBwdStages) & 1;
         if (!(ok = g.wait(&sm.p_full, it & 1, 83))) break;
         tc_fence_after();
-        issue_acc(tV, tS, sm.dout[st], it == 0);             // dV += P^T dO'
+        issue_gemm_tn<true>(tV, tS, dod_mn[st], idesc_acc, it > 0);     // dV += P^T dO
         mma_commit(&sm.do_empty[st]);
         if (it + 1 < n) {
           if (!(ok = g.wait(&sm.q_full[st1], ph1, 84))) break;
           tc_fence_after();
-          issue_nt(tS, sm.k, sm.q[st1]);                     // S^T of the next query tile
+          issue_gemm_nt<D>(tS, kd, qd[st1], idesc_s);        // S^T of the next query tile
           mma_commit(&sm.s_full);
         }
         if (!(ok = g.wait(&sm.ds_full, it & 1, 85))) break;
         tc_fence_after();
-        issue_acc(tK, tP, sm.q[st], it == 0);                // dK += dS^T Q
+        issue_gemm_tn<true>(tK, tP, qd_mn[st], idesc_acc, it > 0);      // dK += dS^T Q
         mma_commit(&sm.q_empty[st]);
         if (it + 1 < n) {
           if (!(ok = g.wait(&sm.do_full[st1], ph1, 86))) break;
           tc_fence_after();
-          issue_nt(tP, sm.v, sm.dout[st1]);                  // dP'^T of the next query tile
+          issue_gemm_nt<D>(tP, vd, dod[st1], idesc_s);       // dP^T of the next query tile
           mma_commit(&sm.dp_full);
         }
       }
@@ -426,14 +431,17 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
     const int key = kt * BLK + r;
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
     const float slope = p.slopes[h], scale = p.scale;
+    const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(-2.f * slope, -2.f * slope);
     bool ok = true;
     for (int it = 0; it < n; ++it) {
       const int st = it % kBwdStages, qi = kt + it;
       const bool diag = (it == 0);
-      float gq[64];
-      // ---- phase A: p = sigma^4 inv -> packed P^T over S^T; g inv kept in registers
+      f32x2 gq[32];
+      // ---- phase A: p = sigma^4 / (L+eps) -> packed P^T over S^T; g / (L+eps) kept in registers
+      TR_BEGIN();
       if (!(ok = g.wait(&sm.q_full[st], (it / kBwdStages) & 1, 93))) break;       // Delta / inv arrived with the Q tile
       if (!(ok = g.wait(&sm.s_full, it & 1, 90))) break;
+      TR_WAITED();
       tc_fence_after();
       const float base = slope * float(key - qi * BLK);      // bias of query column 0: -slope*(q-key)
       const float* iv = sm.inv[st];
@@ -441,62 +449,73 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       for (int c = 0; c < 2; ++c) {
         uint32_t sreg[32], preg[16];
         tmem_ld32(tmem_addr(tS, lane_base, 64 * w + 32 * c), sreg);
-        tmem_wait_ld();
-        float F[32];
+        tmem_wait_ld_regs(sreg);
+        const int col0 = 64 * w + 32 * c;
+        f32x2 bias2 = pk2(fmaf(-slope, float(col0), base), fmaf(-slope, float(col0 + 1), base));
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const float4 v4 = *reinterpret_cast<const float4*>(iv + 64 * w + 32 * c + 4 * i4);
-          const float invs[4] = {v4.x, v4.y, v4.z, v4.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = 4 * i4 + e, col = 64 * w + 32 * c + i;
-            float f, gg;
-            score_fg(__uint_as_float(sreg[i]), scale, fmaf(-slope, float(col), base), f, gg);
-            const bool dead = diag && col < r;
-            F[i] = dead ? 0.f : f * (invs[e] * kPScale);
-            gq[32 * c + i] = dead ? 0.f : gg * (invs[e] * kDsScale);
+        for (int i = 0; i < 16; ++i) {
+          const float2 iv2f = *reinterpret_cast<const float2*>(iv + col0 + 2 * i);
+          const f32x2 iv2 = pk2(iv2f.x, iv2f.y);
+          f32x2 F2, g2;
+          const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+          if (i % 4 == 0) score_fg2<true, true>(acc2, scale2, bias2, half2, F2, g2);
+          else            score_fg2<true, false>(acc2, scale2, bias2, half2, F2, g2);
+          bias2 = add2(bias2, step2);
+          F2 = mul2(F2, iv2);
+          g2 = mul2(g2, iv2);
+          float p0, p1;
+          upk2(F2, p0, p1);
+          if (diag) {                                        // queries before the key see nothing of it
+            float g0, g1;
+            upk2(g2, g0, g1);
+            if (col0 + 2 * i < r) { p0 = 0.f; g0 = 0.f; }
+            if (col0 + 2 * i + 1 < r) { p1 = 0.f; g1 = 0.f; }
+            g2 = pk2(g0, g1);
           }
+          gq[16 * c + i] = g2;
+          preg[i] = Pack16<T>::pack(p0, p1);
         }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) preg[i] = Pack16<T>::pack(F[2 * i], F[2 * i + 1]);
         tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full);
-      // ---- phase B: dS^T = g inv (dP^T - Delta[q]) -> packed over dP^T
+      TR_WORKED();
+      // ---- phase B: dS^T = g (dP^T - Delta[q]) -> packed over dP^T
       if (!(ok = g.wait(&sm.dp_full, it & 1, 91))) break;
+      TR_WAITED2();
       tc_fence_after();
       const float* dl = sm.delta[st];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t dreg[32], preg[16];
         tmem_ld32(tmem_addr(tP, lane_base, 64 * w + 32 * c), dreg);
-        tmem_wait_ld();
-        float ds[32];
+        tmem_wait_ld_regs(dreg);
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(dl + 64 * w + 32 * c + 4 * i4);
-          ds[4 * i4 + 0] = gq[32 * c + 4 * i4 + 0] * (__uint_as_float(dreg[4 * i4 + 0]) - d4.x);
-          ds[4 * i4 + 1] = gq[32 * c + 4 * i4 + 1] * (__uint_as_float(dreg[4 * i4 + 1]) - d4.y);
-          ds[4 * i4 + 2] = gq[32 * c + 4 * i4 + 2] * (__uint_as_float(dreg[4 * i4 + 2]) - d4.z);
-          ds[4 * i4 + 3] = gq[32 * c + 4 * i4 + 3] * (__uint_as_float(dreg[4 * i4 + 3]) - d4.w);
+        for (int i = 0; i < 16; ++i) {
+          const float2 d2 = *reinterpret_cast<const float2*>(dl + 64 * w + 32 * c + 2 * i);
+          const f32x2 ds2 = mul2(gq[16 * c + i], add2(pk2(__uint_as_float(dreg[2 * i]), __uint_as_float(dreg[2 * i + 1])), pk2(-d2.x, -d2.y)));
+          float d0, d1;
+          upk2(ds2, d0, d1);
+          preg[i] = Pack16<T>::pack(d0, d1);
         }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) preg[i] = Pack16<T>::pack(ds[2 * i], ds[2 * i + 1]);
         tmem_st16(tmem_addr(tP, lane_base, packed_col(w, c)), preg);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.ds_full);
+      TR_WORKED2();
     }
+#ifdef FAT_TRACE
+    if (traced && (tid & 127) == 0) { long long* o = trace + 16 + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
+#endif
     if (ok) ok = g.wait(&sm.acc_full, 0, 92);
     named_barrier(1, 256);
     if (!g.aborted()) {
       // warpgroup 0 stores d_v, warpgroup 1 stores d_k (scaled by 2*scale)
       tc_fence_after();
       unsigned char* stage = sm.q[w];
-      const float mul = w == 0 ? 1.0f / kPScale : 2.0f * scale / kDsScale;
+      const float mul = w == 0 ? 0.0625f / kOpScale : 0.25f * scale / kOpScale;    // undo the 16x (F16) and 8x (g8) units
       const uint32_t src = w == 0 ? tV : tK;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {

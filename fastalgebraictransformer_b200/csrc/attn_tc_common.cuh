@@ -63,5 +63,113 @@ __device__ __forceinline__ void load_tile_tma(unsigned char* dst, const CUtensor
   for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + c * (BLK * 128), m, bar, c * 64, row0, h, b);
 }
 
+// ------------------------------------------------------------------ GEMM issue helpers (one thread)
+// Descriptors are built once per shared-memory buffer; inside the loops a K-step only adds a constant
+// to the address field, so issuing a whole 128x128x128 GEMM costs a few dozen instructions.
+__device__ __forceinline__ uint64_t desc_kmajor(const void* tile) { return smem_desc_sw128(smem_u32(tile), 16, 1024); }
+__device__ __forceinline__ uint64_t desc_mnmajor(const void* tile) { return smem_desc_sw128(smem_u32(tile), BLK * 128, 1024); }
+
+// acc[128 x 128] = A B^T over the head dimension; A and B are K-major [128][D] tiles.
+template <int D>
+__device__ __forceinline__ void issue_gemm_nt(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+#pragma unroll
+  for (int s = 0; s < D / 16; ++s) {
+    const uint32_t off = ((s / 4) * (BLK * 128) + (s % 4) * 32) >> 4;
+    mma_ss(d_tmem, adesc + off, bdesc + off, idesc, s > 0);
+  }
+}
+
+// acc[128 x N] (+)= A B with A in TMEM (128 x 128, packed 16-bit) and B an MN-major [128][N] tile.
+// SPLIT: A is stored as two 32-column halves 64 columns apart (one per element-wise warpgroup).
+template <bool SPLIT>
+__device__ __forceinline__ void issue_gemm_tn(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int s = 0; s < BLK / 16; ++s) {
+    const uint32_t acol = SPLIT ? uint32_t((s / 4) * 64 + (s % 4) * 8) : uint32_t(s * 8);
+    mma_ts(d_tmem, a_tmem + acol, bdesc + ((s * 2048) >> 4), idesc, accumulate || s > 0);
+  }
+}
+
+// ------------------------------------------------------------------ optional cycle tracing (-DFAT_TRACE builds only)
+// One chosen CTA accumulates the cycles its roles spend waiting and working and writes them to the buffer
+// registered with fat_debug_set_trace().  Compiled out of the shipped library.
+#ifdef FAT_TRACE
+#define FAT_TRACE_DECL(cond)                                                      \
+  long long* trace = reinterpret_cast<long long*>(p.dq_acc);                      \
+  const bool traced = trace && (cond);                                            \
+  long long tr_wait = 0, tr_work = 0, tr_wait2 = 0, tr_work2 = 0, tr_t0 = clock64(), tr_a = 0, tr_b = 0; \
+  (void)traced; (void)tr_wait; (void)tr_work; (void)tr_wait2; (void)tr_work2; (void)tr_t0; (void)tr_a; (void)tr_b
+#define TR_BEGIN() tr_a = clock64()
+#define TR_WAITED() tr_b = clock64(); tr_wait += tr_b - tr_a
+#define TR_WORKED() tr_a = clock64(); tr_work += tr_a - tr_b
+#define TR_WAITED2() tr_b = clock64(); tr_wait2 += tr_b - tr_a
+#define TR_WORKED2() tr_a = clock64(); tr_work2 += tr_a - tr_b
+#else
+#define FAT_TRACE_DECL(cond)
+#define TR_BEGIN()
+#define TR_WAITED()
+#define TR_WORKED()
+#define TR_WAITED2()
+#define TR_WORKED2()
+#endif
+
+// ------------------------------------------------------------------ packed fp32 pairs (sm_100 FFMA2 / FMUL2 / FADD2)
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void upk2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// Reciprocals of two numbers >= 1.  SHARED: from ONE special-function op, 1/a = b * (1/(a b)),
+// 1/b = a * (1/(a b)) (three extra multiplies); otherwise two special-function ops.  The kernels
+// mix both so that neither the special-function pipe nor the FMA pipe becomes the limiter.
+template <bool SHARED>
+__device__ __forceinline__ f32x2 rcp_pair(float a, float b) {
+  if (SHARED) {
+    const float rr = rcp_approx(a * b);
+    return pk2(b * rr, a * rr);
+  }
+  return pk2(rcp_approx(a), rcp_approx(b));
+}
+
+// For a packed pair of scores s: r = 1/(|s|+1) and w = 1 + s r = 2 sigma(s).
+template <bool SHARED>
+__device__ __forceinline__ void sigma_terms2(f32x2 s2, f32x2 one2, f32x2& r2, f32x2& w2) {
+  float s0, s1;
+  upk2(s2, s0, s1);
+  r2 = rcp_pair<SHARED>(fabsf(s0) + 1.0f, fabsf(s1) + 1.0f);
+  w2 = fma2(s2, r2, one2);
+}
+
+// Waits for this thread's outstanding TMEM loads.  The registers are listed as read-write operands so that
+// the compiler cannot move arithmetic on them above the wait.
+__device__ __forceinline__ void tmem_wait_ld_regs(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :: "memory");
+}
+
 }  // namespace tcattn
 }  // namespace fat

@@ -37,6 +37,44 @@ struct FwdSmem {
 
 struct FwdMaps { CUtensorMap q, k, v, out, out_lo; };
 
+// One thread's row of a 128x128 score tile: S (fp32, TMEM columns [0,128) from `trow`) ->
+// P = (2 sigma(S*scale + bias))^4 = 16 sigma^4 written back packed 16-bit over columns [0,64) (the factor
+// 16 cancels in O = P V / sum P); adds the row sum to l2.  `half2` holds the packed constant 1.
+// MASK: diagonal tile, keys with column index > r get no weight.  The chunk loop is kept rolled
+// (the body is ~400 instructions; unrolled four times it no longer fits the instruction cache).
+template <typename T, bool MASK>
+__device__ __forceinline__ void softmax_tile(uint32_t trow, int r, f32x2 scale2, f32x2 half2, f32x2 step2,
+                                             float slope, float base, f32x2& l2) {
+  uint32_t sreg[32];
+  tmem_ld32(trow, sreg);
+#pragma unroll 1
+  for (int c = 0; c < BLK / 32; ++c) {
+    tmem_wait_ld_regs(sreg);
+    uint32_t preg[16];
+    f32x2 bias2 = pk2(fmaf(slope, float(c * 32), base), fmaf(slope, float(c * 32 + 1), base));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const f32x2 s2 = fma2(pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), scale2, bias2);
+      bias2 = add2(bias2, step2);
+      f32x2 r2, w2;
+      if (i % 4 == 0) sigma_terms2<true>(s2, half2, r2, w2); else sigma_terms2<false>(s2, half2, r2, w2);
+      const f32x2 q2 = mul2(w2, w2);
+      f32x2 f2 = mul2(q2, q2);                               // (2 sigma)^4 = 16 sigma^4
+      float f0, f1;
+      upk2(f2, f0, f1);
+      if (MASK) {
+        if (c * 32 + 2 * i > r) f0 = 0.f;
+        if (c * 32 + 2 * i + 1 > r) f1 = 0.f;
+        f2 = pk2(f0, f1);
+      }
+      l2 = add2(l2, f2);
+      preg[i] = Pack16<T>::pack(f0, f1);
+    }
+    if (c + 1 < BLK / 32) tmem_ld32(trow + (c + 1) * 32, sreg);      // next chunk in flight while this one is stored
+    tmem_st16(trow + c * 16, preg);
+  }
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
@@ -53,6 +91,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
   for (int t = 0; t < 2; ++t) n_tiles[t] = (2 * qb + t) * BLK < p.T ? min(2 * qb + t + 1, n_kv_total) : 0;
   const int n_max = max(n_tiles[0], n_tiles[1]);
   Guard g{&sm.abort_flag, p.status};
+  FAT_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -90,20 +129,12 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     if (elect_one()) {
       constexpr uint32_t idesc_qk = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
       constexpr uint32_t idesc_pv = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
-      auto issue_qk = [&](int t, int st) {            // S_t = Q_t K^T
-        const uint32_t qa = smem_u32(sm.q[t]), ka = smem_u32(sm.k[st]);
-#pragma unroll
-        for (int s = 0; s < D / 16; ++s) {
-          const uint32_t off = (s / 4) * (BLK * 128) + (s % 4) * 32;
-          mma_ss(tmem + t * BLK, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), idesc_qk, s > 0);
-        }
-      };
-      auto issue_pv = [&](int t, int st, bool first) { // O_t += P_t V
-        const uint32_t va = smem_u32(sm.v[st]);
-#pragma unroll
-        for (int s = 0; s < BLK / 16; ++s)
-          mma_ts(tmem + 2 * BLK + t * D, tmem + t * BLK + s * 8, smem_desc_sw128(va + s * 2048, BLK * 128, 1024), idesc_pv,
-                 !(first && s == 0));
+      const uint64_t qd[2] = {desc_kmajor(sm.q[0]), desc_kmajor(sm.q[1])};
+      const uint64_t kd[kStages] = {desc_kmajor(sm.k[0]), desc_kmajor(sm.k[1])};
+      const uint64_t vd[kStages] = {desc_mnmajor(sm.v[0]), desc_mnmajor(sm.v[1])};
+      auto issue_qk = [&](int t, int st) { issue_gemm_nt<D>(tmem + t * BLK, qd[t], kd[st], idesc_qk); };          // S_t = Q_t K^T
+      auto issue_pv = [&](int t, int st, bool first) {                                                           // O_t += P_t V
+        issue_gemm_tn<false>(tmem + 2 * BLK + t * D, tmem + t * BLK, vd[st], idesc_pv, !first);
       };
       bool ok = true;
       // prologue: scores of key tile 0 for both query tiles
@@ -123,8 +154,10 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
         bool k_next_ready = false;
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_tiles[t]) continue;
+          TR_BEGIN();
           if (!(ok = g.wait(&sm.p_full[t], j & 1, 22))) break;
           if (!(ok = g.wait(&sm.v_full[st], ph, 23))) break;
+          TR_WAITED();
           tc_fence_after();
           issue_pv(t, st, j == 0);
           if (j + 1 < n_tiles[t]) {
@@ -139,6 +172,9 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
         mma_commit(&sm.v_empty[st]);                       // V(j) and, if it was read, K(j+1) are free once these finish
         if (j + 1 < n_max) mma_commit(&sm.k_empty[st1]);
       }
+#ifdef FAT_TRACE
+      if (traced) { trace[0] = tr_wait; trace[1] = clock64() - tr_t0; trace[2] = n_max; }
+#endif
     }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
@@ -149,46 +185,38 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     const float slope = p.slopes[h];
     const float scale = p.scale;
     const int n = n_tiles[t];
-    float l_sum = 0.f;
+    f32x2 l2 = pk2(0.f, 0.f);
+    const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(2.f * slope, 2.f * slope);
     bool ok = true;
     for (int j = 0; j < n; ++j) {
+      TR_BEGIN();
       if (!(ok = g.wait(&sm.s_full[t], j & 1, 30))) break;
+      TR_WAITED();
       tc_fence_after();
-      const int k0 = j * BLK;
-      const float base = slope * float(k0 - row);            // bias of column 0 of this tile: -slope*(row-k0)
+      const float base = slope * float(j * BLK - row);       // bias of column 0 of this tile: -slope*(row-k0)
       const bool diag = (j == 2 * qb + t);
-#pragma unroll
-      for (int c = 0; c < BLK / 32; ++c) {
-        uint32_t sreg[32], preg[16];
-        tmem_ld32(tmem_addr(tmem, lane_base, t * BLK + c * 32), sreg);
-        tmem_wait_ld();
-        float f[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c * 32 + i;
-          const float s = fmaf(__uint_as_float(sreg[i]), scale, fmaf(slope, float(col), base));
-          f[i] = sigma4(s);
-        }
-        if (diag) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) if (c * 32 + i > r) f[i] = 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) l_sum += f[i];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) preg[i] = Pack16<T>::pack(f[2 * i], f[2 * i + 1]);
-        tmem_st16(tmem_addr(tmem, lane_base, t * BLK + c * 16), preg);
-      }
+      if (diag) softmax_tile<T, true>(tmem_addr(tmem, lane_base, t * BLK), r, scale2, half2, step2, slope, base, l2);
+      else      softmax_tile<T, false>(tmem_addr(tmem, lane_base, t * BLK), r, scale2, half2, step2, slope, base, l2);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full[t]);
+      TR_WORKED();
+    }
+#ifdef FAT_TRACE
+    if (traced && r == 0) { trace[4 + 4 * t] = tr_wait; trace[5 + 4 * t] = tr_work; trace[6 + 4 * t] = clock64() - tr_t0; trace[7 + 4 * t] = n; }
+#endif
+    float l_sum;
+    {
+      float la, lb;
+      upk2(l2, la, lb);
+      l_sum = (la + lb) * 0.0625f;                             // back to sum of sigma^4
     }
     if (ok && n > 0) ok = g.wait(&sm.o_full[t], 0, 31);
     named_barrier(1 + t, BLK);                               // reached by all 128 threads, aborted or not
     if (n > 0 && !g.aborted()) {
       // -------------------------------------------------------------- epilogue: O / (L + eps), hi + residual
       tc_fence_after();
-      const float inv = 1.0f / (l_sum + p.eps);
+      const float inv = 0.0625f / (l_sum + p.eps);             // the accumulator holds 16 sigma^4 V
       if (row < p.T) p.L[(int64_t(b) * p.H + h) * p.T + row] = l_sum;
       unsigned char* stage = sm.q[t];
       const bool want_lo = p.out_lo != nullptr;

@@ -29,20 +29,23 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// One try: the hardware parks the thread until the phase completes or about `kWaitHintNs` pass, so a
+// waiting warp does not compete for issue slots with the warps that are doing arithmetic.
+constexpr uint32_t kWaitHintNs = 100000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitHintNs) : "memory");
   return ok != 0;
 }
 
 // Every wait in these kernels is bounded.  When the bound is hit the kernel records a status
 // word, raises a CTA-wide abort flag that makes all later waits fall through, and runs to
 // its normal teardown (TMEM is released, the launch ends, the context stays usable).
-constexpr uint32_t kWaitSpins = 1u << 24;
+constexpr uint32_t kWaitSpins = 1u << 15;      // x kWaitHintNs: a few seconds at most
 
 struct Guard {
   volatile int* abort_flag;   // shared memory, zeroed at kernel start
@@ -56,7 +59,7 @@ struct Guard {
   __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, int where) const {
     for (uint32_t i = 0; i < kWaitSpins; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
-      if ((i & 1023u) == 1023u && aborted()) return false;
+      if (aborted()) return false;
     }
     fail(where);
     return false;
