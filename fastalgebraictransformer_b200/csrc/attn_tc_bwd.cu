@@ -25,7 +25,12 @@ using namespace tcattn;
 constexpr float kOpScale = 256.0f;       // applied to p (<= 1) and dS (|dS| stays far below 65504/256); the prepare
                                          // kernel folds it into the per-row normaliser it writes
 
-constexpr int kBwdThreads = 320;         // warps 0-7: element-wise (2 warpgroups), warp 8: TMA, warp 9: MMA
+constexpr int kEwGroups = 2;                          // element-wise warpgroups per CTA
+constexpr int kEwThreads = 128 * kEwGroups;
+constexpr int kColsPerGroup = BLK / kEwGroups;        // score columns owned by one warpgroup
+constexpr int kChunks = kColsPerGroup / 32;           // 32-column chunks per thread and phase
+constexpr int kTmaWarp = 4 * kEwGroups, kMmaWarp = kTmaWarp + 1;
+constexpr int kBwdThreads = kEwThreads + 64;          // + one TMA producer warp + one MMA issuer warp
 constexpr int kBwdStages = 2;
 
 __host__ __device__ inline int64_t pad_rows(int T) { return int64_t((T + BLK - 1) / BLK) * BLK; }
@@ -89,11 +94,8 @@ __device__ __forceinline__ void score_fg2(f32x2 acc2, f32x2 scale2, f32x2 bias2,
 }
 
 // TMEM column (relative to the start of a 128-column region) where warpgroup w keeps its packed
-// 16-bit results: elements [64w, 64w+64) live in columns [64w, 64w+32), inside the fp32 columns
-// that only this warpgroup reads.
-__device__ __forceinline__ uint32_t packed_col(int w, int chunk16) { return uint32_t(64 * w + 16 * chunk16); }
-// TMEM column of the A operand of K-step s (16 elements = 8 packed columns) for such a region.
-__device__ __forceinline__ uint32_t packed_kstep_col(int s) { return uint32_t((s / 4) * 64 + (s % 4) * 8); }
+// 16-bit results: its elements live in the first half of the fp32 columns that only this warpgroup reads.
+__device__ __forceinline__ uint32_t packed_col(int w, int chunk16) { return uint32_t(kColsPerGroup * w + 16 * chunk16); }
 
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -155,21 +157,21 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
 
   if (tid == 0) {
     sm.abort_flag = 0;
-    mbar_init(&sm.qdo_full, 1); mbar_init(&sm.s_full, 1); mbar_init(&sm.s_free, 256);
-    mbar_init(&sm.dp_full, 1); mbar_init(&sm.ds_full, 256); mbar_init(&sm.dq_full, 1);
+    mbar_init(&sm.qdo_full, 1); mbar_init(&sm.s_full, 1); mbar_init(&sm.s_free, kEwThreads);
+    mbar_init(&sm.dp_full, 1); mbar_init(&sm.ds_full, kEwThreads); mbar_init(&sm.dq_full, 1);
     for (int i = 0; i < kBwdStages; ++i) {
       mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1);
     }
     mbar_fence_init();
   }
-  if (warp == 8) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
+  if (warp == kTmaWarp) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const uint32_t tS = tmem, tP = tmem + BLK, tQ = tmem + 2 * BLK;
 
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     if (elect_one()) {
       mbar_expect_tx(&sm.qdo_full, 2 * S::kTileBytes);
       load_tile_tma_noexpect<D>(sm.q, &maps.q, &sm.qdo_full, qt * BLK, h, b);
@@ -183,7 +185,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
         load_tile_tma<D>(sm.v[st], &maps.v, &sm.v_full[st], j * BLK, h, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
       constexpr uint32_t idesc_dq = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
@@ -207,7 +209,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
         }
         if (!(ok = g.wait(&sm.ds_full, j & 1, 55))) break;
         tc_fence_after();
-        issue_gemm_tn<true>(tQ, tP, kd_mn[st], idesc_dq, j > 0);       // dQ += dS K
+        issue_gemm_tn<kColsPerGroup>(tQ, tP, kd_mn[st], idesc_dq, j > 0);       // dQ += dS K
         mma_commit(&sm.k_empty[st]);
         if (j + 1 < n) {
           if (!(ok = g.wait(&sm.v_full[st1], ph1, 56))) break;
@@ -220,7 +222,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       if (ok) mma_commit(&sm.dq_full);
     }
   } else {
-    const int w = warp >> 2;                                 // column half of this warpgroup
+    const int w = warp >> 2;                                 // column slice of this warpgroup
     const int r = tid & (BLK - 1);                           // query row inside the tile == TMEM lane
     const int row = qt * BLK + r;
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
@@ -232,7 +234,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
     const f32x2 ndlt2 = pk2(-dlt, -dlt);
     bool ok = true;
     for (int j = 0; j < n; ++j) {
-      f32x2 gq[32];
+      f32x2 gq[kColsPerGroup / 2];
       // ---- phase A: g = sigma^3 r^2 / (L+eps) from the scores
       TR_BEGIN();
       if (!(ok = g.wait(&sm.s_full, j & 1, 60))) break;
@@ -240,11 +242,11 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       tc_fence_after();
       const float base = slope * float(j * BLK - row);       // bias of key column 0 of this tile
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t sreg[32];
-        tmem_ld32(tmem_addr(tS, lane_base, 64 * w + 32 * c), sreg);
+        tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
         tmem_wait_ld_regs(sreg);
-        const int col0 = 64 * w + 32 * c;
+        const int col0 = kColsPerGroup * w + 32 * c;
         f32x2 bias2 = pk2(fmaf(slope, float(col0), base), fmaf(slope, float(col0 + 1), base));
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -265,9 +267,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       tc_fence_after();
       const bool diag = (j == qt);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t dreg[32], preg[16];
-        tmem_ld32(tmem_addr(tP, lane_base, 64 * w + 32 * c), dreg);
+        tmem_ld32(tmem_addr(tP, lane_base, kColsPerGroup * w + 32 * c), dreg);
         tmem_wait_ld_regs(dreg);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -275,8 +277,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
           float d0, d1;
           upk2(ds2, d0, d1);
           if (diag) {
-            if (64 * w + 32 * c + 2 * i > r) d0 = 0.f;
-            if (64 * w + 32 * c + 2 * i + 1 > r) d1 = 0.f;
+            if (kColsPerGroup * w + 32 * c + 2 * i > r) d0 = 0.f;
+            if (kColsPerGroup * w + 32 * c + 2 * i + 1 > r) d1 = 0.f;
           }
           preg[i] = Pack16<T>::pack(d0, d1);
         }
@@ -288,23 +290,21 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       TR_WORKED2();
     }
 #ifdef FAT_TRACE
-    if (traced && (tid & 127) == 0) { long long* o = trace + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
+    if (traced && (tid & 127) == 0 && tid < 256) { long long* o = trace + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
 #endif
     if (ok) ok = g.wait(&sm.dq_full, 0, 62);
-    named_barrier(1, 256);
+    named_barrier(1, kEwThreads);
     if (!g.aborted()) {
       tc_fence_after();
       const float mul = 0.25f * scale * ginv / kOpScale;        // 2 (derivative) / 8 (g8 units) * scale / (L+eps)
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {                     // warpgroup w stores columns [w*D/2, (w+1)*D/2)
+      for (int col0 = 32 * w; col0 < D; col0 += 32 * kEwGroups) {   // warpgroups interleave 32-column chunks of d_q
         uint32_t oreg[32];
-        const int col0 = w * (D / 2) + c * 32;
         tmem_ld32(tmem_addr(tQ, lane_base, col0), oreg);
-        tmem_wait_ld();
+        tmem_wait_ld_regs(oreg);
         stage_row32<T>(sm.q, r, col0, oreg, mul);
       }
       fence_async_smem();
-      named_barrier(1, 256);
+      named_barrier(1, kEwThreads);
       if (tid == 0) {
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) tma_store_4d(&maps.dq, sm.q + c * (BLK * 128), c * 64, qt * BLK, h, b);
@@ -315,7 +315,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem, kTmemCols);
+  if (warp == kTmaWarp) tmem_dealloc(tmem, kTmemCols);
 }
 
 // ------------------------------------------------------------------------------------- 3. d_k / d_v kernel
@@ -353,21 +353,21 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
 
   if (tid == 0) {
     sm.abort_flag = 0;
-    mbar_init(&sm.kv_full, 1); mbar_init(&sm.s_full, 1); mbar_init(&sm.p_full, 256);
-    mbar_init(&sm.dp_full, 1); mbar_init(&sm.ds_full, 256); mbar_init(&sm.acc_full, 1);
+    mbar_init(&sm.kv_full, 1); mbar_init(&sm.s_full, 1); mbar_init(&sm.p_full, kEwThreads);
+    mbar_init(&sm.dp_full, 1); mbar_init(&sm.ds_full, kEwThreads); mbar_init(&sm.acc_full, 1);
     for (int i = 0; i < kBwdStages; ++i) {
       mbar_init(&sm.q_full[i], 1); mbar_init(&sm.q_empty[i], 1); mbar_init(&sm.do_full[i], 1); mbar_init(&sm.do_empty[i], 1);
     }
     mbar_fence_init();
   }
-  if (warp == 8) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
+  if (warp == kTmaWarp) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const uint32_t tS = tmem, tP = tmem + BLK, tV = tmem + 2 * BLK, tK = tmem + 2 * BLK + D;
 
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     if (elect_one()) {
       mbar_expect_tx(&sm.kv_full, 2 * S::kTileBytes);
       load_tile_tma_noexpect<D>(sm.k, &maps.k, &sm.kv_full, kt * BLK, h, b);
@@ -386,7 +386,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
         load_tile_tma<D>(sm.dout[st], &maps.dout, &sm.do_full[st], qi * BLK, h, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
       constexpr uint32_t idesc_acc = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
@@ -404,7 +404,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
         const uint32_t ph1 = ((it + 1) / kBwdStages) & 1;
         if (!(ok = g.wait(&sm.p_full, it & 1, 83))) break;
         tc_fence_after();
-        issue_gemm_tn<true>(tV, tS, dod_mn[st], idesc_acc, it > 0);     // dV += P^T dO
+        issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn[st], idesc_acc, it > 0);     // dV += P^T dO
         mma_commit(&sm.do_empty[st]);
         if (it + 1 < n) {
           if (!(ok = g.wait(&sm.q_full[st1], ph1, 84))) break;
@@ -414,7 +414,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
         }
         if (!(ok = g.wait(&sm.ds_full, it & 1, 85))) break;
         tc_fence_after();
-        issue_gemm_tn<true>(tK, tP, qd_mn[st], idesc_acc, it > 0);      // dK += dS^T Q
+        issue_gemm_tn<kColsPerGroup>(tK, tP, qd_mn[st], idesc_acc, it > 0);      // dK += dS^T Q
         mma_commit(&sm.q_empty[st]);
         if (it + 1 < n) {
           if (!(ok = g.wait(&sm.do_full[st1], ph1, 86))) break;
@@ -426,7 +426,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       if (ok) mma_commit(&sm.acc_full);
     }
   } else {
-    const int w = warp >> 2;                                 // query-column half of this warpgroup
+    const int w = warp >> 2;                                 // query-column slice of this warpgroup
     const int r = tid & (BLK - 1);                           // key row inside the tile == TMEM lane
     const int key = kt * BLK + r;
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
@@ -436,7 +436,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
     for (int it = 0; it < n; ++it) {
       const int st = it % kBwdStages, qi = kt + it;
       const bool diag = (it == 0);
-      f32x2 gq[32];
+      f32x2 gq[kColsPerGroup / 2];
       // ---- phase A: p = sigma^4 / (L+eps) -> packed P^T over S^T; g / (L+eps) kept in registers
       TR_BEGIN();
       if (!(ok = g.wait(&sm.q_full[st], (it / kBwdStages) & 1, 93))) break;       // Delta / inv arrived with the Q tile
@@ -446,11 +446,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       const float base = slope * float(key - qi * BLK);      // bias of query column 0: -slope*(q-key)
       const float* iv = sm.inv[st];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t sreg[32], preg[16];
-        tmem_ld32(tmem_addr(tS, lane_base, 64 * w + 32 * c), sreg);
+        tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
         tmem_wait_ld_regs(sreg);
-        const int col0 = 64 * w + 32 * c;
+        const int col0 = kColsPerGroup * w + 32 * c;
         f32x2 bias2 = pk2(fmaf(-slope, float(col0), base), fmaf(-slope, float(col0 + 1), base));
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -487,13 +487,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       tc_fence_after();
       const float* dl = sm.delta[st];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t dreg[32], preg[16];
-        tmem_ld32(tmem_addr(tP, lane_base, 64 * w + 32 * c), dreg);
+        tmem_ld32(tmem_addr(tP, lane_base, kColsPerGroup * w + 32 * c), dreg);
         tmem_wait_ld_regs(dreg);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float2 d2 = *reinterpret_cast<const float2*>(dl + 64 * w + 32 * c + 2 * i);
+          const float2 d2 = *reinterpret_cast<const float2*>(dl + kColsPerGroup * w + 32 * c + 2 * i);
           const f32x2 ds2 = mul2(gq[16 * c + i], add2(pk2(__uint_as_float(dreg[2 * i]), __uint_as_float(dreg[2 * i + 1])), pk2(-d2.x, -d2.y)));
           float d0, d1;
           upk2(ds2, d0, d1);
@@ -507,29 +507,30 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       TR_WORKED2();
     }
 #ifdef FAT_TRACE
-    if (traced && (tid & 127) == 0) { long long* o = trace + 16 + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
+    if (traced && (tid & 127) == 0 && tid < 256) { long long* o = trace + 16 + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
 #endif
     if (ok) ok = g.wait(&sm.acc_full, 0, 92);
-    named_barrier(1, 256);
+    named_barrier(1, kEwThreads);
     if (!g.aborted()) {
-      // warpgroup 0 stores d_v, warpgroup 1 stores d_k (scaled by 2*scale)
+      // d_v (columns [0,D) of the accumulators) is staged in q[0], d_k (columns [D,2D)) in q[1]; the
+      // warpgroups interleave 32-column chunks.  The multipliers undo the 16x (F16) and 8x (g8) units.
       tc_fence_after();
-      unsigned char* stage = sm.q[w];
-      const float mul = w == 0 ? 0.0625f / kOpScale : 0.25f * scale / kOpScale;    // undo the 16x (F16) and 8x (g8) units
-      const uint32_t src = w == 0 ? tV : tK;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int ch = w; ch < 2 * D / 32; ch += kEwGroups) {
+        const bool is_dk = ch >= D / 32;
+        const int col0 = (is_dk ? ch - D / 32 : ch) * 32;
         uint32_t oreg[32];
-        tmem_ld32(tmem_addr(src, lane_base, c * 32), oreg);
-        tmem_wait_ld();
-        stage_row32<T>(stage, r, c * 32, oreg, mul);
+        tmem_ld32(tmem_addr(is_dk ? tK : tV, lane_base, col0), oreg);
+        tmem_wait_ld_regs(oreg);
+        stage_row32<T>(sm.q[is_dk ? 1 : 0], r, col0, oreg, is_dk ? 0.25f * scale / kOpScale : 0.0625f / kOpScale);
       }
       fence_async_smem();
-      named_barrier(2 + w, BLK);
-      if (r == 0) {
-        const CUtensorMap* m = w == 0 ? &maps.dv : &maps.dk;
+      named_barrier(1, kEwThreads);
+      if (tid == 0) {
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) tma_store_4d(m, stage + c * (BLK * 128), c * 64, kt * BLK, h, b);
+        for (int c = 0; c < D / 64; ++c) {
+          tma_store_4d(&maps.dv, sm.q[0] + c * (BLK * 128), c * 64, kt * BLK, h, b);
+          tma_store_4d(&maps.dk, sm.q[1] + c * (BLK * 128), c * 64, kt * BLK, h, b);
+        }
         tma_store_commit();
         tma_store_wait_all();
       }
@@ -537,7 +538,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem, kTmemCols);
+  if (warp == kTmaWarp) tmem_dealloc(tmem, kTmemCols);
 }
 
 

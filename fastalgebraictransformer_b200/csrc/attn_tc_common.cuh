@@ -80,12 +80,13 @@ __device__ __forceinline__ void issue_gemm_nt(uint32_t d_tmem, uint64_t adesc, u
 }
 
 // acc[128 x N] (+)= A B with A in TMEM (128 x 128, packed 16-bit) and B an MN-major [128][N] tile.
-// SPLIT: A is stored as two 32-column halves 64 columns apart (one per element-wise warpgroup).
-template <bool SPLIT>
+// CW: the packed A is stored in pieces, one per element-wise warpgroup: elements [CW*w, CW*w+CW) occupy the
+// CW/2 columns that start at column CW*w (CW = 128: one contiguous run of 64 columns).
+template <int CW>
 __device__ __forceinline__ void issue_gemm_tn(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int s = 0; s < BLK / 16; ++s) {
-    const uint32_t acol = SPLIT ? uint32_t((s / 4) * 64 + (s % 4) * 8) : uint32_t(s * 8);
+    const uint32_t acol = uint32_t(CW * ((16 * s) / CW) + ((16 * s) % CW) / 2);
     mma_ts(d_tmem, a_tmem + acol, bdesc + ((s * 2048) >> 4), idesc, accumulate || s > 0);
   }
 }

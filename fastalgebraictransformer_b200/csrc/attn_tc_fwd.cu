@@ -134,7 +134,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       const uint64_t vd[kStages] = {desc_mnmajor(sm.v[0]), desc_mnmajor(sm.v[1])};
       auto issue_qk = [&](int t, int st) { issue_gemm_nt<D>(tmem + t * BLK, qd[t], kd[st], idesc_qk); };          // S_t = Q_t K^T
       auto issue_pv = [&](int t, int st, bool first) {                                                           // O_t += P_t V
-        issue_gemm_tn<false>(tmem + 2 * BLK + t * D, tmem + t * BLK, vd[st], idesc_pv, !first);
+        issue_gemm_tn<BLK>(tmem + 2 * BLK + t * D, tmem + t * BLK, vd[st], idesc_pv, !first);
       };
       bool ok = true;
       // prologue: scores of key tile 0 for both query tiles
