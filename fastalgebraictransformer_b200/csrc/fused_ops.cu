@@ -16,6 +16,18 @@
 namespace fat {
 namespace {
 
+// Launch-shape constants (blocks per SM that the grids are sized for, 16-byte loads in flight per thread
+// and tensor); the values were picked by sweeping them on a B200.
+#ifndef FAT_NORM_FWD_BPS
+#define FAT_NORM_FWD_BPS 8
+#define FAT_NORM_FWD_PPT 2
+#define FAT_NORM_BWD_BPS 2
+#define FAT_NORM_BWD_PPT 2
+#define FAT_SOFTMAX_BPS 6
+#define FAT_SOFTMAX_PPT 4
+#define FAT_SWIGLU_BPS 24
+#endif
+
 constexpr int kThreads = 256;
 constexpr int kMaxVPT = 8;
 constexpr int kNormBwdMaxBlocks = 4 * kNumSM;   // rows of the d_weight partial-sum scratch
@@ -27,15 +39,15 @@ constexpr int kMaxDevices = 64;
 
 // ------------------------------------------------------------------ group reduction
 // Sums NV values over the G threads (G = 32..256, power of two) that share a row.
-// `buf` is shared memory of 2*8*NV values; `phase` alternates the half in use so that one
+// `buf` is shared memory of 2*(NT/32)*NV values; `phase` alternates the half in use so that one
 // __syncthreads per call suffices.  Every thread of the block must call it.
-template <typename C, int NV>
+template <typename C, int NV, int NT = 256>
 __device__ __forceinline__ void group_sum(C (&v)[NV], int G, C* buf, int& phase) {
 #pragma unroll
   for (int n = 0; n < NV; ++n) v[n] = warp_sum(v[n]);
   if (G > 32) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    C* b = buf + phase * (kThreads / 32) * NV;
+    C* b = buf + phase * (NT / 32) * NV;
     if (lane == 0) {
 #pragma unroll
       for (int n = 0; n < NV; ++n) b[warp * NV + n] = v[n];
@@ -108,10 +120,34 @@ swiglu_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ gate, const
 // =====================================================================================
 // Register-resident row kernels (fast path)
 // =====================================================================================
+// The packs of one row as they come from memory.  Rows are fetched one iteration ahead: the loads of
+// the next row are issued before the current row's reduction (which ends in a block-wide barrier), so
+// memory stays busy across the barrier.
+template <typename T, int VPT>
+struct RawRow {
+  static constexpr int W = 16 / sizeof(T);
+  uint4 v[VPT];
+  __device__ __forceinline__ void fetch(const T* row, int t, int G, int npk, bool ok) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int pk = t + i * G;
+      v[i] = (ok && pk < npk) ? __ldcs(reinterpret_cast<const uint4*>(row + int64_t(pk) * W)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+};
+
 template <typename T, int W, int VPT>
 struct RowRegs {
   using C = typename Elem<T>::C;
   C v[VPT][W];
+  __device__ __forceinline__ void from_raw(const RawRow<T, VPT>& raw) {     // all-zero bits are 0.0 in every element type
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const T* e = reinterpret_cast<const T*>(&raw.v[i]);
+#pragma unroll
+      for (int j = 0; j < W; ++j) v[i][j] = Elem<T>::to_c(e[j]);
+    }
+  }
   __device__ __forceinline__ void load(const T* row, int t, int G, int npk, bool ok) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -141,11 +177,15 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ weight, T* __rest
     const int pk = t + i * G;
     if (pk < npk) load_pack_cached<T, W>(weight + int64_t(pk) * W, w[i]);
   }
+  const int64_t row_step = int64_t(gridDim.x) * rpc, first_row = int64_t(blockIdx.x) * rpc + g;
+  RawRow<T, VPT> next_x;
+  next_x.fetch(x + first_row * xs, t, G, npk, first_row < n_rows);
   for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += int64_t(gridDim.x) * rpc) {
     const int64_t row = row0 + g;
     const bool ok = row < n_rows;
     RowRegs<T, W, VPT> xr;
-    xr.load(x + row * xs, t, G, npk, ok);
+    xr.from_raw(next_x);
+    next_x.fetch(x + (row + row_step) * xs, t, G, npk, row + row_step < n_rows);
     C s[1] = {C(0)};
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
@@ -171,91 +211,80 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ weight, T* __rest
 }
 
 // d_x for every row, plus this block's partial column sums of d_out * x / mu into
-// partial[blockIdx.x][0..n_cols) (compute type).  dyn smem: (256/G) * n_cols values when
-// several rows share a block.
-template <typename T, int W, int VPT>
-__global__ void __launch_bounds__(kThreads)
+// partial[blockIdx.x][0..n_cols) (compute type).  To leave registers for rows in flight the weight stays
+// packed (converted where used) and the running column sums live in thread-private shared-memory slots.
+// dyn smem: NT * VPT * W values.
+template <typename T, int W, int VPT, int NT>
+__global__ void __launch_bounds__(NT)
 norm_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ x, const T* __restrict__ weight,
                 const float* __restrict__ mean, T* __restrict__ d_x,
                 typename Elem<T>::C* __restrict__ partial,
                 int64_t n_rows, int n_cols, int64_t dos, int64_t xs, int64_t dxs,
                 double eps_d, int G) {
   using C = typename Elem<T>::C;
-  __shared__ C red[2 * (kThreads / 32)];
+  __shared__ C red[2 * (NT / 32)];
   extern __shared__ __align__(16) unsigned char dyn_smem[];
+  C* acc_sm = reinterpret_cast<C*>(dyn_smem);            // slot (i, j) of thread tid: acc_sm[(i * W + j) * NT + tid]
   int phase = 0;
-  const int npk = n_cols / W, rpc = kThreads / G, g = threadIdx.x / G, t = threadIdx.x % G;
+  const int npk = n_cols / W, rpc = NT / G, g = threadIdx.x / G, t = threadIdx.x % G;
   const C eps = C(eps_d);
-  C w[VPT][W], acc[VPT][W];
+  RawRow<T, VPT> wraw;
+  wraw.fetch(weight, t, G, npk, true);
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int pk = t + i * G;
-    if (pk < npk) load_pack_cached<T, W>(weight + int64_t(pk) * W, w[i]);
-#pragma unroll
-    for (int j = 0; j < W; ++j) acc[i][j] = C(0);
-  }
+  for (int i = 0; i < VPT * W; ++i) acc_sm[i * NT + threadIdx.x] = C(0);
+  const int64_t row_step = int64_t(gridDim.x) * rpc, first_row = int64_t(blockIdx.x) * rpc + g;
+  RawRow<T, VPT> next_x;
+  next_x.fetch(x + first_row * xs, t, G, npk, first_row < n_rows);
+  RawRow<T, VPT> next_g;
+  next_g.fetch(d_out + first_row * dos, t, G, npk, first_row < n_rows);
+  float next_mean = first_row < n_rows ? __ldg(mean + first_row) : 0.f;       // fetched a row ahead like the packs
   for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += int64_t(gridDim.x) * rpc) {
     const int64_t row = row0 + g;
     const bool ok = row < n_rows;
-    RowRegs<T, W, VPT> xr, gr;
-    xr.load(x + row * xs, t, G, npk, ok);
-    gr.load(d_out + row * dos, t, G, npk, ok);
-    const C inv = ok ? C(1) / (C(mean[row]) + eps) : C(0);
+    RowRegs<T, W, VPT> xr;
+    xr.from_raw(next_x);
+    next_x.fetch(x + (row + row_step) * xs, t, G, npk, row + row_step < n_rows);
+    RowRegs<T, W, VPT> gr;
+    gr.from_raw(next_g);
+    next_g.fetch(d_out + (row + row_step) * dos, t, G, npk, row + row_step < n_rows);
+    const C inv = ok ? C(1) / (C(next_mean) + eps) : C(0);
+    next_mean = row + row_step < n_rows ? __ldg(mean + row + row_step) : 0.f;
     C s[1] = {C(0)};
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      if (t + i * G < npk) {
+      const T* we = reinterpret_cast<const T*>(&wraw.v[i]);
 #pragma unroll
-        for (int j = 0; j < W; ++j) {
-          const C gxn = gr.v[i][j] * (xr.v[i][j] * inv);      // d_out * x / mu
-          acc[i][j] += gxn;
-          s[0] += gxn * w[i][j];
-        }
+      for (int j = 0; j < W; ++j) {
+        const C gxn = gr.v[i][j] * (xr.v[i][j] * inv);      // d_out * x / mu  (0 beyond the row: zero packs)
+        acc_sm[(i * W + j) * NT + threadIdx.x] += gxn;
+        s[0] += gxn * Elem<T>::to_c(we[j]);
       }
     }
-    group_sum<C, 1>(s, G, red, phase);
+    group_sum<C, 1, NT>(s, G, red, phase);
     const C corr = s[0] / C(n_cols) * inv;
     if (ok) {
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int pk = t + i * G;
         if (pk < npk) {
+          const T* we = reinterpret_cast<const T*>(&wraw.v[i]);
           C o[W];
 #pragma unroll
           for (int j = 0; j < W; ++j)
-            o[j] = gr.v[i][j] * w[i][j] * inv - sgn(xr.v[i][j]) * corr;
+            o[j] = gr.v[i][j] * Elem<T>::to_c(we[j]) * inv - sgn(xr.v[i][j]) * corr;
           store_pack<T, W>(d_x + row * dxs + int64_t(pk) * W, o);
         }
       }
     }
   }
-  // fold the row groups of this block, then publish the block's partial sums
+  // fold the row groups of this block and publish the block's partial sums
   C* prow = partial + int64_t(blockIdx.x) * n_cols;
-  if (rpc == 1) {
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int pk = t + i * G;
-      if (pk < npk) {
-#pragma unroll
-        for (int j = 0; j < W; ++j) prow[pk * W + j] = acc[i][j];
-      }
-    }
-  } else {
-    C* sm = reinterpret_cast<C*>(dyn_smem);
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int pk = t + i * G;
-      if (pk < npk) {
-#pragma unroll
-        for (int j = 0; j < W; ++j) sm[g * n_cols + pk * W + j] = acc[i][j];
-      }
-    }
-    __syncthreads();
-    for (int c = threadIdx.x; c < n_cols; c += kThreads) {
-      C s = C(0);
-      for (int r = 0; r < rpc; ++r) s += sm[r * n_cols + c];
-      prow[c] = s;
-    }
+  __syncthreads();
+  for (int c = threadIdx.x; c < n_cols; c += NT) {
+    const int pk = c / W, j = c % W, i = pk / G, tt = pk % G;
+    C sum = C(0);
+    for (int r = 0; r < rpc; ++r) sum += acc_sm[(i * W + j) * NT + r * G + tt];
+    prow[c] = sum;
   }
 }
 
@@ -269,8 +298,10 @@ norm_bwd_reduce_kernel(const typename Elem<T>::C* __restrict__ partial, T* __res
   const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + lane;
   C s = C(0);
-  if (c < n_cols)
+  if (c < n_cols) {
+#pragma unroll 4
     for (int r = slice; r < n_part; r += 8) s += partial[int64_t(r) * n_cols + c];
+  }
   sm[slice][lane] = s;
   __syncthreads();
   if (slice == 0 && c < n_cols) {
@@ -289,11 +320,15 @@ softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ p, int64_t n_rows, i
   int phase = 0;
   const int npk = n_cols / W, rpc = kThreads / G, g = threadIdx.x / G, t = threadIdx.x % G;
   const C eps = C(eps_d);
+  const int64_t row_step = int64_t(gridDim.x) * rpc, first_row = int64_t(blockIdx.x) * rpc + g;
+  RawRow<T, VPT> next_x;
+  next_x.fetch(x + first_row * xs, t, G, npk, first_row < n_rows);
   for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += int64_t(gridDim.x) * rpc) {
     const int64_t row = row0 + g;
     const bool ok = row < n_rows;
     RowRegs<T, W, VPT> xr;
-    xr.load(x + row * xs, t, G, npk, ok);
+    xr.from_raw(next_x);
+    next_x.fetch(x + (row + row_step) * xs, t, G, npk, row + row_step < n_rows);
     C s[1] = {C(0)};
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -335,12 +370,20 @@ softmax_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ x, T* __re
   int phase = 0;
   const int npk = n_cols / W, rpc = kThreads / G, g = threadIdx.x / G, t = threadIdx.x % G;
   const C eps = C(eps_d);
+  const int64_t row_step = int64_t(gridDim.x) * rpc, first_row = int64_t(blockIdx.x) * rpc + g;
+  RawRow<T, VPT> next_x;
+  next_x.fetch(x + first_row * xs, t, G, npk, first_row < n_rows);
+  RawRow<T, VPT> next_g;
+  next_g.fetch(d_out + first_row * dos, t, G, npk, first_row < n_rows);
   for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += int64_t(gridDim.x) * rpc) {
     const int64_t row = row0 + g;
     const bool ok = row < n_rows;
-    RowRegs<T, W, VPT> xr, gr;
-    xr.load(x + row * xs, t, G, npk, ok);
-    gr.load(d_out + row * dos, t, G, npk, ok);
+    RowRegs<T, W, VPT> xr;
+    xr.from_raw(next_x);
+    next_x.fetch(x + (row + row_step) * xs, t, G, npk, row + row_step < n_rows);
+    RowRegs<T, W, VPT> gr;
+    gr.from_raw(next_g);
+    next_g.fetch(d_out + (row + row_step) * dos, t, G, npk, row + row_step < n_rows);
     // after this loop xr holds k = 2 sigma^3 r^2 (the un-normalised derivative factor)
     C s[2] = {C(0), C(0)};                 // Z = sum sigma^4 ; sum d_out * sigma^4
 #pragma unroll
@@ -447,20 +490,21 @@ struct RowPlan { bool fast; int G; int vpt; int grid; };
 // width, and the row fits in registers (<= 256 * 8 packs).
 template <typename T>
 RowPlan plan_rows(int64_t n_rows, int64_t n_cols, std::initializer_list<const void*> ptrs,
-                  std::initializer_list<int64_t> strides, int blocks_per_sm) {
+                  std::initializer_list<int64_t> strides, int blocks_per_sm, int packs_per_thread = 2,
+                  int threads = kThreads) {
   constexpr int W = 16 / sizeof(T);
   RowPlan p{true, 32, 1, 1};
   for (const void* q : ptrs) if (q && !aligned16(q)) p.fast = false;
   for (int64_t s : strides) if (s % W) p.fast = false;
-  if (n_cols % W || n_cols / W > int64_t(kThreads) * kMaxVPT) p.fast = false;
+  if (n_cols % W || n_cols / W > int64_t(threads) * kMaxVPT) p.fast = false;
   if (p.fast) {
     const int npk = int(n_cols / W);
     int G = 32;
-    while (G < kThreads && (npk + G - 1) / G > 2) G <<= 1;      // aim for <= 2 packs per thread
+    while (G < threads && (npk + G - 1) / G > packs_per_thread) G <<= 1;   // aim for this many 16-byte loads in flight per thread and tensor
     p.G = G;
     const int need = (npk + G - 1) / G;
     p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
-    const int rpc = kThreads / G;
+    const int rpc = threads / G;
     const int64_t blocks = (n_rows + rpc - 1) / rpc;
     p.grid = int(blocks < int64_t(blocks_per_sm) * kNumSM ? blocks : int64_t(blocks_per_sm) * kNumSM);
   } else {
@@ -487,7 +531,7 @@ int swiglu_fwd_t(const void* gate, const void* value, void* out, int64_t n_rows,
                    gs % W == 0 && vs % W == 0 && os % W == 0;
   const int64_t ppr = vec ? n_cols / W : n_cols;
   int64_t gx = (ppr + kThreads - 1) / kThreads;
-  const int64_t cap = 8 * kNumSM;
+  const int64_t cap = FAT_SWIGLU_BPS * kNumSM;
   if (gx > cap) gx = cap;
   int64_t gy = n_rows < (cap + gx - 1) / gx ? n_rows : (cap + gx - 1) / gx;
   dim3 grid((unsigned)gx, (unsigned)gy);
@@ -508,7 +552,7 @@ int swiglu_bwd_t(const void* d_out, const void* gate, const void* value, void* d
                    n_cols % W == 0 && dos % W == 0 && gs % W == 0 && vs % W == 0 && dgs % W == 0 && dvs % W == 0;
   const int64_t ppr = vec ? n_cols / W : n_cols;
   int64_t gx = (ppr + kThreads - 1) / kThreads;
-  const int64_t cap = 8 * kNumSM;
+  const int64_t cap = FAT_SWIGLU_BPS * kNumSM;
   if (gx > cap) gx = cap;
   int64_t gy = n_rows < (cap + gx - 1) / gx ? n_rows : (cap + gx - 1) / gx;
   dim3 grid((unsigned)gx, (unsigned)gy);
@@ -521,7 +565,7 @@ template <typename T>
 int norm_fwd_t(const void* x, const void* w, void* y, float* mean, int64_t n_rows, int64_t n_cols,
                int64_t xs, int64_t ys, double eps, cudaStream_t st) {
   constexpr int W = 16 / sizeof(T);
-  RowPlan p = plan_rows<T>(n_rows, n_cols, {x, w, y}, {xs, ys}, 8);
+  RowPlan p = plan_rows<T>(n_rows, n_cols, {x, w, y}, {xs, ys}, FAT_NORM_FWD_BPS, FAT_NORM_FWD_PPT);
   if (p.fast) {
     FAT_VPT_SWITCH(p.vpt, (norm_fwd_kernel<T, W, VPT><<<p.grid, kThreads, 0, st>>>(
         (const T*)x, (const T*)w, (T*)y, mean, n_rows, int(n_cols), xs, ys, eps, p.G)));
@@ -538,7 +582,12 @@ int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mea
                double eps, cudaStream_t st) {
   using C = typename Elem<T>::C;
   constexpr int W = 16 / sizeof(T);
-  RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, w, d_x}, {dos, xs, dxs}, 2);
+  // wide rows run with 512-thread blocks so that a thread owns one or two packs of a row: the per-thread
+  // state (weight, d_weight partials, the row and the prefetched next row) then fits in 64 registers
+  constexpr int kWide = 512;
+  const bool wide = n_cols / W > kThreads;
+  const int threads = wide ? kWide : kThreads;
+  RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, w, d_x}, {dos, xs, dxs}, FAT_NORM_BWD_BPS, FAT_NORM_BWD_PPT, threads);
   if (p.grid > kNormBwdMaxBlocks) p.grid = kNormBwdMaxBlocks;
   if (size_t(p.grid) * size_t(n_cols) * sizeof(C) > ws_bytes) {
     set_error("norm_bwd: workspace of %zu bytes is smaller than the %zu needed", ws_bytes,
@@ -547,14 +596,13 @@ int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mea
   }
   C* partial = reinterpret_cast<C*>(ws);
   if (p.fast) {
-    const int rpc = kThreads / p.G;
-    const size_t smem = rpc > 1 ? size_t(rpc) * n_cols * sizeof(C) : 0;
-    FAT_VPT_SWITCH(p.vpt, {
-      auto kern = norm_bwd_kernel<T, W, VPT>;
+    auto go = [&](auto kern, size_t smem) {
       if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      kern<<<p.grid, kThreads, smem, st>>>((const T*)d_out, (const T*)x, (const T*)w, mean, (T*)d_x, partial,
-                                          n_rows, int(n_cols), dos, xs, dxs, eps, p.G);
-    });
+      kern<<<p.grid, threads, smem, st>>>((const T*)d_out, (const T*)x, (const T*)w, mean, (T*)d_x, partial,
+                                         n_rows, int(n_cols), dos, xs, dxs, eps, p.G);
+    };
+    if (wide) { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kWide>, size_t(kWide) * VPT * W * sizeof(C))); }
+    else      { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kThreads>, size_t(kThreads) * VPT * W * sizeof(C))); }
   } else {
     row_slow_kernel<T, kNormBwd><<<p.grid, kThreads, 0, st>>>((const T*)x, (const T*)d_out, (const T*)w, nullptr, mean,
                                                                (T*)d_x, partial, n_rows, n_cols, xs, dos, dxs, eps);
@@ -569,7 +617,7 @@ template <typename T>
 int softmax_fwd_t(const void* x, void* pr, int64_t n_rows, int64_t n_cols, int64_t xs, int64_t ps, double eps,
                   cudaStream_t st) {
   constexpr int W = 16 / sizeof(T);
-  RowPlan p = plan_rows<T>(n_rows, n_cols, {x, pr}, {xs, ps}, 8);
+  RowPlan p = plan_rows<T>(n_rows, n_cols, {x, pr}, {xs, ps}, FAT_SOFTMAX_BPS, FAT_SOFTMAX_PPT);
   if (p.fast) {
     FAT_VPT_SWITCH(p.vpt, (softmax_fwd_kernel<T, W, VPT><<<p.grid, kThreads, 0, st>>>(
         (const T*)x, (T*)pr, n_rows, int(n_cols), xs, ps, eps, p.G)));
@@ -584,7 +632,7 @@ template <typename T>
 int softmax_bwd_t(const void* d_out, const void* x, void* d_x, int64_t n_rows, int64_t n_cols, int64_t dos,
                   int64_t xs, int64_t dxs, double eps, cudaStream_t st) {
   constexpr int W = 16 / sizeof(T);
-  RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, d_x}, {dos, xs, dxs}, 8);
+  RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, d_x}, {dos, xs, dxs}, FAT_SOFTMAX_BPS, FAT_SOFTMAX_PPT);
   if (p.fast) {
     FAT_VPT_SWITCH(p.vpt, (softmax_bwd_kernel<T, W, VPT><<<p.grid, kThreads, 0, st>>>(
         (const T*)d_out, (const T*)x, (T*)d_x, n_rows, int(n_cols), dos, xs, dxs, eps, p.G)));
