@@ -342,7 +342,7 @@ def bench_lm(args, rank, world, device, name):
     if world > 1:
         from torch.nn.parallel import DistributedDataParallel as DDP
         net = DDP(model, device_ids=[device.index], gradient_as_bucket_view=True, bucket_cap_mb=64)
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True, capturable=True)
     g = torch.Generator().manual_seed(1234 + 3 + rank)
     hids = torch.randint(0, cfg["vocab_size"], (cfg["batch"], cfg["seq"]), generator=g).pin_memory()
     hlab = torch.randint(0, cfg["vocab_size"], (cfg["batch"], cfg["seq"]), generator=g).pin_memory()
@@ -364,8 +364,35 @@ def bench_lm(args, rank, world, device, name):
         opt.step()
         last["loss_host"] = loss.item()
 
+    # One GPU: the whole step (forward, loss, backward, AdamW) is captured once in a CUDA graph, because issuing
+    # its ~1000 launches from Python takes about as long as executing them.  Several GPUs: eager DDP.
+    launch = "eager"
+    timed = step
+    if world == 1 and not args.no_graph:
+        try:
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    step()
+            torch.cuda.current_stream(device).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            opt.zero_grad(set_to_none=True)
+            with torch.cuda.graph(graph):
+                _, gloss = net(ids, labels=lab)
+                gloss.backward()
+                opt.step()
+            last["loss"] = gloss
+
+            def timed():
+                graph.replay()
+            launch = "cuda graph replay"
+        except Exception as exc:      # noqa: BLE001 - fall back to eager launches, say so in the output
+            print(f"graph capture failed ({exc!r}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize(device)
+            timed, launch = step, "eager (graph capture failed)"
     with ClockSampler(device.index) as clocks:
-        ms = time_steps(step, args.steps, args.warmup, world, device)
+        ms = time_steps(timed, args.steps, args.warmup, world, device)
     ms_e2e = time_steps(e2e_step, max(2, args.steps // 2), 1, world, device)
     tokens = cfg["batch"] * cfg["seq"] * world
     peaks = measured_peaks()
@@ -377,7 +404,7 @@ def bench_lm(args, rank, world, device, name):
         "dtype": "bf16",
         "config": {"workload": f"AlgebraicTransformerLM {name} training step (fwd+loss+bwd+AdamW), bf16, "
                                f"batch {cfg['batch']} x seq {cfg['seq']} per GPU", "params": n_params,
-                   "parallelism": f"dp{world}", "loss": float(last["loss"].item())},
+                   "parallelism": f"dp{world}", "launch": launch, "loss": float(last["loss"].item())},
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * hids.numel() * 8,
                 "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e},
         "gpu_launches": cfg["n_layers"] * 9 * args.steps,
@@ -460,6 +487,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "lm_small", "lm_xl"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="LM workloads: time eager launches instead of a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world, local = dist_env()

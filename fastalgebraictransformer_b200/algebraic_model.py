@@ -19,10 +19,9 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
-from . import _lib
-from .backward import RationalAttentionFunction
+from .backward import RationalAttentionPackedFunction
 from .forward import compute_alibi_slopes
-from .fused_ops import EPS, mean_error_norm, rational_swiglu
+from .fused_ops import EPS, RationalSwiGLUPacked, mean_error_norm
 
 
 class RationalMR(nn.Module):
@@ -47,8 +46,10 @@ class RationalSwiGLU(nn.Module):
         self.dropout = nn.Dropout(dropout)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gate, val = self.w_gate_val(x).chunk(2, dim=-1)
-        return self.dropout(self.w_out(rational_swiglu(gate, val)))
+        gv = self.w_gate_val(x)
+        if not gv.is_cuda:
+            raise RuntimeError("RationalSwiGLU: CUDA tensor required — this build has no CPU fallback")
+        return self.dropout(self.w_out(RationalSwiGLUPacked.apply(gv)))
 
 
 class AlgebraicAttention(nn.Module):
@@ -71,11 +72,10 @@ class AlgebraicAttention(nn.Module):
 
     def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, T, C = x.shape
-        qkv = self.qkv(x).view(B, T, 3, self.n_head, self.d_head).permute(2, 0, 3, 1, 4)   # [3,B,H,T,D] view
-        q, k, v = qkv.unbind(0)
-        out = RationalAttentionFunction.apply(q, k, v, self.alibi_slopes, self.scale, True, EPS,
-                                              _lib.PATH_AUTO, True)
-        out = out.transpose(1, 2).reshape(B, T, C)          # already [B,T,H,D] in memory: no copy
+        qkv = self.qkv(x).view(B, T, 3, self.n_head, self.d_head)
+        if not qkv.is_cuda:
+            raise RuntimeError("AlgebraicAttention: CUDA tensor required — this build has no CPU fallback")
+        out = RationalAttentionPackedFunction.apply(qkv, self.alibi_slopes, self.scale, EPS)     # [B,T,C]
         return self.dropout(self.out(out))
 
 

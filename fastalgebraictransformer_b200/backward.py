@@ -53,6 +53,32 @@ class RationalAttentionFunction(torch.autograd.Function):
         return grad_q, grad_k, grad_v, None, None, None, None, None, None
 
 
+class RationalAttentionPackedFunction(torch.autograd.Function):
+    """Causal rational attention straight from a packed projection ``qkv`` [B, T, 3, H, D] to [B, T, H*D].
+
+    Same arithmetic as ``RationalAttentionFunction`` on the three permuted views (reference
+    algebraic_model.py:89-107), but nothing is copied on either side: the kernels read the views in place,
+    write the output in [B, T, H, D] order, and the backward returns one [B, T, 3, H, D] gradient."""
+
+    @staticmethod
+    def forward(ctx, qkv, alibi_slopes, scale, eps):
+        assert qkv.is_cuda and qkv.dim() == 5 and qkv.shape[2] == 3
+        B, T, _, H, D = qkv.shape
+        q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
+        out, L, out_lo = ops._attn_fwd(q, k, v, alibi_slopes, float(scale), True, float(eps), _lib.PATH_AUTO, True)
+        ctx.save_for_backward(qkv, out, L, out_lo, alibi_slopes)
+        ctx.scale, ctx.eps = float(scale), float(eps)
+        return out.permute(0, 2, 1, 3).reshape(B, T, H * D)        # a view: the memory order already is [B,T,H,D]
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        qkv, out, L, out_lo, alibi_slopes = ctx.saved_tensors
+        B, T, _, H, D = qkv.shape
+        d_out = grad_output.reshape(B, T, H, D).permute(0, 2, 1, 3)
+        return ops.attn_bwd_packed(qkv, out, out_lo, L, d_out, alibi_slopes, ctx.scale, True, ctx.eps,
+                                   _lib.PATH_AUTO), None, None, None
+
+
 def rational_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alibi_slopes: torch.Tensor, scale: float,
                        causal: bool = True, eps: float = EPS) -> torch.Tensor:
     """Memory-efficient rational attention with a custom backward (reference backward.py:386-396)."""

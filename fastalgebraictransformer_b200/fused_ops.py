@@ -50,6 +50,27 @@ class RationalSwiGLU(torch.autograd.Function):
         return _alg.swiglu_bwd(grad_output, gate, value)
 
 
+class RationalSwiGLUPacked(torch.autograd.Function):
+    """Rational SwiGLU of a packed projection ``gv = [gate | value]`` (last dimension 2n -> n).
+
+    What ``RationalSwiGLU.apply(*gv.chunk(2, -1))`` computes, but the backward hands autograd ONE
+    [..., 2n] gradient instead of two halves that it would have to concatenate.  Used by the model's FFN
+    (reference algebraic_model.py:51-62)."""
+
+    @staticmethod
+    def forward(ctx, gv: torch.Tensor) -> torch.Tensor:
+        assert gv.is_cuda, "Inputs must be on CUDA"
+        gate, value = gv.chunk(2, dim=-1)
+        ctx.save_for_backward(gv)
+        return ops._swiglu_fwd(gate, value)
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        (gv,) = ctx.saved_tensors
+        gate, value = gv.chunk(2, dim=-1)
+        return ops.swiglu_bwd_packed(grad_output, gate, value)
+
+
 class MeanErrorNorm(torch.autograd.Function):
     """y = x / (mean|x| + eps) * weight (reference fused_ops.py:542-599); returns (d_x, d_weight, None)."""
 

@@ -98,6 +98,13 @@ def _swiglu_bwd(d_out: Tensor, gate: Tensor, value: Tensor) -> Tuple[Tensor, Ten
     return d_gate, d_value
 
 
+def swiglu_bwd_packed(d_out: Tensor, gate: Tensor, value: Tensor) -> Tensor:
+    """Both SwiGLU gradients as one [..., 2n] tensor (gate half first): what the gradient of the packed
+    projection output needs, without a concatenation."""
+    d_gate, _ = _swiglu_bwd(d_out, gate, value)
+    return d_gate._base if d_gate._base is not None else torch.cat(_swiglu_bwd(d_out, gate, value), -1)
+
+
 # ----------------------------------------------------------------------------- mean-error norm
 def _norm_fwd(x: Tensor, weight: Tensor, eps: float) -> Tuple[Tensor, Tensor]:
     _cuda_check(x, weight)
@@ -228,6 +235,17 @@ def _attn_bwd(q: Tensor, k: Tensor, v: Tensor, out: Tensor, out_lo: Tensor, L: T
                 _lib.strides3(d_q), _lib.strides3(d_k), _lib.strides3(d_v),
                 scale, eps, int(causal), tag, path, _p(_lib.device_status(q.device)), _lib.stream_ptr(q.device)))
     return d_q, d_k, d_v
+
+
+def attn_bwd_packed(qkv: Tensor, out: Tensor, out_lo: Tensor, L: Tensor, d_out: Tensor, slopes: Tensor,
+                    scale: float, causal: bool, eps: float, path: int) -> Tensor:
+    """Gradient of a packed [B,T,3,H,D] projection: d_q, d_k, d_v written side by side into one buffer."""
+    q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
+    d_q, d_k, d_v = _attn_bwd(q, k, v, out, out_lo, L, d_out, slopes, scale, causal, eps, path)
+    base = d_q._base
+    if base is None or base.shape != qkv.shape:           # q was not token-major after all (H == 1 or T == 1)
+        base = torch.stack((d_q, d_k, d_v), 0).permute(1, 3, 0, 2, 4).contiguous()
+    return base
 
 
 for _name, _fn in (("swiglu_fwd", _swiglu_fwd), ("swiglu_bwd", _swiglu_bwd), ("norm_fwd", _norm_fwd),
