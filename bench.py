@@ -160,7 +160,7 @@ def make_attn_inputs(cfg, seed, device=None, pin=False):
 def bench_attn(args, rank, world, device):
     import fastalgebraictransformer_b200 as fat
     from fastalgebraictransformer_b200 import _lib
-    cfg = ATTN
+    cfg = dict(ATTN, B=args.batch) if args.batch else ATTN
     (q, k, v, go), slopes = make_attn_inputs(cfg, 1234 + 1 + rank, device)
     slopes = slopes.to(device)
     scale = 1.0 / math.sqrt(cfg["D"])
@@ -208,8 +208,9 @@ def bench_attn(args, rank, world, device):
     return {
         "metric": "rational_attention_fwd_bwd_tflops", "value": tfl, "unit": "TFLOP/s",
         "ms_per_step": ms, "dtype": "bf16",
-        "config": {"workload": "rational_attention fwd+bwd causal ALiBi bf16 B=8 H=16 S=4096 D=128 per GPU "
-                               "(BASELINE configs[1])", "units_per_gpu": cfg["B"] * cfg["H"], "shard": "batch x head",
+        "config": {"workload": f"rational_attention fwd+bwd causal ALiBi bf16 B={cfg['B']} H=16 S=4096 D=128 per GPU "
+                               + ("(BASELINE configs[1])" if cfg["B"] == 8 else "(REDUCED batch: profiling case, not a bench value)"),
+                   "units_per_gpu": cfg["B"] * cfg["H"], "shard": "batch x head",
                    "kernel_path": "tcgen05" if path == 2 else "simt", "l2": "inputs (4 x 134 MB) exceed the 126 MB L2",
                    "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
                    "pct_of_bf16_peak": 100.0 * tfl / world / peaks["bf16_tflops"]},
@@ -417,6 +418,16 @@ def bench_lm(args, rank, world, device, name):
 
 
 # ------------------------------------------------------------------------------------------ CPU arm
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every core it may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_attention_sample(heads: int, repeats: int = 1):
     """The oracle (CPU restatement of the reference's PyTorch path) on `heads` heads of one batch element of the
     attention workload, float32, all host threads.  Returns (seconds per pass, flops per pass)."""
@@ -436,6 +447,7 @@ def cpu_attention_sample(heads: int, repeats: int = 1):
 
 
 def cpu_baseline_attn():
+    use_all_host_threads()
     heads = 2
     sec, flops = cpu_attention_sample(heads, repeats=1)           # warm-up / sizing pass
     total, n = 0.0, 0
@@ -453,6 +465,7 @@ def run_reference(args, rank, world):
         return None
     if args.workload != "attn":
         return {"impl": "reference", "unavailable": "the CPU arm is implemented for the attention workload only"}
+    use_all_host_threads()
     heads = 1
     cpu_attention_sample(heads)                                    # untimed
     for _ in range(max(0, args.warmup - 1)):
@@ -487,6 +500,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "lm_small", "lm_xl"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="attn workload: override the batch size (profiling captures use a smaller case)")
     ap.add_argument("--no-graph", action="store_true", help="LM workloads: time eager launches instead of a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
