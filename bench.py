@@ -217,18 +217,21 @@ def bench_attn(args, rank, world, device):
         "e2e": {"value": (fwd_flops + bwd_flops) * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "ms_per_step": ms_e2e},
         "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "attention backward", "achieved": bwd_tfl,
+        # traffic: dram bytes of the three backward launches, ncu capture at B=2 scaled by the units processed
+        # (profiles/attention_tcgen05_b8_h16_s4096_d128.md)
+        "roofline": {"bound": "tensor", "kernel": "attention backward (prepare + d_q + d_k/d_v launches)", "achieved": bwd_tfl,
                      "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": bwd_tfl / peaks["bf16_tflops"],
-                     "traffic": None, "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                     "traffic": 438.3e6 * cfg["B"] / 2, "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
                      "fwd_achieved": fwd_flops / (ms_fwd * 1e-3) / 1e12},
         "clocks": clocks.summary(),
     }
 
 
+# `traffic`: dram bytes of one step's launches from the ncu capture summarised in profiles/fused_ops_bf16_config3.md
 FUSED = {
-    "swiglu": dict(rows=16384, cols=8192, bytes=2147483648),
-    "norm": dict(rows=16384, cols=4096, bytes=671088640),
-    "softmax": dict(rows=4096, cols=4096, bytes=150994944),   # backward reads d_out and x only (p is recomputed)
+    "swiglu": dict(rows=16384, cols=8192, bytes=2147483648, traffic=2068e6),
+    "norm": dict(rows=16384, cols=4096, bytes=671088640, traffic=587e6),
+    "softmax": dict(rows=4096, cols=4096, bytes=150994944, traffic=106e6),   # backward reads d_out and x only (p is recomputed)
 }
 
 
@@ -320,7 +323,7 @@ def bench_fused(args, rank, world, device, name):
                 "d2h_bytes_per_step": n_out * shape[0] * shape[1] * 2, "ms_per_step": ms_e2e},
         "gpu_launches": (3 if name == "norm" else 2) * args.steps,
         "roofline": {"bound": "hbm", "kernel": f"{name} fwd+bwd", "achieved": gbs / world, "peak": peaks["hbm_gbs"],
-                     "unit": "GB/s", "frac": gbs / world / peaks["hbm_gbs"], "traffic": None,
+                     "unit": "GB/s", "frac": gbs / world / peaks["hbm_gbs"], "traffic": cfg["traffic"],
                      "peak_source": peaks["source"]},
         "clocks": clocks.summary(),
     }
