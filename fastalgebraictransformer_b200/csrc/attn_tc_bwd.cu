@@ -32,6 +32,7 @@ constexpr int kChunks = kColsPerGroup / 32;           // 32-column chunks per th
 constexpr int kTmaWarp = 4 * kEwGroups, kMmaWarp = kTmaWarp + 1;
 constexpr int kBwdThreads = kEwThreads + 64;          // + one TMA producer warp + one MMA issuer warp
 constexpr int kBwdStages = 2;
+constexpr int kDqKStages = 3;
 
 __host__ __device__ inline int64_t pad_rows(int T) { return int64_t((T + BLK - 1) / BLK) * BLK; }
 
@@ -131,17 +132,18 @@ struct DqSmem {
   static constexpr int kTileBytes = BLK * D * 2;
   alignas(1024) unsigned char q[kTileBytes];               // reused as d_q staging in the epilogue
   alignas(1024) unsigned char dout[kTileBytes];
-  alignas(1024) unsigned char k[kBwdStages][kTileBytes];
+  alignas(1024) unsigned char k[kDqKStages][kTileBytes];   // K(j) is read by S(j) early and by dQ(j) late: three stages keep the loads ahead
   alignas(1024) unsigned char v[kBwdStages][kTileBytes];
-  uint64_t qdo_full, k_full[kBwdStages], k_empty[kBwdStages], v_full[kBwdStages], v_empty[kBwdStages];
-  uint64_t s_full, s_free, dp_full, ds_full, dq_full;
+  uint64_t qdo_full, k_full[kDqKStages], k_empty[kDqKStages], v_full[kBwdStages], v_empty[kBwdStages];
+  uint64_t s_full, s_free, dp_full[2], ds_full[2], dq_full;   // dp_/ds_: one per dP buffer, so no barrier runs two phases ahead
   uint32_t tmem_base;
   int abort_flag;
 };
 
 struct DqMaps { CUtensorMap q, dout, k, v, dq; };
 
-// TMEM columns: S [0,128)   dP' / packed dS [128,256)   dQ [256,256+D)
+// TMEM columns: S [0,128)   dP / packed dS of even / odd key tiles [128,256) / [256,384)   dQ [384,384+D)
+// dP is double-buffered: dP of the next key tile is computed while dS of the current one is still feeding dQ.
 template <typename T, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
@@ -157,11 +159,11 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
 
   if (tid == 0) {
     sm.abort_flag = 0;
-    mbar_init(&sm.qdo_full, 1); mbar_init(&sm.s_full, 1); mbar_init(&sm.s_free, kEwThreads);
-    mbar_init(&sm.dp_full, 1); mbar_init(&sm.ds_full, kEwThreads); mbar_init(&sm.dq_full, 1);
-    for (int i = 0; i < kBwdStages; ++i) {
-      mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1);
-    }
+    mbar_init(&sm.qdo_full, 1);
+    mbar_init(&sm.s_full, 1); mbar_init(&sm.s_free, kEwThreads); mbar_init(&sm.dq_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.dp_full[i], 1); mbar_init(&sm.ds_full[i], kEwThreads); }
+    for (int i = 0; i < kDqKStages; ++i) { mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); }
+    for (int i = 0; i < kBwdStages; ++i) { mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1); }
     mbar_fence_init();
   }
   if (warp == kTmaWarp) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
@@ -169,7 +171,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t tS = tmem, tP = tmem + BLK, tQ = tmem + 2 * BLK;
+  const uint32_t tS = tmem, tP0 = tmem + BLK, tQ = tmem + 3 * BLK;            // dP(j) lives at tP0 + (j & 1) * BLK
 
   if (warp == kTmaWarp) {
     if (elect_one()) {
@@ -177,12 +179,11 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       load_tile_tma_noexpect<D>(sm.q, &maps.q, &sm.qdo_full, qt * BLK, h, b);
       load_tile_tma_noexpect<D>(sm.dout, &maps.dout, &sm.qdo_full, qt * BLK, h, b);
       for (int j = 0; j < n; ++j) {
-        const int st = j % kBwdStages;
-        const uint32_t ph = (j / kBwdStages) & 1;
-        if (!g.wait(&sm.k_empty[st], ph ^ 1, 40)) break;
-        load_tile_tma<D>(sm.k[st], &maps.k, &sm.k_full[st], j * BLK, h, b);
-        if (!g.wait(&sm.v_empty[st], ph ^ 1, 41)) break;
-        load_tile_tma<D>(sm.v[st], &maps.v, &sm.v_full[st], j * BLK, h, b);
+        const int ks = j % kDqKStages, vs = j % kBwdStages;
+        if (!g.wait(&sm.k_empty[ks], ((j / kDqKStages) & 1) ^ 1, 40)) break;
+        load_tile_tma<D>(sm.k[ks], &maps.k, &sm.k_full[ks], j * BLK, h, b);
+        if (!g.wait(&sm.v_empty[vs], ((j / kBwdStages) & 1) ^ 1, 41)) break;
+        load_tile_tma<D>(sm.v[vs], &maps.v, &sm.v_full[vs], j * BLK, h, b);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -190,35 +191,50 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
       constexpr uint32_t idesc_dq = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
       const uint64_t qd = desc_kmajor(sm.q), dod = desc_kmajor(sm.dout);
-      const uint64_t kd[kBwdStages] = {desc_kmajor(sm.k[0]), desc_kmajor(sm.k[1])};
-      const uint64_t kd_mn[kBwdStages] = {desc_mnmajor(sm.k[0]), desc_mnmajor(sm.k[1])};
+      const uint64_t kd[kDqKStages] = {desc_kmajor(sm.k[0]), desc_kmajor(sm.k[1]), desc_kmajor(sm.k[2])};
+      const uint64_t kd_mn[kDqKStages] = {desc_mnmajor(sm.k[0]), desc_mnmajor(sm.k[1]), desc_mnmajor(sm.k[2])};
       const uint64_t vd[kBwdStages] = {desc_kmajor(sm.v[0]), desc_kmajor(sm.v[1])};
       bool ok = g.wait(&sm.qdo_full, 0, 50) && g.wait(&sm.k_full[0], 0, 51);
       if (ok) { tc_fence_after(); issue_gemm_nt<D>(tS, qd, kd[0], idesc_s); mma_commit(&sm.s_full); }
       ok = ok && g.wait(&sm.v_full[0], 0, 52);
-      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tP, dod, vd[0], idesc_s); mma_commit(&sm.dp_full); mma_commit(&sm.v_empty[0]); }
+      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tP0, dod, vd[0], idesc_s); mma_commit(&sm.dp_full[0]); mma_commit(&sm.v_empty[0]); }
       for (int j = 0; j < n && ok; ++j) {
-        const int st = j % kBwdStages, st1 = (j + 1) % kBwdStages;
-        const uint32_t ph1 = ((j + 1) / kBwdStages) & 1;
+        const int ks = j % kDqKStages, ks1 = (j + 1) % kDqKStages, vs1 = (j + 1) % kBwdStages;
+        const uint32_t kph1 = ((j + 1) / kDqKStages) & 1, vph1 = ((j + 1) / kBwdStages) & 1;
         if (j + 1 < n) {
+          // S(j+1) as soon as phase A has read S(j); dP(j+1) into the other dP buffer (its previous tenant dS(j-1)
+          // was consumed by dQ(j-1), issued before this point), so phase B of the next tile never waits for it
+          TR_BEGIN();
           if (!(ok = g.wait(&sm.s_free, j & 1, 53))) break;
-          if (!(ok = g.wait(&sm.k_full[st1], ph1, 54))) break;
+          TR_WAITED();
+          TR_STAMP(64 + 8 * (j - 10) + 0, j >= 10 && j < 13);
+          if (!(ok = g.wait(&sm.k_full[ks1], kph1, 54))) break;
+          TR_WORKED();                                         // (trace builds: time spent waiting for K)
           tc_fence_after();
-          issue_gemm_nt<D>(tS, qd, kd[st1], idesc_s);
+          issue_gemm_nt<D>(tS, qd, kd[ks1], idesc_s);
           mma_commit(&sm.s_full);
-        }
-        if (!(ok = g.wait(&sm.ds_full, j & 1, 55))) break;
-        tc_fence_after();
-        issue_gemm_tn<kColsPerGroup>(tQ, tP, kd_mn[st], idesc_dq, j > 0);       // dQ += dS K
-        mma_commit(&sm.k_empty[st]);
-        if (j + 1 < n) {
-          if (!(ok = g.wait(&sm.v_full[st1], ph1, 56))) break;
+          TR_BEGIN();
+          if (!(ok = g.wait(&sm.v_full[vs1], vph1, 56))) break;
+          TR_WAITED2();                                        // (trace builds: time spent waiting for V)
           tc_fence_after();
-          issue_gemm_nt<D>(tP, dod, vd[st1], idesc_s);
-          mma_commit(&sm.dp_full);
-          mma_commit(&sm.v_empty[st1]);
+          TR_STAMP(64 + 8 * (j - 10) + 1, j >= 10 && j < 13);
+          issue_gemm_nt<D>(tP0 + ((j + 1) & 1) * BLK, dod, vd[vs1], idesc_s);
+          mma_commit(&sm.dp_full[(j + 1) & 1]);
+          TR_STAMP(64 + 8 * (j - 10) + 2, j >= 10 && j < 13);
+          mma_commit(&sm.v_empty[vs1]);
         }
+        TR_BEGIN();
+        if (!(ok = g.wait(&sm.ds_full[j & 1], (j >> 1) & 1, 55))) break;
+        TR_MARK();
+        TR_WORKED2();                                          // (trace builds: time spent waiting for dS)
+        TR_STAMP(64 + 8 * (j - 10) + 3, j >= 10 && j < 13);
+        tc_fence_after();
+        issue_gemm_tn<kColsPerGroup>(tQ, tP0 + (j & 1) * BLK, kd_mn[ks], idesc_dq, j > 0);       // dQ += dS K
+        mma_commit(&sm.k_empty[ks]);
       }
+#ifdef FAT_TRACE
+      if (traced) { long long* o = trace + 32; o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
+#endif
       if (ok) mma_commit(&sm.dq_full);
     }
   } else {
@@ -239,6 +255,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       TR_BEGIN();
       if (!(ok = g.wait(&sm.s_full, j & 1, 60))) break;
       TR_WAITED();
+      TR_STAMP(64 + 8 * (j - 10) + 4, tid == 0 && j >= 10 && j < 13);
       tc_fence_after();
       const float base = slope * float(j * BLK - row);       // bias of key column 0 of this tile
 #pragma unroll
@@ -252,7 +269,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
         for (int i = 0; i < 16; ++i) {
           f32x2 F2, g2;
           const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-          if (i % 4 == 0) score_fg2<false, true>(acc2, scale2, bias2, half2, F2, g2);
+          if (rcp_shared(i, FAT_RCP_SHARE_BWD)) score_fg2<false, true>(acc2, scale2, bias2, half2, F2, g2);
           else            score_fg2<false, false>(acc2, scale2, bias2, half2, F2, g2);
           bias2 = add2(bias2, step2);
           gq[16 * c + i] = g2;
@@ -261,11 +278,14 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       tc_fence_before();
       mbar_arrive(&sm.s_free);
       TR_WORKED();
+      TR_STAMP(64 + 8 * (j - 10) + 5, tid == 0 && j >= 10 && j < 13);
       // ---- phase B: dS = g (dP - Delta), packed over dP
-      if (!(ok = g.wait(&sm.dp_full, j & 1, 61))) break;
+      if (!(ok = g.wait(&sm.dp_full[j & 1], (j >> 1) & 1, 61))) break;
       TR_WAITED2();
+      TR_STAMP(64 + 8 * (j - 10) + 6, tid == 0 && j >= 10 && j < 13);
       tc_fence_after();
       const bool diag = (j == qt);
+      const uint32_t tP = tP0 + (j & 1) * BLK;
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) {
         uint32_t dreg[32], preg[16];
@@ -286,8 +306,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&sm.ds_full);
+      mbar_arrive(&sm.ds_full[j & 1]);
       TR_WORKED2();
+      TR_STAMP(64 + 8 * (j - 10) + 7, tid == 0 && j >= 10 && j < 13);
     }
 #ifdef FAT_TRACE
     if (traced && (tid & 127) == 0 && tid < 256) { long long* o = trace + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
@@ -458,7 +479,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
           const f32x2 iv2 = pk2(iv2f.x, iv2f.y);
           f32x2 F2, g2;
           const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-          if (i % 4 == 0) score_fg2<true, true>(acc2, scale2, bias2, half2, F2, g2);
+          if (rcp_shared(i, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, bias2, half2, F2, g2);
           else            score_fg2<true, false>(acc2, scale2, bias2, half2, F2, g2);
           bias2 = add2(bias2, step2);
           F2 = mul2(F2, iv2);

@@ -105,6 +105,8 @@ __device__ __forceinline__ void issue_gemm_tn(uint32_t d_tmem, uint32_t a_tmem, 
 #define TR_WORKED() tr_a = clock64(); tr_work += tr_a - tr_b
 #define TR_WAITED2() tr_b = clock64(); tr_wait2 += tr_b - tr_a
 #define TR_WORKED2() tr_a = clock64(); tr_work2 += tr_a - tr_b
+#define TR_MARK() tr_b = tr_a
+#define TR_STAMP(idx, cond) do { if (traced && (cond)) trace[idx] = clock64() - tr_t0; } while (0)
 #else
 #define FAT_TRACE_DECL(cond)
 #define TR_BEGIN()
@@ -112,6 +114,8 @@ __device__ __forceinline__ void issue_gemm_tn(uint32_t d_tmem, uint32_t a_tmem, 
 #define TR_WORKED()
 #define TR_WAITED2()
 #define TR_WORKED2()
+#define TR_MARK()
+#define TR_STAMP(idx, cond)
 #endif
 
 // ------------------------------------------------------------------ packed fp32 pairs (sm_100 FFMA2 / FMUL2 / FADD2)
@@ -139,6 +143,13 @@ __device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+
+// Every kRcpShare*-th pair of scores takes its two reciprocals from one special-function op (0: never).
+#ifndef FAT_RCP_SHARE_FWD
+#define FAT_RCP_SHARE_FWD 2
+#define FAT_RCP_SHARE_BWD 8
+#endif
+__device__ __forceinline__ constexpr bool rcp_shared(int i, int every) { return every > 0 && i % every == 0; }
 
 // Reciprocals of two numbers >= 1.  SHARED: from ONE special-function op, 1/a = b * (1/(a b)),
 // 1/b = a * (1/(a b)) (three extra multiplies); otherwise two special-function ops.  The kernels

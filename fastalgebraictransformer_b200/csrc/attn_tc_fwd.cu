@@ -57,7 +57,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t trow, int r, f32x2 scale2,
       const f32x2 s2 = fma2(pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), scale2, bias2);
       bias2 = add2(bias2, step2);
       f32x2 r2, w2;
-      if (i % 4 == 0) sigma_terms2<true>(s2, half2, r2, w2); else sigma_terms2<false>(s2, half2, r2, w2);
+      if (rcp_shared(i, FAT_RCP_SHARE_FWD)) sigma_terms2<true>(s2, half2, r2, w2); else sigma_terms2<false>(s2, half2, r2, w2);
       const f32x2 q2 = mul2(w2, w2);
       f32x2 f2 = mul2(q2, q2);                               // (2 sigma)^4 = 16 sigma^4
       float f0, f1;
