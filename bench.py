@@ -209,7 +209,7 @@ def bench_attn(args, rank, world, device):
         "metric": "rational_attention_fwd_bwd_tflops", "value": tfl, "unit": "TFLOP/s",
         "ms_per_step": ms, "dtype": "bf16",
         "config": {"workload": f"rational_attention fwd+bwd causal ALiBi bf16 B={cfg['B']} H=16 S=4096 D=128 per GPU "
-                               + ("(BASELINE configs[1])" if cfg["B"] == 8 else "(REDUCED batch: profiling case, not a bench value)"),
+                               + ("(headline configuration)" if cfg["B"] == 8 else "(REDUCED batch: profiling case, not a bench value)"),
                    "units_per_gpu": cfg["B"] * cfg["H"], "shard": "batch x head",
                    "kernel_path": "tcgen05" if path == 2 else "simt", "l2": "inputs (4 x 134 MB) exceed the 126 MB L2",
                    "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
@@ -218,7 +218,7 @@ def bench_attn(args, rank, world, device):
                 "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "ms_per_step": ms_e2e},
         "gpu_launches": launches_per_step * args.steps,
         # traffic: dram bytes of the three backward launches, ncu capture at B=2 scaled by the units processed
-        # (profiles/attention_tcgen05_b8_h16_s4096_d128.md)
+        # (the capture's summary is kept with the other profiler summaries of this repository)
         "roofline": {"bound": "tensor", "kernel": "attention backward (prepare + d_q + d_k/d_v launches)", "achieved": bwd_tfl,
                      "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": bwd_tfl / peaks["bf16_tflops"],
                      "traffic": 438.3e6 * cfg["B"] / 2, "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
@@ -227,7 +227,7 @@ def bench_attn(args, rank, world, device):
     }
 
 
-# `traffic`: dram bytes of one step's launches from the ncu capture summarised in profiles/fused_ops_bf16_config3.md
+# `traffic`: dram bytes of one step's launches, from an ncu capture of these kernels at these shapes
 FUSED = {
     "swiglu": dict(rows=16384, cols=8192, bytes=2147483648, traffic=2068e6),
     "norm": dict(rows=16384, cols=4096, bytes=671088640, traffic=587e6),
@@ -314,7 +314,7 @@ def bench_fused(args, rank, world, device, name):
     n_out = {"swiglu": 3, "norm": 2, "softmax": 2}[name]
     return {
         "metric": f"rational_{name}_fwd_bwd_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "dtype": "bf16",
-        "config": {"workload": f"{name} fwd+bwd bf16 [{cfg['rows']},{cfg['cols']}] (BASELINE configs[2])",
+        "config": {"workload": f"{name} fwd+bwd bf16 [{cfg['rows']},{cfg['cols']}] (bandwidth-sweep configuration)",
                    "algorithmic_bytes_per_step": cfg["bytes"],
                    "launch": "each step replayed from a CUDA graph",
                    "l2": "tensors exceed L2" if nset == 1 else f"{nset} rotating input sets (each pass touches > 126 MB before reuse)"},
@@ -486,7 +486,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "rational_attention_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "rational_attention fwd+bwd causal ALiBi B=8 H=16 S=4096 D=128 (BASELINE configs[1]); "
+        "config": {"workload": "rational_attention fwd+bwd causal ALiBi B=8 H=16 S=4096 D=128 (headline configuration); "
                                "CPU restatement of the reference's PyTorch path on a bounded sample"},
         "cpu_baseline": base,
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -63,7 +63,7 @@ def test_fp32_vs_oracle(shape):
 
 
 def test_config1_fp32_closed_form_slopes():
-    """BASELINE config 1: B=2,H=12,S=512,D=64 float32, slopes 2^(-8(i+1)/12)."""
+    """Benchmark configuration 1: B=2,H=12,S=512,D=64 float32, slopes 2^(-8(i+1)/12)."""
     B, H, T, D = 2, 12, 512, 64
     g = torch.Generator().manual_seed(1234 + 0)
     q, k, v, go = (torch.randn(B, H, T, D, generator=g) for _ in range(4))
@@ -188,7 +188,7 @@ def test_forced_tensor_path_rejects_ineligible_requests():
 
 
 def test_config2_slice_bf16():
-    """BASELINE config 2 (B=8,H=16,S=4096,D=128 bf16), one batch element against the oracle, the rest through
+    """Benchmark configuration 2 (B=8,H=16,S=4096,D=128 bf16), one batch element against the oracle, the rest through
     a property: heads and batch elements are independent, so batch element b of the full run equals a run on it alone."""
     H, T, D = 16, 4096, 128
     g = torch.Generator().manual_seed(1234 + 1)

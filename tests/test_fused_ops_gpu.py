@@ -195,7 +195,7 @@ def test_torch_library_ops_have_autograd():
 
 
 def test_full_size_properties():
-    """BASELINE sizes, checked through size-independent properties instead of the (slow) oracle."""
+    """Benchmark sizes, checked through size-independent properties instead of the (slow) oracle."""
     f = fat()
     g = torch.Generator(device=DEV).manual_seed(19)
     x = (torch.randn(4096, 4096, generator=g, device=DEV) * 1.4142).to(torch.bfloat16)
