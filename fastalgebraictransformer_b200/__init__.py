@@ -10,7 +10,7 @@ from .backward import rational_attention, rational_attention_backward, RationalA
 from .algebraic_model import (AlgebraicTransformerLM, RationalMR, RationalSwiGLU as RationalSwiGLUModule,
                               AlgebraicAttention, AlgebraicBlock, create_small_model, create_medium_model,
                               create_large_model, create_xl_model)
-from ._lib import check_device_status, PATH_AUTO, PATH_SIMT, PATH_TENSOR
+from ._lib import check_device_status, PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_TENSOR_DETERMINISTIC
 
 __all__ = [
     "rational_softmax", "rational_swiglu", "mean_error_norm", "RationalSoftmax", "RationalSwiGLU", "MeanErrorNorm", "EPS",

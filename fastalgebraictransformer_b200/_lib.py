@@ -15,7 +15,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libfat_b200.so")
 
 F32, BF16, F16, F64 = 0, 1, 2, 3
-PATH_AUTO, PATH_SIMT, PATH_TENSOR = 0, 1, 2
+PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_TENSOR_DETERMINISTIC = 0, 1, 2, 3
 DTYPE_TAG = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16, torch.float64: F64}
 
 _lock = threading.Lock()

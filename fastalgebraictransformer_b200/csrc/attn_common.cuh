@@ -18,6 +18,7 @@ struct AttnParams {
   int64_t qs[3], ks[3], vs[3], os[3], dos[3], dqs[3], dks[3], dvs[3];
   float scale, eps;
   int causal;
+  int deterministic;                          // tensor path backward: two kernels without atomics instead of the fused one
   int* status;
 };
 

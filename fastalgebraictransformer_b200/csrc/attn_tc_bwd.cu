@@ -10,6 +10,8 @@
 // In both main kernels the element-wise work is split in two phases so that the tensor core
 // never waits for it: phase A needs only the scores (sigma, F, g), phase B only dP'.
 // Eight element-wise warps share a tile: warpgroup w owns score columns [64w, 64w+64).
+#include <type_traits>
+
 #include "attn_tc_common.cuh"
 
 namespace fat {
@@ -286,24 +288,29 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       tc_fence_after();
       const bool diag = (j == qt);
       const uint32_t tP = tP0 + (j & 1) * BLK;
+      // (the diagonal tile gets its own copy of the loop: a run-time test inside the unrolled body would split it
+      //  into basic blocks and keep the compiler from interleaving the independent pairs)
+      auto phase_b = [&](auto DIAG) {
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t dreg[32], preg[16];
-        tmem_ld32(tmem_addr(tP, lane_base, kColsPerGroup * w + 32 * c), dreg);
-        tmem_wait_ld_regs(dreg);
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t dreg[32], preg[16];
+          tmem_ld32(tmem_addr(tP, lane_base, kColsPerGroup * w + 32 * c), dreg);
+          tmem_wait_ld_regs(dreg);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const f32x2 ds2 = mul2(gq[16 * c + i], add2(pk2(__uint_as_float(dreg[2 * i]), __uint_as_float(dreg[2 * i + 1])), ndlt2));
-          float d0, d1;
-          upk2(ds2, d0, d1);
-          if (diag) {
-            if (kColsPerGroup * w + 32 * c + 2 * i > r) d0 = 0.f;
-            if (kColsPerGroup * w + 32 * c + 2 * i + 1 > r) d1 = 0.f;
+          for (int i = 0; i < 16; ++i) {
+            const f32x2 ds2 = mul2(gq[16 * c + i], add2(pk2(__uint_as_float(dreg[2 * i]), __uint_as_float(dreg[2 * i + 1])), ndlt2));
+            float d0, d1;
+            upk2(ds2, d0, d1);
+            if constexpr (decltype(DIAG)::value) {
+              if (kColsPerGroup * w + 32 * c + 2 * i > r) d0 = 0.f;
+              if (kColsPerGroup * w + 32 * c + 2 * i + 1 > r) d1 = 0.f;
+            }
+            preg[i] = Pack16<T>::pack(d0, d1);
           }
-          preg[i] = Pack16<T>::pack(d0, d1);
+          tmem_st16(tmem_addr(tP, lane_base, packed_col(w, c)), preg);
         }
-        tmem_st16(tmem_addr(tP, lane_base, packed_col(w, c)), preg);
-      }
+      };
+      if (diag) phase_b(std::true_type{}); else phase_b(std::false_type{});
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.ds_full[j & 1]);
@@ -466,38 +473,41 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       tc_fence_after();
       const float base = slope * float(key - qi * BLK);      // bias of query column 0: -slope*(q-key)
       const float* iv = sm.inv[st];
+      auto phase_a = [&](auto DIAG) {          // the diagonal tile gets its own copy (no run-time test in the unrolled body)
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t sreg[32], preg[16];
-        tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
-        tmem_wait_ld_regs(sreg);
-        const int col0 = kColsPerGroup * w + 32 * c;
-        f32x2 bias2 = pk2(fmaf(-slope, float(col0), base), fmaf(-slope, float(col0 + 1), base));
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t sreg[32], preg[16];
+          tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
+          tmem_wait_ld_regs(sreg);
+          const int col0 = kColsPerGroup * w + 32 * c;
+          f32x2 bias2 = pk2(fmaf(-slope, float(col0), base), fmaf(-slope, float(col0 + 1), base));
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 iv2f = *reinterpret_cast<const float2*>(iv + col0 + 2 * i);
-          const f32x2 iv2 = pk2(iv2f.x, iv2f.y);
-          f32x2 F2, g2;
-          const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-          if (rcp_shared(i, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, bias2, half2, F2, g2);
-          else            score_fg2<true, false>(acc2, scale2, bias2, half2, F2, g2);
-          bias2 = add2(bias2, step2);
-          F2 = mul2(F2, iv2);
-          g2 = mul2(g2, iv2);
-          float p0, p1;
-          upk2(F2, p0, p1);
-          if (diag) {                                        // queries before the key see nothing of it
-            float g0, g1;
-            upk2(g2, g0, g1);
-            if (col0 + 2 * i < r) { p0 = 0.f; g0 = 0.f; }
-            if (col0 + 2 * i + 1 < r) { p1 = 0.f; g1 = 0.f; }
-            g2 = pk2(g0, g1);
+          for (int i = 0; i < 16; ++i) {
+            const float2 iv2f = *reinterpret_cast<const float2*>(iv + col0 + 2 * i);
+            const f32x2 iv2 = pk2(iv2f.x, iv2f.y);
+            f32x2 F2, g2;
+            const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+            if (rcp_shared(i, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, bias2, half2, F2, g2);
+            else                                  score_fg2<true, false>(acc2, scale2, bias2, half2, F2, g2);
+            bias2 = add2(bias2, step2);
+            F2 = mul2(F2, iv2);
+            g2 = mul2(g2, iv2);
+            float p0, p1;
+            upk2(F2, p0, p1);
+            if constexpr (decltype(DIAG)::value) {            // queries before the key see nothing of it
+              float g0, g1;
+              upk2(g2, g0, g1);
+              if (col0 + 2 * i < r) { p0 = 0.f; g0 = 0.f; }
+              if (col0 + 2 * i + 1 < r) { p1 = 0.f; g1 = 0.f; }
+              g2 = pk2(g0, g1);
+            }
+            gq[16 * c + i] = g2;
+            preg[i] = Pack16<T>::pack(p0, p1);
           }
-          gq[16 * c + i] = g2;
-          preg[i] = Pack16<T>::pack(p0, p1);
+          tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
         }
-        tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
-      }
+      };
+      if (diag) phase_a(std::true_type{}); else phase_a(std::false_type{});
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full);
@@ -563,9 +573,407 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
 }
 
 
+// ------------------------------------------------------------------------------------- 4. fused d_k / d_v / d_q kernel
+// Key-major like kernel 3, but it also produces d_q, so the scores are recomputed once instead of twice
+// (5 GEMM-units per tile pair instead of 7).  Query tiles are 64 rows so that everything fits in TMEM:
+//   S^T (two buffers) [0,64) [64,128)   dP^T [128,192)   dV [192,320)   dK [320,448)   dQ^T [448,512)
+// dS^T goes to shared memory ([128 keys][64 queries], 16-bit): the same bytes are the K-major A operand of
+// dK += dS^T Q and the MN-major B operand of dQ^T = K^T dS^T ([128 d] x [64 queries], K as MN-major A).
+// Four extra warps drain dQ^T (transposing through shared memory) into a float32 accumulator in global
+// memory with TMA reduce-add; key tiles of one head add into the same rows, so the order of those additions
+// (and with it the last bits of d_q) varies from run to run.  D = 128 only.
+constexpr int QH = 64;                                  // query rows per step
+constexpr int kQStages = 3, kDoStages = 2;
+constexpr int kFusedDrainWarp = 4 * kEwGroups;          // warps 8..11 drain dQ^T
+constexpr int kFusedTmaWarp = kFusedDrainWarp + 4;
+// Two MMA issuer warps: X drives the chain that depends on phase A (dV, next S^T), Y the chain that depends on
+// phase B (next dP^T, dK, dQ^T).  One in-order issuer would make each chain wait for the other's barrier.
+constexpr int kFusedMmaWarpX = kFusedTmaWarp + 1, kFusedMmaWarpY = kFusedTmaWarp + 2;
+constexpr int kFusedThreads = (kFusedMmaWarpY + 1) * 32;
+
+template <int D>
+struct FusedSmem {
+  static constexpr int kKvBytes = BLK * D * 2, kQhBytes = QH * D * 2, kDsBytes = BLK * QH * 2;
+  alignas(1024) unsigned char k[kKvBytes];
+  alignas(1024) unsigned char v[kKvBytes];
+  alignas(1024) unsigned char q[kQStages][kQhBytes];        // q[0..1] double as d_v staging in the epilogue
+  alignas(1024) unsigned char dout[kDoStages][kQhBytes];    // d_k staging in the epilogue
+  alignas(1024) unsigned char ds[2][kDsBytes];
+  alignas(1024) float dq_stage[QH * D];
+  alignas(16) float delta[kQStages][QH];
+  alignas(16) float inv[kQStages][QH];
+  uint64_t kv_full, q_full[kQStages], q_empty[kQStages], do_full[kDoStages], do_empty[kDoStages];
+  uint64_t s_full[2], p_full[2], dp_full, ds_full[2], ds_empty[2], dq_full, dq_free, acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct FusedMaps { CUtensorMap qh, doh, k, v, dk, dv, dq_acc; };    // qh / doh: 64-row boxes
+
+template <int D>
+__device__ __forceinline__ void load_half_tile(unsigned char* dst, const CUtensorMap* m, uint64_t* bar, int row0, int h, int b) {
+#pragma unroll
+  for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + c * (QH * 128), m, bar, c * 64, row0, h, b);
+}
+
 template <typename T, int D>
-int launch_bwd(const AttnParams& p, cudaStream_t st) {
+__global__ void __launch_bounds__(kFusedThreads, 1)
+attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParams p) {
+  static_assert(D == 128 && kEwGroups == 2, "the fused backward is laid out for D = 128 and two element-wise warpgroups");
+  extern __shared__ unsigned char smem_raw[];
+  using S = FusedSmem<D>;
+  S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int b = blockIdx.z, h = blockIdx.y, kt = blockIdx.x;
+  const int q_begin = kt * BLK;                              // first query that sees this key tile (causal)
+  const int n = (p.T - q_begin + QH - 1) / QH;               // 64-row query steps
+  Guard g{&sm.abort_flag, p.status};
+  FAT_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.kv_full, 1); mbar_init(&sm.dp_full, 1); mbar_init(&sm.dq_full, 1); mbar_init(&sm.dq_free, 128);
+    mbar_init(&sm.acc_full, 2);                               // both issuers
+    for (int i = 0; i < kQStages; ++i) { mbar_init(&sm.q_full[i], 1); mbar_init(&sm.q_empty[i], 2); }
+    for (int i = 0; i < kDoStages; ++i) { mbar_init(&sm.do_full[i], 1); mbar_init(&sm.do_empty[i], 2); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.s_full[i], 1); mbar_init(&sm.p_full[i], kEwThreads);
+      mbar_init(&sm.ds_full[i], kEwThreads); mbar_init(&sm.ds_empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == kFusedTmaWarp) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tS0 = tmem, tP = tmem + 2 * QH, tV = tmem + 3 * QH, tK = tV + D, tQ = tK + D;
+
+  if (warp == kFusedTmaWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      mbar_expect_tx(&sm.kv_full, 2 * S::kKvBytes);
+      load_tile_tma_noexpect<D>(sm.k, &maps.k, &sm.kv_full, kt * BLK, h, b);
+      load_tile_tma_noexpect<D>(sm.v, &maps.v, &sm.kv_full, kt * BLK, h, b);
+      const float* delta_bh = p.delta + (int64_t(b) * p.H + h) * pad_rows(p.T);
+      const float* inv_bh = delta_bh + int64_t(p.B) * p.H * pad_rows(p.T);
+      for (int i = 0; i < n; ++i) {
+        const int qs = i % kQStages, ds = i % kDoStages, row0 = q_begin + i * QH;
+        if (!g.wait(&sm.q_empty[qs], ((i / kQStages) & 1) ^ 1, 100)) break;
+        mbar_expect_tx(&sm.q_full[qs], S::kQhBytes + 2 * QH * 4);
+        load_half_tile<D>(sm.q[qs], &maps.qh, &sm.q_full[qs], row0, h, b);
+        bulk_load(sm.delta[qs], delta_bh + row0, QH * 4, &sm.q_full[qs]);
+        bulk_load(sm.inv[qs], inv_bh + row0, QH * 4, &sm.q_full[qs]);
+        if (!g.wait(&sm.do_empty[ds], ((i / kDoStages) & 1) ^ 1, 101)) break;
+        mbar_expect_tx(&sm.do_full[ds], S::kQhBytes);
+        load_half_tile<D>(sm.dout[ds], &maps.doh, &sm.do_full[ds], row0, h, b);
+      }
+    }
+  } else if (warp == kFusedMmaWarpX || warp == kFusedMmaWarpY) {
+    // ------------------------------------------------------------------ tensor-core issuers
+    if (elect_one()) {
+      constexpr int F = Pack16<T>::kFmt;
+      constexpr uint32_t idesc_s = idesc_f16(BLK, QH, F, 0, 0);           // S^T, dP^T: [128 keys] x [64 queries]
+      constexpr uint32_t idesc_acc = idesc_f16(BLK, D, F, 0, 1);          // dV, dK: B (dO / Q) MN-major
+      constexpr uint32_t idesc_dq = idesc_f16(BLK, QH, F, 1, 1);          // dQ^T: A = K (MN-major), B = dS^T (MN-major)
+      const uint64_t kd = desc_kmajor(sm.k), vd = desc_kmajor(sm.v), kd_mn = desc_mnmajor(sm.k);
+      uint64_t qd[kQStages], qd_mn[kQStages], dod[kDoStages], dod_mn[kDoStages], dsd_k[2], dsd_mn[2];
+      for (int i = 0; i < kQStages; ++i) {
+        qd[i] = smem_desc_sw128(smem_u32(sm.q[i]), 16, 1024);
+        qd_mn[i] = smem_desc_sw128(smem_u32(sm.q[i]), QH * 128, 1024);
+      }
+      for (int i = 0; i < kDoStages; ++i) {
+        dod[i] = smem_desc_sw128(smem_u32(sm.dout[i]), 16, 1024);
+        dod_mn[i] = smem_desc_sw128(smem_u32(sm.dout[i]), QH * 128, 1024);
+      }
+      for (int i = 0; i < 2; ++i) {
+        dsd_k[i] = smem_desc_sw128(smem_u32(sm.ds[i]), 16, 1024);
+        dsd_mn[i] = smem_desc_sw128(smem_u32(sm.ds[i]), BLK * 128, 1024);
+      }
+      // [128 keys] x [64 queries] = A (key-side tile, [128][D]) B^T (query-side half tile, [64][D]) over the head dimension
+      auto issue_st = [&](uint32_t d_tmem, uint64_t a, uint64_t bq) {
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s)
+          mma_ss(d_tmem, a + (((s / 4) * (BLK * 128) + (s % 4) * 32) >> 4), bq + (((s / 4) * (QH * 128) + (s % 4) * 32) >> 4),
+                 idesc_s, s > 0);
+      };
+      bool ok = g.wait(&sm.kv_full, 0, 110);
+      if (warp == kFusedMmaWarpX) {
+        // ---- issuer X: S^T two steps ahead, dV as soon as P^T is written
+        for (int i = 0; i < 2 && i < n && ok; ++i) {
+          if (!(ok = g.wait(&sm.q_full[i], 0, 111))) break;
+          tc_fence_after();
+          issue_st(tS0 + i * QH, kd, qd[i]);
+          mma_commit(&sm.s_full[i]);
+        }
+        for (int i = 0; i < n && ok; ++i) {
+          const int bf = i & 1, qs = i % kQStages, dst = i % kDoStages;
+          if (!(ok = g.wait(&sm.p_full[bf], (i >> 1) & 1, 113))) break;
+          TR_STAMP(128 + 16 * (i - 10) + 0, i >= 10 && i < 13);
+          if (!(ok = g.wait(&sm.do_full[dst], (i / kDoStages) & 1, 112))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int s = 0; s < QH / 16; ++s)       // dV += P^T dO   (A: packed P^T over S^T buffer bf, 64 queries = 4 K-steps)
+            mma_ts(tV, tS0 + bf * QH + uint32_t(32 * (s / 2) + 8 * (s % 2)), dod_mn[dst] + ((s * 2048) >> 4), idesc_acc, i > 0 || s > 0);
+          mma_commit(&sm.do_empty[dst]);          // X's share of releasing dO(i) ...
+          mma_commit(&sm.q_empty[qs]);            // ... and Q(i) (its S^T was issued two steps ago)
+          TR_STAMP(128 + 16 * (i - 10) + 1, i >= 10 && i < 13);
+          if (i + 2 < n) {                        // S^T two steps ahead into the buffer just consumed
+            const int qs2 = (i + 2) % kQStages;
+            if (!(ok = g.wait(&sm.q_full[qs2], ((i + 2) / kQStages) & 1, 114))) break;
+            tc_fence_after();
+            issue_st(tS0 + bf * QH, kd, qd[qs2]);
+            mma_commit(&sm.s_full[bf]);
+            TR_STAMP(128 + 16 * (i - 10) + 2, i >= 10 && i < 13);
+          }
+        }
+      } else {
+        // ---- issuer Y: dP^T one step ahead, then dK += dS^T Q and dQ^T = K^T dS^T from the shared-memory dS^T tile
+        if (ok && (ok = g.wait(&sm.do_full[0], 0, 112))) {
+          tc_fence_after();
+          issue_st(tP, vd, dod[0]);
+          mma_commit(&sm.dp_full);
+          mma_commit(&sm.do_empty[0]);
+        }
+        for (int i = 0; i < n && ok; ++i) {
+          const int bf = i & 1, qs = i % kQStages;
+          if (!(ok = g.wait(&sm.ds_full[bf], (i >> 1) & 1, 115))) break;    // phase B done: dS^T in smem, dP^T read
+          TR_STAMP(128 + 16 * (i - 10) + 3, i >= 10 && i < 13);
+          if (i + 1 < n) {
+            const int dst1 = (i + 1) % kDoStages;
+            if (!(ok = g.wait(&sm.do_full[dst1], ((i + 1) / kDoStages) & 1, 117))) break;
+            tc_fence_after();
+            issue_st(tP, vd, dod[dst1]);
+            mma_commit(&sm.dp_full);
+            mma_commit(&sm.do_empty[dst1]);       // Y's share of releasing dO(i+1)
+            TR_STAMP(128 + 16 * (i - 10) + 4, i >= 10 && i < 13);
+          }
+          if (!(ok = g.wait(&sm.q_full[qs], (i / kQStages) & 1, 118))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int s = 0; s < QH / 16; ++s)
+            mma_ss(tK, dsd_k[bf] + ((s * 32) >> 4), qd_mn[qs] + ((s * 2048) >> 4), idesc_acc, i > 0 || s > 0);
+          mma_commit(&sm.q_empty[qs]);            // Y's share of releasing Q(i)
+          if (i > 0 && !(ok = g.wait(&sm.dq_free, (i - 1) & 1, 116))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int s = 0; s < BLK / 16; ++s)
+            mma_ss(tQ, kd_mn + ((s * 2048) >> 4), dsd_mn[bf] + ((s * 2048) >> 4), idesc_dq, s > 0);
+          mma_commit(&sm.dq_full);
+          mma_commit(&sm.ds_empty[bf]);
+          TR_STAMP(128 + 16 * (i - 10) + 5, i >= 10 && i < 13);
+        }
+      }
+      if (ok) mma_commit(&sm.acc_full);
+    }
+  } else if (warp >= kFusedDrainWarp) {
+    // ------------------------------------------------------------------ dQ^T drain: TMEM -> smem (transposed) -> reduce-add
+    const int dl = tid - kFusedDrainWarp * 32;                // head-dimension index == TMEM lane
+    const uint32_t lane_base = uint32_t(warp & 3) * 32;
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
+      TR_BEGIN();
+      if (!(ok = g.wait(&sm.dq_full, i & 1, 120))) break;
+      TR_WAITED();
+      TR_STAMP(128 + 16 * (i - 10) + 11, dl == 0 && i >= 10 && i < 13);
+      tc_fence_after();
+      uint32_t a[32], c[32];
+      tmem_ld32(tmem_addr(tQ, lane_base, 0), a);
+      tmem_ld32(tmem_addr(tQ, lane_base, 32), c);
+      tmem_wait_ld_regs(a);
+      tmem_wait_ld_regs(c);
+      tc_fence_before();
+      mbar_arrive(&sm.dq_free);
+      if (dl == 0) tma_store_wait_read();                    // the previous reduce has finished reading the staging tile
+      named_barrier(3, 128);
+#pragma unroll
+      for (int qi = 0; qi < 32; ++qi) {
+        sm.dq_stage[qi * D + dl] = __uint_as_float(a[qi]);
+        sm.dq_stage[(qi + 32) * D + dl] = __uint_as_float(c[qi]);
+      }
+      fence_async_smem();
+      named_barrier(3, 128);
+      if (dl == 0) {
+        tma_reduce_add_4d(&maps.dq_acc, sm.dq_stage, 0, q_begin + i * QH, h, b);
+        tma_store_commit();
+      }
+      TR_WORKED();
+    }
+#ifdef FAT_TRACE
+    if (traced && dl == 0) { long long* o = trace + 40; o[0] = tr_wait; o[1] = tr_work; o[2] = clock64() - tr_t0; o[3] = n; }
+#endif
+    if (dl == 0) tma_store_wait_all();
+  } else {
+    // ------------------------------------------------------------------ element-wise warpgroups
+    const int w = warp >> 2;                                 // query columns [32w, 32w+32) of each step
+    const int r = tid & (BLK - 1);                           // key row inside the tile == TMEM lane
+    const int key = kt * BLK + r;
+    const uint32_t lane_base = uint32_t(warp & 3) * 32;
+    const float slope = p.slopes[h], scale = p.scale;
+    const f32x2 scale2 = pk2(scale, scale), one2 = pk2(1.0f, 1.0f), step2 = pk2(-2.f * slope, -2.f * slope);
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
+      const int bf = i & 1, qs = i % kQStages;
+      const uint32_t bph = (i >> 1) & 1;
+      const bool diag = i < 2;                               // the first two steps straddle the diagonal
+      const int col0 = 32 * w;                               // first query column of this thread inside the step
+      f32x2 gq[16];
+      // ---- phase A
+      TR_BEGIN();
+      if (!(ok = g.wait(&sm.q_full[qs], (i / kQStages) & 1, 130))) break;
+      if (!(ok = g.wait(&sm.s_full[bf], bph, 131))) break;
+      TR_WAITED();
+      TR_STAMP(128 + 16 * (i - 10) + 6, tid == 0 && i >= 10 && i < 13);
+      tc_fence_after();
+      auto phase_a = [&](auto DIAG) {          // the diagonal steps get their own copy (no run-time test in the unrolled body)
+        uint32_t sreg[32], preg[16];
+        tmem_ld32(tmem_addr(tS0 + bf * QH, lane_base, col0), sreg);
+        tmem_wait_ld_regs(sreg);
+        const float base = slope * float(key - (q_begin + i * QH));          // bias of query column 0 of the step
+        f32x2 bias2 = pk2(fmaf(-slope, float(col0), base), fmaf(-slope, float(col0 + 1), base));
+        const float* iv = sm.inv[qs];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float2 ivf = *reinterpret_cast<const float2*>(iv + col0 + 2 * e);
+          const f32x2 iv2 = pk2(ivf.x, ivf.y);
+          const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * e]), __uint_as_float(sreg[2 * e + 1]));
+          f32x2 F2, g2;
+          if (rcp_shared(e, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, bias2, one2, F2, g2);
+          else                                  score_fg2<true, false>(acc2, scale2, bias2, one2, F2, g2);
+          bias2 = add2(bias2, step2);
+          F2 = mul2(F2, iv2);
+          g2 = mul2(g2, iv2);
+          float p0, p1;
+          upk2(F2, p0, p1);
+          if constexpr (decltype(DIAG)::value) {            // queries before the key see nothing of it
+            float g0, g1;
+            upk2(g2, g0, g1);
+            if (i * QH + col0 + 2 * e < r) { p0 = 0.f; g0 = 0.f; }
+            if (i * QH + col0 + 2 * e + 1 < r) { p1 = 0.f; g1 = 0.f; }
+            g2 = pk2(g0, g1);
+          }
+          gq[e] = g2;
+          preg[e] = Pack16<T>::pack(p0, p1);
+        }
+        tmem_st16(tmem_addr(tS0 + bf * QH, lane_base, col0), preg);
+      };
+      if (diag) phase_a(std::true_type{}); else phase_a(std::false_type{});
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.p_full[bf]);
+      TR_WORKED();
+      TR_STAMP(128 + 16 * (i - 10) + 7, tid == 0 && i >= 10 && i < 13);
+      // ---- phase B
+      if (!(ok = g.wait(&sm.dp_full, i & 1, 132))) break;
+      TR_STAMP(128 + 16 * (i - 10) + 8, tid == 0 && i >= 10 && i < 13);
+      if (!(ok = g.wait(&sm.ds_empty[bf], bph ^ 1, 133))) break;
+      TR_WAITED2();
+      TR_STAMP(128 + 16 * (i - 10) + 9, tid == 0 && i >= 10 && i < 13);
+      tc_fence_after();
+      {
+        uint32_t dreg[32], preg[16];
+        tmem_ld32(tmem_addr(tP, lane_base, col0), dreg);
+        tmem_wait_ld_regs(dreg);
+        const float* dl = sm.delta[qs];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float2 d2 = *reinterpret_cast<const float2*>(dl + col0 + 2 * e);
+          const f32x2 ds2 = mul2(gq[e], add2(pk2(__uint_as_float(dreg[2 * e]), __uint_as_float(dreg[2 * e + 1])), pk2(-d2.x, -d2.y)));
+          float d0, d1;
+          upk2(ds2, d0, d1);
+          preg[e] = Pack16<T>::pack(d0, d1);
+        }
+#pragma unroll
+        for (int sgm = 0; sgm < 4; ++sgm)
+          *reinterpret_cast<uint4*>(sm.ds[bf] + sw128_offset(r, 4 * w + sgm)) =
+              make_uint4(preg[4 * sgm], preg[4 * sgm + 1], preg[4 * sgm + 2], preg[4 * sgm + 3]);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&sm.ds_full[bf]);
+      TR_WORKED2();
+      TR_STAMP(128 + 16 * (i - 10) + 10, tid == 0 && i >= 10 && i < 13);
+    }
+#ifdef FAT_TRACE
+    if (traced && (tid & 127) == 0) { long long* o = trace + 16 + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
+#endif
+    if (ok) ok = g.wait(&sm.acc_full, 0, 134);
+    named_barrier(1, kEwThreads);
+    if (!g.aborted()) {
+      // d_v (staged in q[0..1]) and d_k (staged in dout[0..1]); the multipliers undo the 16x (F16) and 8x (g8) units
+      tc_fence_after();
+      for (int ch = w; ch < 2 * D / 32; ch += kEwGroups) {
+        const bool is_dk = ch >= D / 32;
+        const int c0 = (is_dk ? ch - D / 32 : ch) * 32;
+        uint32_t oreg[32];
+        tmem_ld32(tmem_addr(is_dk ? tK : tV, lane_base, c0), oreg);
+        tmem_wait_ld_regs(oreg);
+        stage_row32<T>(is_dk ? sm.dout[0] : sm.q[0], r, c0, oreg, is_dk ? 0.25f * scale / kOpScale : 0.0625f / kOpScale);
+      }
+      fence_async_smem();
+      named_barrier(1, kEwThreads);
+      if (tid == 0) {
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_store_4d(&maps.dv, sm.q[0] + c * (BLK * 128), c * 64, kt * BLK, h, b);
+          tma_store_4d(&maps.dk, sm.dout[0] + c * (BLK * 128), c * 64, kt * BLK, h, b);
+        }
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kFusedTmaWarp) tmem_dealloc(tmem, kTmemCols);
+}
+
+// d_q = round(dq_acc * mul): float32 accumulator (dense [B,H,T,D]) -> tensor dtype with the caller's strides.
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+attn_bwd_dq_convert_kernel(const AttnParams p, const float* __restrict__ dq_acc, float mul) {
+  const int64_t n_packs = int64_t(p.B) * p.H * p.T * (D / 8);
+  T* dq = static_cast<T*>(p.d_q);
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_packs; i += int64_t(gridDim.x) * blockDim.x) {
+    const int c = int(i % (D / 8)) * 8;
+    const int64_t row = i / (D / 8);
+    const int t = int(row % p.T);
+    const int64_t bh = row / p.T;
+    const int h = int(bh % p.H), b = int(bh / p.H);
+    const float4 lo = __ldcs(reinterpret_cast<const float4*>(dq_acc + row * D + c));
+    const float4 hi = __ldcs(reinterpret_cast<const float4*>(dq_acc + row * D + c + 4));
+    const float v[8] = {lo.x * mul, lo.y * mul, lo.z * mul, lo.w * mul, hi.x * mul, hi.y * mul, hi.z * mul, hi.w * mul};
+    store_pack<T, 8>(dq + b * p.dqs[0] + h * p.dqs[1] + int64_t(t) * p.dqs[2] + c, v);
+  }
+}
+
+size_t stats_bytes(int B, int H, int T) { return (2 * size_t(B) * H * pad_rows(T) * sizeof(float) + 1023) / 1024 * 1024; }
+
+template <typename T, int D>
+int launch_prepare(const AttnParams& p, cudaStream_t st) {
   float* inv_rows = p.delta + int64_t(p.B) * p.H * pad_rows(p.T);
+  constexpr int RPW = 32 / (D / 8);
+  const int64_t rows = int64_t(p.B) * p.H * pad_rows(p.T);
+  int64_t blocks = (rows + RPW * 8 - 1) / (RPW * 8);
+  if (blocks > 16 * kNumSM) blocks = 16 * kNumSM;
+  attn_bwd_prepare_kernel<T, D><<<unsigned(blocks), 256, 0, st>>>(p, inv_rows);
+  return check_launch("attn_bwd_prepare");
+}
+
+template <typename Kern, typename Maps>
+int launch_main(Kern kern, const Maps& maps, const AttnParams& p, size_t smem, int threads, cudaStream_t st, const char* what) {
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+    set_error("%s: cannot reserve %zu bytes of shared memory", what, smem);
+    return FAT_ERR_LAUNCH;
+  }
+  dim3 grid((p.T + BLK - 1) / BLK, p.H, p.B);
+  kern<<<grid, threads, smem, st>>>(maps, p);
+  return check_launch(what);
+}
+
+// Deterministic backward: prepare, query-major d_q kernel, key-major d_k/d_v kernel.
+template <typename T, int D>
+int launch_bwd_split(const AttnParams& p, cudaStream_t st) {
   DqMaps mq;
   DkvMaps mk;
   if (!make_tmap_bhtd(&mq.q, p.q, p.B, p.H, p.T, D, p.qs, 64, BLK) ||
@@ -577,48 +985,52 @@ int launch_bwd(const AttnParams& p, cudaStream_t st) {
       !make_tmap_bhtd(&mk.dv, p.d_v, p.B, p.H, p.T, D, p.dvs, 64, BLK))
     return FAT_ERR_LAUNCH;
   mk.q = mq.q; mk.dout = mq.dout; mk.k = mq.k; mk.v = mq.v;
+  if (int rc = launch_prepare<T, D>(p, st)) return rc;
+  if (int rc = launch_main(attn_bwd_dq_tc_kernel<T, D>, mq, p, sizeof(DqSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dq_tc")) return rc;
+  return launch_main(attn_bwd_dkv_tc_kernel<T, D>, mk, p, sizeof(DkvSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dkv_tc");
+}
 
-  {   // 1. prepare
-    constexpr int RPW = 32 / (D / 8);
-    const int64_t rows = int64_t(p.B) * p.H * pad_rows(p.T);
-    int64_t blocks = (rows + RPW * 8 - 1) / (RPW * 8);
-    if (blocks > 16 * kNumSM) blocks = 16 * kNumSM;
-    attn_bwd_prepare_kernel<T, D><<<unsigned(blocks), 256, 0, st>>>(p, inv_rows);
-    if (int rc = check_launch("attn_bwd_prepare")) return rc;
-  }
-  const int tiles = (p.T + BLK - 1) / BLK;
-  dim3 grid(tiles, p.H, p.B);
-  {   // 2. d_q
-    auto kern = attn_bwd_dq_tc_kernel<T, D>;
-    const size_t smem = sizeof(DqSmem<D>) + 1024;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-      set_error("attn_bwd_dq_tc: cannot reserve %zu bytes of shared memory", smem); return FAT_ERR_LAUNCH;
-    }
-    kern<<<grid, kBwdThreads, smem, st>>>(mq, p);
-    if (int rc = check_launch("attn_bwd_dq_tc")) return rc;
-  }
-  {   // 3. d_k, d_v
-    auto kern = attn_bwd_dkv_tc_kernel<T, D>;
-    const size_t smem = sizeof(DkvSmem<D>) + 1024;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-      set_error("attn_bwd_dkv_tc: cannot reserve %zu bytes of shared memory", smem); return FAT_ERR_LAUNCH;
-    }
-    kern<<<grid, kBwdThreads, smem, st>>>(mk, p);
-    if (int rc = check_launch("attn_bwd_dkv_tc")) return rc;
-  }
-  return FAT_OK;
+// Fused backward (D = 128): prepare, clear the float32 d_q accumulator, fused kernel, convert d_q.
+template <typename T>
+int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
+  constexpr int D = 128;
+  float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.delta) + stats_bytes(p.B, p.H, p.T));
+  const size_t acc_bytes = size_t(p.B) * p.H * p.T * D * sizeof(float);
+  FusedMaps m;
+  if (!make_tmap_bhtd(&m.qh, p.q, p.B, p.H, p.T, D, p.qs, 64, QH) ||
+      !make_tmap_bhtd(&m.doh, p.d_out, p.B, p.H, p.T, D, p.dos, 64, QH) ||
+      !make_tmap_bhtd(&m.k, p.k, p.B, p.H, p.T, D, p.ks, 64, BLK) ||
+      !make_tmap_bhtd(&m.v, p.v, p.B, p.H, p.T, D, p.vs, 64, BLK) ||
+      !make_tmap_bhtd(&m.dk, p.d_k, p.B, p.H, p.T, D, p.dks, 64, BLK) ||
+      !make_tmap_bhtd(&m.dv, p.d_v, p.B, p.H, p.T, D, p.dvs, 64, BLK) ||
+      !make_tmap_bhtd_f32(&m.dq_acc, dq_acc, p.B, p.H, p.T, D, D, QH))
+    return FAT_ERR_LAUNCH;
+  if (int rc = launch_prepare<T, D>(p, st)) return rc;
+  if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) { set_error("attn_bwd_fused: clearing the d_q accumulator failed"); return FAT_ERR_LAUNCH; }
+  if (int rc = launch_main(attn_bwd_fused_tc_kernel<T, D>, m, p, sizeof(FusedSmem<D>) + 1024, kFusedThreads, st, "attn_bwd_fused_tc")) return rc;
+  const int64_t packs = int64_t(p.B) * p.H * p.T * (D / 8);
+  int64_t blocks = (packs + 255) / 256;
+  if (blocks > 16 * kNumSM) blocks = 16 * kNumSM;
+  attn_bwd_dq_convert_kernel<T, D><<<unsigned(blocks), 256, 0, st>>>(p, dq_acc, 0.25f * p.scale / kOpScale);
+  return check_launch("attn_bwd_dq_convert");
+}
+
+template <typename T>
+int launch_bwd(const AttnParams& p, cudaStream_t st) {
+  if (p.D == 128) return p.deterministic ? launch_bwd_split<T, 128>(p, st) : launch_bwd_fused<T>(p, st);
+  return launch_bwd_split<T, 64>(p, st);
 }
 
 }  // namespace
 
 size_t attn_bwd_tc_workspace_bytes(int B, int H, int T, int D) {
-  (void)D;
-  return 2 * size_t(B) * H * pad_rows(T) * sizeof(float);      // Delta and 1/(L+eps), rows padded to whole tiles
+  // Delta and 1/(L+eps) (rows padded to whole tiles), then the float32 d_q accumulator of the fused kernel
+  return stats_bytes(B, H, T) + (D == 128 ? size_t(B) * H * T * D * sizeof(float) : 0);
 }
 
 int attn_bwd_tc(const AttnParams& p, int dtype, cudaStream_t st) {
-  if (dtype == FAT_BF16) return p.D == 128 ? launch_bwd<__nv_bfloat16, 128>(p, st) : launch_bwd<__nv_bfloat16, 64>(p, st);
-  if (dtype == FAT_F16) return p.D == 128 ? launch_bwd<__half, 128>(p, st) : launch_bwd<__half, 64>(p, st);
+  if (dtype == FAT_BF16) return launch_bwd<__nv_bfloat16>(p, st);
+  if (dtype == FAT_F16) return launch_bwd<__half>(p, st);
   set_error("attn_bwd_tc: unsupported dtype tag %d", dtype);
   return FAT_ERR_DTYPE;
 }

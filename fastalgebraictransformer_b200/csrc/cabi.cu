@@ -45,7 +45,7 @@ void copy3(int64_t (&dst)[3], const int64_t* src) { dst[0] = src[0]; dst[1] = sr
 int resolve_path(const char* what, int path, int T, int D, int dtype, bool aligned, bool causal, bool backward) {
   const bool ok = attn_tc_eligible(T, D, dtype, aligned, causal, backward);
   if (path == FAT_PATH_SIMT) return FAT_PATH_SIMT;
-  if (path == FAT_PATH_TENSOR) {
+  if (path == FAT_PATH_TENSOR || path == FAT_PATH_TENSOR_DETERMINISTIC) {
     if (!ok) {
       set_error("%s: the tensor-core path needs bf16/f16, D in {64,128}, causal masking, 16-byte aligned pointers and "
                 "strides (got dtype %d, D=%d, causal=%d, aligned=%d)", what, dtype, D, int(causal), int(aligned));
@@ -154,6 +154,7 @@ int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, c
   copy3(p.qs, qs); copy3(p.ks, ks); copy3(p.vs, vs); copy3(p.os, os); copy3(p.dos, dos);
   copy3(p.dqs, dqs); copy3(p.dks, dks); copy3(p.dvs, dvs);
   p.scale = float(scale); p.eps = float(eps); p.causal = causal != 0; p.status = status;
+  p.deterministic = path == FAT_PATH_TENSOR_DETERMINISTIC;
 #ifdef FAT_TRACE
   p.dq_acc = static_cast<float*>(g_trace);
 #endif

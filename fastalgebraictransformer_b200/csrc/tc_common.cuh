@@ -83,6 +83,12 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* s
       "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
       ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+// Element-wise add of a shared-memory tile into global memory (performed in L2).  Coordinates must not be negative.
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
@@ -203,5 +209,7 @@ __device__ __forceinline__ bool elect_one() {
 // Returns false (and sets the library error string) when the driver rejects the description.
 bool make_tmap_bhtd(CUtensorMap* out, const void* base, int B, int H, int T, int D,
                     const int64_t* strides_bht, int box_d, int box_t);
+// Same for a dense float32 [B,H,T,D] tensor, no swizzle (box rows are plain row-major in shared memory).
+bool make_tmap_bhtd_f32(CUtensorMap* out, const void* base, int B, int H, int T, int D, int box_d, int box_t);
 
 }  // namespace fat

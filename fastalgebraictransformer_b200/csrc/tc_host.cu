@@ -54,4 +54,23 @@ bool make_tmap_bhtd(CUtensorMap* out, const void* base, int B, int H, int T, int
   return true;
 }
 
+bool make_tmap_bhtd_f32(CUtensorMap* out, const void* base, int B, int H, int T, int D, int box_d, int box_t) {
+  static thread_local bool bound = false;
+  if (!bound) { cudaFree(nullptr); bound = true; }
+  EncodeFn fn = encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return false; }
+  const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(T), cuuint64_t(H), cuuint64_t(B)};
+  const cuuint64_t strides[3] = {cuuint64_t(D) * 4, cuuint64_t(D) * T * 4, cuuint64_t(D) * T * H * 4};
+  const cuuint32_t box[4] = {cuuint32_t(box_d), cuuint32_t(box_t), 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (float32) failed with code %d (dims %d,%d,%d,%d box %d,%d)", int(r), D, T, H, B, box_d, box_t);
+    return false;
+  }
+  return true;
+}
+
 }  // namespace fat

@@ -166,6 +166,28 @@ def test_deterministic():
     assert all(torch.equal(x, y) for x, y in zip(a, b))
 
 
+def test_deterministic_tensor_path_d128():
+    """D=128: the default backward accumulates d_q across key tiles with reduce-adds (order varies between runs, so its
+    last bits may); path 3 selects the two-kernel backward, which is bit-reproducible."""
+    from fastalgebraictransformer_b200 import PATH_TENSOR_DETERMINISTIC
+    B, H, T, D = 1, 4, 700, 128
+    q, k, v, go = gen_qkv(29, B, H, T, D, torch.bfloat16)
+    slopes = oracle.compute_alibi_slopes(H)
+    a = run_attention(q, k, v, go, slopes, 0.09, path=PATH_TENSOR_DETERMINISTIC)
+    b = run_attention(q, k, v, go, slopes, 0.09, path=PATH_TENSOR_DETERMINISTIC)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    c = run_attention(q, k, v, go, slopes, 0.09)              # fused backward
+    for x, y, name in zip(a, c, ("out", "dq", "dk", "dv")):
+        if name == "out":
+            assert torch.equal(x, y)
+        else:
+            assert norm_max_err(x.float(), y.float().cpu()) < 1e-2, name
+    want = oracle.rational_attention_grads(q.float(), k.float(), v.float(), go.float(), slopes, 0.09)
+    for got, w, name in zip(c, want, ("out", "dq", "dk", "dv")):
+        bad, nme = bf16_violations(got.float(), w)
+        assert bad < 5e-3 and nme < 1.5e-2, f"{name}: {bad:.2e} outside the bar (norm max err {nme:.2e})"
+
+
 def test_tensor_core_path_agrees_with_cuda_core_path():
     """The two kernel families against each other on the device (bf16, D=128, ragged T)."""
     B, H, T, D = 2, 4, 777, 128
@@ -197,8 +219,11 @@ def test_config2_slice_bf16():
     scale = 1.0 / math.sqrt(D)
     full = run_attention(q, k, v, go, slopes, scale)
     one = run_attention(q[1:], k[1:], v[1:], go[1:], slopes, scale)
-    for a, b in zip(full, one):
-        assert torch.equal(a[1:], b)
+    for a, b, name in zip(full, one, ("out", "dq", "dk", "dv")):
+        if name == "dq":     # D=128: float32 reduce-adds across key tiles in an unordered sequence (last-bit differences)
+            assert (a[1:] != b).float().mean().item() < 1e-2 and norm_max_err(a[1:].float(), b.float().cpu()) < 1e-2
+        else:
+            assert torch.equal(a[1:], b), name
     want = oracle.rational_attention_grads(q[:1, :2].float(), k[:1, :2].float(), v[:1, :2].float(), go[:1, :2].float(),
                                            slopes[:2], scale)
     got = run_attention(q[:1, :2], k[:1, :2], v[:1, :2], go[:1, :2], slopes[:2], scale)
