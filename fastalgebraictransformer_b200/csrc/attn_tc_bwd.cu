@@ -1,6 +1,8 @@
 // Causal rational attention backward on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
 //
-// Three launches, no atomics, bit-reproducible:
+// Default for D = 128: prepare (1), a float32 d_q accumulator cleared with a memset, the fused key-major
+// kernel (4) that produces d_k, d_v and adds its d_q contributions with TMA reduce-add, and a convert pass.
+// Deterministic variant (and D = 64): three launches, no atomics, bit-reproducible:
 //   1. prepare:  per query row  inv = 1/(L+eps) and Delta = dO . O  (two padded float32 arrays)
 //   2. d_q kernel, query-major (one 128-query tile per CTA, key tiles streamed):
 //                S = Q K^T, dP = dO V^T -> dS = g inv (dP - Delta) (16-bit, packed into TMEM over dP)
@@ -574,72 +576,68 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
 
 
 // ------------------------------------------------------------------------------------- 4. fused d_k / d_v / d_q kernel
-// Key-major like kernel 3, but it also produces d_q, so the scores are recomputed once instead of twice
-// (5 GEMM-units per tile pair instead of 7).  Query tiles are 64 rows so that everything fits in TMEM:
-//   S^T (two buffers) [0,64) [64,128)   dP^T [128,192)   dV [192,320)   dK [320,448)   dQ^T [448,512)
-// dS^T goes to shared memory ([128 keys][64 queries], 16-bit): the same bytes are the K-major A operand of
-// dK += dS^T Q and the MN-major B operand of dQ^T = K^T dS^T ([128 d] x [64 queries], K as MN-major A).
-// Four extra warps drain dQ^T (transposing through shared memory) into a float32 accumulator in global
-// memory with TMA reduce-add; key tiles of one head add into the same rows, so the order of those additions
-// (and with it the last bits of d_q) varies from run to run.  D = 128 only.
-constexpr int QH = 64;                                  // query rows per step
-constexpr int kQStages = 3, kDoStages = 2;
-constexpr int kFusedDrainWarp = 4 * kEwGroups;          // warps 8..11 drain dQ^T
-constexpr int kFusedTmaWarp = kFusedDrainWarp + 4;
-// Two MMA issuer warps: X drives the chain that depends on phase A (dV, next S^T), Y the chain that depends on
-// phase B (next dP^T, dK, dQ^T).  One in-order issuer would make each chain wait for the other's barrier.
-constexpr int kFusedMmaWarpX = kFusedTmaWarp + 1, kFusedMmaWarpY = kFusedTmaWarp + 2;
-constexpr int kFusedThreads = (kFusedMmaWarpY + 1) * 32;
+// Key-major: one CTA owns a 128-key tile and walks the 128-query tiles that see it.  Every GEMM is a full
+// 128x128x128 (tcgen05.mma below N = 128 runs at about half rate).  TMEM is exactly full:
+//   R1 [0,128)    S^T, then the packed P^T over it         R2 [128,256)  dP^T, then dQ^T over it
+//   dV [256,384)  dK [384,512)
+// dS^T goes to shared memory ([128 keys][128 queries], 16-bit): K-major A operand of dK += dS^T Q and MN-major B
+// operand of dQ^T = K^T dS^T.  Four drain warps move dQ^T (head dimension on the TMEM lanes) through shared
+// memory, transposed, into a float32 accumulator in global memory with TMA reduce-add, 64 query rows at a time.
+// dO has a single buffer: dO(i+1) is only needed once dQ^T(i) has been drained, long after dV(i) released dO(i).
+// The element-wise warps keep g for 64 score columns in registers between phase A and phase B, which needs
+// about 168 registers per thread; the other warps need far fewer, so the warpgroups trade registers with
+// setmaxnreg (the launch allocates 512 x 128).
+constexpr int kFusedDrainWarp = 8, kFusedTmaWarp = 12, kFusedMmaWarpX = 13, kFusedMmaWarpY = 14, kFusedThreads = 512;
+constexpr int kFusedRegsLaunch = 128, kFusedRegsEw = 168, kFusedRegsDrain = 104, kFusedRegsAux = 64;
+static_assert(256 * kFusedRegsEw + 128 * kFusedRegsDrain + 128 * kFusedRegsAux <= kFusedThreads * kFusedRegsLaunch,
+              "the warpgroups' register shares must fit in what the launch allocates");
+
+template <int N> __device__ __forceinline__ void reg_share_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_share_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 template <int D>
 struct FusedSmem {
-  static constexpr int kKvBytes = BLK * D * 2, kQhBytes = QH * D * 2, kDsBytes = BLK * QH * 2;
-  alignas(1024) unsigned char k[kKvBytes];
-  alignas(1024) unsigned char v[kKvBytes];
-  alignas(1024) unsigned char q[kQStages][kQhBytes];        // q[0..1] double as d_v staging in the epilogue
-  alignas(1024) unsigned char dout[kDoStages][kQhBytes];    // d_k staging in the epilogue
-  alignas(1024) unsigned char ds[2][kDsBytes];
-  alignas(1024) float dq_stage[QH * D];
-  alignas(16) float delta[kQStages][QH];
-  alignas(16) float inv[kQStages][QH];
-  uint64_t kv_full, q_full[kQStages], q_empty[kQStages], do_full[kDoStages], do_empty[kDoStages];
-  uint64_t s_full[2], p_full[2], dp_full, ds_full[2], ds_empty[2], dq_full, dq_free, acc_full;
+  static constexpr int kTileBytes = BLK * D * 2;
+  alignas(1024) unsigned char k[kTileBytes];
+  alignas(1024) unsigned char v[kTileBytes];
+  alignas(1024) unsigned char q[2][kTileBytes];             // q[0] doubles as d_v staging in the epilogue
+  alignas(1024) unsigned char dout[kTileBytes];             // doubles as d_k staging in the epilogue
+  alignas(1024) unsigned char ds[kTileBytes];               // dS^T, 16-bit [128 keys][128 queries]
+  alignas(1024) float dq_stage[64 * D];                     // d_q staging tile [64 query rows][D]
+  alignas(16) float delta[2][BLK];
+  alignas(16) float inv[2][BLK];
+  uint64_t kv_full, q_full[2], q_empty[2], do_full, do_empty;
+  uint64_t s_full, p_full, dp_full, ds_full, dq_full, dq_free, acc_full;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-struct FusedMaps { CUtensorMap qh, doh, k, v, dk, dv, dq_acc; };    // qh / doh: 64-row boxes
-
-template <int D>
-__device__ __forceinline__ void load_half_tile(unsigned char* dst, const CUtensorMap* m, uint64_t* bar, int row0, int h, int b) {
-#pragma unroll
-  for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + c * (QH * 128), m, bar, c * 64, row0, h, b);
-}
+struct FusedMaps { CUtensorMap q, dout, k, v, dk, dv, dq_acc; };    // dq_acc: float32, 32-row boxes
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kFusedThreads, 1)
 attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParams p) {
-  static_assert(D == 128 && kEwGroups == 2, "the fused backward is laid out for D = 128 and two element-wise warpgroups");
-  extern __shared__ unsigned char smem_raw[];
+  static_assert(D == 128 && kEwGroups == 2, "laid out for D = 128 and two element-wise warpgroups");
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   using S = FusedSmem<D>;
-  S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  S& sm = *reinterpret_cast<S*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int b = blockIdx.z, h = blockIdx.y, kt = blockIdx.x;
-  const int q_begin = kt * BLK;                              // first query that sees this key tile (causal)
-  const int n = (p.T - q_begin + QH - 1) / QH;               // 64-row query steps
+  const int n_q_total = (p.T + BLK - 1) / BLK;
+  const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
   Guard g{&sm.abort_flag, p.status};
   FAT_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+  if ((smem_u32(smem_raw) & 1023u) != 0) {                   // the swizzled tiles need a 1024-byte aligned base
+    if (tid == 0 && p.status) atomicOr(p.status, 0x40000000);
+    return;                                                  // uniform: nobody has touched a barrier or TMEM yet
+  }
 
   if (tid == 0) {
     sm.abort_flag = 0;
-    mbar_init(&sm.kv_full, 1); mbar_init(&sm.dp_full, 1); mbar_init(&sm.dq_full, 1); mbar_init(&sm.dq_free, 128);
-    mbar_init(&sm.acc_full, 2);                               // both issuers
-    for (int i = 0; i < kQStages; ++i) { mbar_init(&sm.q_full[i], 1); mbar_init(&sm.q_empty[i], 2); }
-    for (int i = 0; i < kDoStages; ++i) { mbar_init(&sm.do_full[i], 1); mbar_init(&sm.do_empty[i], 2); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&sm.s_full[i], 1); mbar_init(&sm.p_full[i], kEwThreads);
-      mbar_init(&sm.ds_full[i], kEwThreads); mbar_init(&sm.ds_empty[i], 1);
-    }
+    mbar_init(&sm.kv_full, 1); mbar_init(&sm.s_full, 1); mbar_init(&sm.p_full, kEwThreads); mbar_init(&sm.dp_full, 1);
+    mbar_init(&sm.ds_full, kEwThreads); mbar_init(&sm.dq_full, 1);
+    mbar_init(&sm.dq_free, 128); mbar_init(&sm.acc_full, 2); mbar_init(&sm.do_full, 1); mbar_init(&sm.do_empty, 2);
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.q_full[i], 1); mbar_init(&sm.q_empty[i], 1); }
     mbar_fence_init();
   }
   if (warp == kFusedTmaWarp) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
@@ -647,156 +645,168 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t tS0 = tmem, tP = tmem + 2 * QH, tV = tmem + 3 * QH, tK = tV + D, tQ = tK + D;
+  const uint32_t tS = tmem, tP = tmem + BLK, tV = tmem + 2 * BLK, tK = tmem + 3 * BLK;
 
-  if (warp == kFusedTmaWarp) {
-    // ------------------------------------------------------------------ TMA producer
-    if (elect_one()) {
-      mbar_expect_tx(&sm.kv_full, 2 * S::kKvBytes);
-      load_tile_tma_noexpect<D>(sm.k, &maps.k, &sm.kv_full, kt * BLK, h, b);
-      load_tile_tma_noexpect<D>(sm.v, &maps.v, &sm.kv_full, kt * BLK, h, b);
-      const float* delta_bh = p.delta + (int64_t(b) * p.H + h) * pad_rows(p.T);
-      const float* inv_bh = delta_bh + int64_t(p.B) * p.H * pad_rows(p.T);
-      for (int i = 0; i < n; ++i) {
-        const int qs = i % kQStages, ds = i % kDoStages, row0 = q_begin + i * QH;
-        if (!g.wait(&sm.q_empty[qs], ((i / kQStages) & 1) ^ 1, 100)) break;
-        mbar_expect_tx(&sm.q_full[qs], S::kQhBytes + 2 * QH * 4);
-        load_half_tile<D>(sm.q[qs], &maps.qh, &sm.q_full[qs], row0, h, b);
-        bulk_load(sm.delta[qs], delta_bh + row0, QH * 4, &sm.q_full[qs]);
-        bulk_load(sm.inv[qs], inv_bh + row0, QH * 4, &sm.q_full[qs]);
-        if (!g.wait(&sm.do_empty[ds], ((i / kDoStages) & 1) ^ 1, 101)) break;
-        mbar_expect_tx(&sm.do_full[ds], S::kQhBytes);
-        load_half_tile<D>(sm.dout[ds], &maps.doh, &sm.do_full[ds], row0, h, b);
-      }
-    }
-  } else if (warp == kFusedMmaWarpX || warp == kFusedMmaWarpY) {
-    // ------------------------------------------------------------------ tensor-core issuers
-    if (elect_one()) {
-      constexpr int F = Pack16<T>::kFmt;
-      constexpr uint32_t idesc_s = idesc_f16(BLK, QH, F, 0, 0);           // S^T, dP^T: [128 keys] x [64 queries]
-      constexpr uint32_t idesc_acc = idesc_f16(BLK, D, F, 0, 1);          // dV, dK: B (dO / Q) MN-major
-      constexpr uint32_t idesc_dq = idesc_f16(BLK, QH, F, 1, 1);          // dQ^T: A = K (MN-major), B = dS^T (MN-major)
-      const uint64_t kd = desc_kmajor(sm.k), vd = desc_kmajor(sm.v), kd_mn = desc_mnmajor(sm.k);
-      uint64_t qd[kQStages], qd_mn[kQStages], dod[kDoStages], dod_mn[kDoStages], dsd_k[2], dsd_mn[2];
-      for (int i = 0; i < kQStages; ++i) {
-        qd[i] = smem_desc_sw128(smem_u32(sm.q[i]), 16, 1024);
-        qd_mn[i] = smem_desc_sw128(smem_u32(sm.q[i]), QH * 128, 1024);
-      }
-      for (int i = 0; i < kDoStages; ++i) {
-        dod[i] = smem_desc_sw128(smem_u32(sm.dout[i]), 16, 1024);
-        dod_mn[i] = smem_desc_sw128(smem_u32(sm.dout[i]), QH * 128, 1024);
-      }
-      for (int i = 0; i < 2; ++i) {
-        dsd_k[i] = smem_desc_sw128(smem_u32(sm.ds[i]), 16, 1024);
-        dsd_mn[i] = smem_desc_sw128(smem_u32(sm.ds[i]), BLK * 128, 1024);
-      }
-      // [128 keys] x [64 queries] = A (key-side tile, [128][D]) B^T (query-side half tile, [64][D]) over the head dimension
-      auto issue_st = [&](uint32_t d_tmem, uint64_t a, uint64_t bq) {
-#pragma unroll
-        for (int s = 0; s < D / 16; ++s)
-          mma_ss(d_tmem, a + (((s / 4) * (BLK * 128) + (s % 4) * 32) >> 4), bq + (((s / 4) * (QH * 128) + (s % 4) * 32) >> 4),
-                 idesc_s, s > 0);
-      };
-      bool ok = g.wait(&sm.kv_full, 0, 110);
-      if (warp == kFusedMmaWarpX) {
-        // ---- issuer X: S^T two steps ahead, dV as soon as P^T is written
-        for (int i = 0; i < 2 && i < n && ok; ++i) {
-          if (!(ok = g.wait(&sm.q_full[i], 0, 111))) break;
-          tc_fence_after();
-          issue_st(tS0 + i * QH, kd, qd[i]);
-          mma_commit(&sm.s_full[i]);
+  if (warp >= kFusedTmaWarp) {
+    reg_share_dec<kFusedRegsAux>();                             // warps 12..15 (15 only takes part in this)
+    if (warp == kFusedTmaWarp) {
+      // ---------------------------------------------------------------- TMA producer
+      if (elect_one()) {
+        mbar_expect_tx(&sm.kv_full, 2 * S::kTileBytes);
+        load_tile_tma_noexpect<D>(sm.k, &maps.k, &sm.kv_full, kt * BLK, h, b);
+        load_tile_tma_noexpect<D>(sm.v, &maps.v, &sm.kv_full, kt * BLK, h, b);
+        const float* delta_bh = p.delta + (int64_t(b) * p.H + h) * pad_rows(p.T);
+        const float* inv_bh = delta_bh + int64_t(p.B) * p.H * pad_rows(p.T);
+        for (int i = 0; i < n; ++i) {
+          const int st = i & 1, qi = kt + i;
+          const uint32_t ph = (i >> 1) & 1;
+          if (!g.wait(&sm.q_empty[st], ph ^ 1, 140)) break;
+          mbar_expect_tx(&sm.q_full[st], S::kTileBytes + 2 * BLK * 4);
+          load_tile_tma_noexpect<D>(sm.q[st], &maps.q, &sm.q_full[st], qi * BLK, h, b);
+          bulk_load(sm.delta[st], delta_bh + qi * BLK, BLK * 4, &sm.q_full[st]);
+          bulk_load(sm.inv[st], inv_bh + qi * BLK, BLK * 4, &sm.q_full[st]);
+          if (!g.wait(&sm.do_empty, (i & 1) ^ 1, 141)) break;                  // dV(i-1) and dP^T(i-1) have read dO(i-1)
+          load_tile_tma<D>(sm.dout, &maps.dout, &sm.do_full, qi * BLK, h, b);
         }
-        for (int i = 0; i < n && ok; ++i) {
-          const int bf = i & 1, qs = i % kQStages, dst = i % kDoStages;
-          if (!(ok = g.wait(&sm.p_full[bf], (i >> 1) & 1, 113))) break;
-          TR_STAMP(128 + 16 * (i - 10) + 0, i >= 10 && i < 13);
-          if (!(ok = g.wait(&sm.do_full[dst], (i / kDoStages) & 1, 112))) break;
-          tc_fence_after();
-#pragma unroll
-          for (int s = 0; s < QH / 16; ++s)       // dV += P^T dO   (A: packed P^T over S^T buffer bf, 64 queries = 4 K-steps)
-            mma_ts(tV, tS0 + bf * QH + uint32_t(32 * (s / 2) + 8 * (s % 2)), dod_mn[dst] + ((s * 2048) >> 4), idesc_acc, i > 0 || s > 0);
-          mma_commit(&sm.do_empty[dst]);          // X's share of releasing dO(i) ...
-          mma_commit(&sm.q_empty[qs]);            // ... and Q(i) (its S^T was issued two steps ago)
-          TR_STAMP(128 + 16 * (i - 10) + 1, i >= 10 && i < 13);
-          if (i + 2 < n) {                        // S^T two steps ahead into the buffer just consumed
-            const int qs2 = (i + 2) % kQStages;
-            if (!(ok = g.wait(&sm.q_full[qs2], ((i + 2) / kQStages) & 1, 114))) break;
+      }
+    } else if (warp == kFusedMmaWarpX || warp == kFusedMmaWarpY) {
+      // ---------------------------------------------------------------- tensor-core issuers
+      if (elect_one()) {
+        constexpr int F = Pack16<T>::kFmt;
+        constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, F, 0, 0);          // S^T, dP^T: both operands K-major
+        constexpr uint32_t idesc_acc = idesc_f16(BLK, D, F, 0, 1);          // dV, dK: B (dO / Q) MN-major
+        constexpr uint32_t idesc_dq = idesc_f16(BLK, BLK, F, 1, 1);         // dQ^T: A = K (MN-major), B = dS^T (MN-major)
+        bool ok = g.wait(&sm.kv_full, 0, 150);
+        if (warp == kFusedMmaWarpX) {
+          // ---- issuer X: dV as soon as P^T is written, then the next S^T into the same columns
+          const uint64_t kd = desc_kmajor(sm.k);
+          const uint64_t qd[2] = {desc_kmajor(sm.q[0]), desc_kmajor(sm.q[1])};
+          const uint64_t dod_mn = desc_mnmajor(sm.dout);
+          if (ok && (ok = g.wait(&sm.q_full[0], 0, 151))) {
             tc_fence_after();
-            issue_st(tS0 + bf * QH, kd, qd[qs2]);
-            mma_commit(&sm.s_full[bf]);
-            TR_STAMP(128 + 16 * (i - 10) + 2, i >= 10 && i < 13);
+            issue_gemm_nt<D>(tS, kd, qd[0], idesc_s);
+            mma_commit(&sm.s_full);
           }
-        }
-      } else {
-        // ---- issuer Y: dP^T one step ahead, then dK += dS^T Q and dQ^T = K^T dS^T from the shared-memory dS^T tile
-        if (ok && (ok = g.wait(&sm.do_full[0], 0, 112))) {
-          tc_fence_after();
-          issue_st(tP, vd, dod[0]);
-          mma_commit(&sm.dp_full);
-          mma_commit(&sm.do_empty[0]);
-        }
-        for (int i = 0; i < n && ok; ++i) {
-          const int bf = i & 1, qs = i % kQStages;
-          if (!(ok = g.wait(&sm.ds_full[bf], (i >> 1) & 1, 115))) break;    // phase B done: dS^T in smem, dP^T read
-          TR_STAMP(128 + 16 * (i - 10) + 3, i >= 10 && i < 13);
-          if (i + 1 < n) {
-            const int dst1 = (i + 1) % kDoStages;
-            if (!(ok = g.wait(&sm.do_full[dst1], ((i + 1) / kDoStages) & 1, 117))) break;
+          for (int i = 0; i < n && ok; ++i) {
+            const int st = i & 1, st1 = st ^ 1;
+            if (!(ok = g.wait(&sm.p_full, i & 1, 152))) break;
+            TR_STAMP(128 + 24 * (i - 10) + 0, i >= 10 && i < 13);
+            if (!(ok = g.wait(&sm.do_full, i & 1, 153))) break;
             tc_fence_after();
-            issue_st(tP, vd, dod[dst1]);
+            issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn, idesc_acc, i > 0);              // dV += P^T dO
+            mma_commit(&sm.do_empty);                                                // X's share of releasing dO(i)
+            TR_STAMP(128 + 24 * (i - 10) + 1, i >= 10 && i < 13);
+            if (i + 1 < n) {
+              if (!(ok = g.wait(&sm.q_full[st1], ((i + 1) >> 1) & 1, 154))) break;
+              tc_fence_after();
+              issue_gemm_nt<D>(tS, kd, qd[st1], idesc_s);                                // S^T of the next query tile
+              mma_commit(&sm.s_full);
+              TR_STAMP(128 + 24 * (i - 10) + 2, i >= 10 && i < 13);
+            }
+          }
+        } else {
+          // ---- issuer Y: dQ^T and dK from the shared-memory dS^T tile, then the next dP^T once dQ^T has been drained
+          const uint64_t vd = desc_kmajor(sm.v), kd_mn = desc_mnmajor(sm.k);
+          const uint64_t dsd_k = desc_kmajor(sm.ds), dsd_mn = desc_mnmajor(sm.ds);
+          const uint64_t qd_mn[2] = {desc_mnmajor(sm.q[0]), desc_mnmajor(sm.q[1])};
+          const uint64_t dod = desc_kmajor(sm.dout);
+          if (ok && (ok = g.wait(&sm.do_full, 0, 155))) {
+            tc_fence_after();
+            issue_gemm_nt<D>(tP, vd, dod, idesc_s);
             mma_commit(&sm.dp_full);
-            mma_commit(&sm.do_empty[dst1]);       // Y's share of releasing dO(i+1)
-            TR_STAMP(128 + 16 * (i - 10) + 4, i >= 10 && i < 13);
+            mma_commit(&sm.do_empty);
           }
-          if (!(ok = g.wait(&sm.q_full[qs], (i / kQStages) & 1, 118))) break;
-          tc_fence_after();
+          for (int i = 0; i < n && ok; ++i) {
+            const int st = i & 1;
+            if (!(ok = g.wait(&sm.ds_full, i & 1, 156))) break;                          // phase B done: dS^T in smem, dP^T read
+            TR_STAMP(128 + 24 * (i - 10) + 3, i >= 10 && i < 13);
+            tc_fence_after();
 #pragma unroll
-          for (int s = 0; s < QH / 16; ++s)
-            mma_ss(tK, dsd_k[bf] + ((s * 32) >> 4), qd_mn[qs] + ((s * 2048) >> 4), idesc_acc, i > 0 || s > 0);
-          mma_commit(&sm.q_empty[qs]);            // Y's share of releasing Q(i)
-          if (i > 0 && !(ok = g.wait(&sm.dq_free, (i - 1) & 1, 116))) break;
-          tc_fence_after();
+            for (int s = 0; s < BLK / 16; ++s)                                           // dQ^T = K^T dS^T over the keys
+              mma_ss(tP, kd_mn + ((s * 2048) >> 4), dsd_mn + ((s * 2048) >> 4), idesc_dq, s > 0);
+            mma_commit(&sm.dq_full);
 #pragma unroll
-          for (int s = 0; s < BLK / 16; ++s)
-            mma_ss(tQ, kd_mn + ((s * 2048) >> 4), dsd_mn[bf] + ((s * 2048) >> 4), idesc_dq, s > 0);
-          mma_commit(&sm.dq_full);
-          mma_commit(&sm.ds_empty[bf]);
-          TR_STAMP(128 + 16 * (i - 10) + 5, i >= 10 && i < 13);
+            for (int s = 0; s < BLK / 16; ++s)                                           // dK += dS^T Q over the queries
+              mma_ss(tK, dsd_k + ((((s / 4) * (BLK * 128) + (s % 4) * 32)) >> 4), qd_mn[st] + ((s * 2048) >> 4), idesc_acc, i > 0 || s > 0);
+            mma_commit(&sm.q_empty[st]);
+            TR_STAMP(128 + 24 * (i - 10) + 4, i >= 10 && i < 13);
+            if (i + 1 < n) {
+              if (!(ok = g.wait(&sm.dq_free, i & 1, 157))) break;                        // dQ^T(i) has left TMEM
+              TR_STAMP(128 + 24 * (i - 10) + 5, i >= 10 && i < 13);
+              if (!(ok = g.wait(&sm.do_full, (i + 1) & 1, 158))) break;
+              tc_fence_after();
+              issue_gemm_nt<D>(tP, vd, dod, idesc_s);                                    // dP^T of the next query tile
+              mma_commit(&sm.dp_full);
+              mma_commit(&sm.do_empty);                                             // Y's share of releasing dO(i+1)
+              TR_STAMP(128 + 24 * (i - 10) + 12, i >= 10 && i < 13);
+            }
+          }
         }
+        if (ok) mma_commit(&sm.acc_full);
       }
-      if (ok) mma_commit(&sm.acc_full);
     }
   } else if (warp >= kFusedDrainWarp) {
     // ------------------------------------------------------------------ dQ^T drain: TMEM -> smem (transposed) -> reduce-add
-    const int dl = tid - kFusedDrainWarp * 32;                // head-dimension index == TMEM lane
+    reg_share_dec<kFusedRegsDrain>();
+    const int dl = tid - kFusedDrainWarp * 32;                   // head-dimension index == TMEM lane
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
+    float* stage0 = sm.dq_stage;                              // two staging tiles of [32 query rows][D] float32
+    float* stage1 = sm.dq_stage + 32 * D;
     bool ok = true;
+    // One quarter (32 query rows) of dQ^T: registers -> staging tile -> reduce-add.  `pending` bulk groups may still be
+    // reading the other staging tile; the one that read this tile must be done before it is overwritten.
+    auto flush = [&](const uint32_t (&v)[32], float* stage, int row, bool wait_first) {
+      if (wait_first) {
+        if (dl == 0) tma_store_wait_read1();
+        named_barrier(3, 128);
+      }
+#pragma unroll
+      for (int qi = 0; qi < 32; ++qi) stage[qi * D + dl] = __uint_as_float(v[qi]);
+      fence_async_smem();
+      named_barrier(3, 128);
+      if (dl == 0 && row < p.T) {
+        tma_reduce_add_4d(&maps.dq_acc, stage, 0, row, h, b);
+        tma_store_commit();
+      }
+    };
     for (int i = 0; i < n; ++i) {
+      const int row0 = (kt + i) * BLK;
       TR_BEGIN();
-      if (!(ok = g.wait(&sm.dq_full, i & 1, 120))) break;
+      if (!(ok = g.wait(&sm.dq_full, i & 1, 160))) break;
       TR_WAITED();
-      TR_STAMP(128 + 16 * (i - 10) + 11, dl == 0 && i >= 10 && i < 13);
+      TR_STAMP(128 + 24 * (i - 10) + 11, dl == 0 && i >= 10 && i < 13);
       tc_fence_after();
       uint32_t a[32], c[32];
-      tmem_ld32(tmem_addr(tQ, lane_base, 0), a);
-      tmem_ld32(tmem_addr(tQ, lane_base, 32), c);
+      tmem_ld32(tmem_addr(tP, lane_base, 0), a);
+      tmem_ld32(tmem_addr(tP, lane_base, 32), c);
       tmem_wait_ld_regs(a);
       tmem_wait_ld_regs(c);
-      tc_fence_before();
-      mbar_arrive(&sm.dq_free);
-      if (dl == 0) tma_store_wait_read();                    // the previous reduce has finished reading the staging tile
+      if (dl == 0) tma_store_wait_read();                     // both staging tiles are free (the previous step's reduces were issued long ago)
       named_barrier(3, 128);
 #pragma unroll
       for (int qi = 0; qi < 32; ++qi) {
-        sm.dq_stage[qi * D + dl] = __uint_as_float(a[qi]);
-        sm.dq_stage[(qi + 32) * D + dl] = __uint_as_float(c[qi]);
+        stage0[qi * D + dl] = __uint_as_float(a[qi]);
+        stage1[qi * D + dl] = __uint_as_float(c[qi]);
       }
+      tmem_ld32(tmem_addr(tP, lane_base, 64), a);            // second half into the same registers: dQ^T leaves TMEM early
+      tmem_ld32(tmem_addr(tP, lane_base, 96), c);
+      tmem_wait_ld_regs(a);
+      tmem_wait_ld_regs(c);
+      tc_fence_before();
+      mbar_arrive(&sm.dq_free);                               // the next dP^T may be issued
+      TR_STAMP(128 + 24 * (i - 10) + 14, dl == 0 && i >= 10 && i < 13);
       fence_async_smem();
       named_barrier(3, 128);
       if (dl == 0) {
-        tma_reduce_add_4d(&maps.dq_acc, sm.dq_stage, 0, q_begin + i * QH, h, b);
+        tma_reduce_add_4d(&maps.dq_acc, stage0, 0, row0, h, b);
         tma_store_commit();
+        if (row0 + 32 < p.T) { tma_reduce_add_4d(&maps.dq_acc, stage1, 0, row0 + 32, h, b); }
+        tma_store_commit();
+        TR_STAMP(128 + 24 * (i - 10) + 13, i >= 10 && i < 13);
       }
+      flush(a, stage0, row0 + 64, true);                      // waits until only the stage1 group is still reading
+      TR_STAMP(128 + 24 * (i - 10) + 15, dl == 0 && i >= 10 && i < 13);
+      flush(c, stage1, row0 + 96, true);
       TR_WORKED();
     }
 #ifdef FAT_TRACE
@@ -805,7 +815,8 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
     if (dl == 0) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ element-wise warpgroups
-    const int w = warp >> 2;                                 // query columns [32w, 32w+32) of each step
+    reg_share_inc<kFusedRegsEw>();
+    const int w = warp >> 2;                                 // query columns [64w, 64w+64) of each step
     const int r = tid & (BLK - 1);                           // key row inside the tile == TMEM lane
     const int key = kt * BLK + r;
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
@@ -813,94 +824,101 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
     const f32x2 scale2 = pk2(scale, scale), one2 = pk2(1.0f, 1.0f), step2 = pk2(-2.f * slope, -2.f * slope);
     bool ok = true;
     for (int i = 0; i < n; ++i) {
-      const int bf = i & 1, qs = i % kQStages;
-      const uint32_t bph = (i >> 1) & 1;
-      const bool diag = i < 2;                               // the first two steps straddle the diagonal
-      const int col0 = 32 * w;                               // first query column of this thread inside the step
-      f32x2 gq[16];
-      // ---- phase A
+      const int st = i & 1, qi = kt + i;
+      const bool diag = (i == 0);
+      f32x2 gq[kColsPerGroup / 2];
+      // ---- phase A: p = sigma^4 / (L+eps) -> packed P^T over S^T; g / (L+eps) kept in registers
       TR_BEGIN();
-      if (!(ok = g.wait(&sm.q_full[qs], (i / kQStages) & 1, 130))) break;
-      if (!(ok = g.wait(&sm.s_full[bf], bph, 131))) break;
+      if (!(ok = g.wait(&sm.q_full[st], (i >> 1) & 1, 170))) break;        // Delta / inv arrived with the Q tile
+      if (!(ok = g.wait(&sm.s_full, i & 1, 171))) break;
       TR_WAITED();
-      TR_STAMP(128 + 16 * (i - 10) + 6, tid == 0 && i >= 10 && i < 13);
+      TR_STAMP(128 + 24 * (i - 10) + 6, tid == 0 && i >= 10 && i < 13);
       tc_fence_after();
-      auto phase_a = [&](auto DIAG) {          // the diagonal steps get their own copy (no run-time test in the unrolled body)
-        uint32_t sreg[32], preg[16];
-        tmem_ld32(tmem_addr(tS0 + bf * QH, lane_base, col0), sreg);
-        tmem_wait_ld_regs(sreg);
-        const float base = slope * float(key - (q_begin + i * QH));          // bias of query column 0 of the step
-        f32x2 bias2 = pk2(fmaf(-slope, float(col0), base), fmaf(-slope, float(col0 + 1), base));
-        const float* iv = sm.inv[qs];
+      const float base = slope * float(key - qi * BLK);      // bias of query column 0: -slope*(q-key)
+      const float* iv = sm.inv[st];
+      auto phase_a = [&](auto DIAG) {          // the diagonal tile gets its own copy (no run-time test in the unrolled body)
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float2 ivf = *reinterpret_cast<const float2*>(iv + col0 + 2 * e);
-          const f32x2 iv2 = pk2(ivf.x, ivf.y);
-          const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * e]), __uint_as_float(sreg[2 * e + 1]));
-          f32x2 F2, g2;
-          if (rcp_shared(e, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, bias2, one2, F2, g2);
-          else                                  score_fg2<true, false>(acc2, scale2, bias2, one2, F2, g2);
-          bias2 = add2(bias2, step2);
-          F2 = mul2(F2, iv2);
-          g2 = mul2(g2, iv2);
-          float p0, p1;
-          upk2(F2, p0, p1);
-          if constexpr (decltype(DIAG)::value) {            // queries before the key see nothing of it
-            float g0, g1;
-            upk2(g2, g0, g1);
-            if (i * QH + col0 + 2 * e < r) { p0 = 0.f; g0 = 0.f; }
-            if (i * QH + col0 + 2 * e + 1 < r) { p1 = 0.f; g1 = 0.f; }
-            g2 = pk2(g0, g1);
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t sreg[32], preg[16];
+          tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
+          tmem_wait_ld_regs(sreg);
+          const int col0 = kColsPerGroup * w + 32 * c;
+          f32x2 bias2 = pk2(fmaf(-slope, float(col0), base), fmaf(-slope, float(col0 + 1), base));
+          float4 ivq = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            if (e % 2 == 0) ivq = *reinterpret_cast<const float4*>(iv + col0 + 2 * e);
+            const f32x2 iv2 = e % 2 == 0 ? pk2(ivq.x, ivq.y) : pk2(ivq.z, ivq.w);
+            f32x2 F2, g2;
+            const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * e]), __uint_as_float(sreg[2 * e + 1]));
+            if (rcp_shared(e, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, bias2, one2, F2, g2);
+            else                                  score_fg2<true, false>(acc2, scale2, bias2, one2, F2, g2);
+            bias2 = add2(bias2, step2);
+            F2 = mul2(F2, iv2);
+            g2 = mul2(g2, iv2);
+            float p0, p1;
+            upk2(F2, p0, p1);
+            if constexpr (decltype(DIAG)::value) {            // queries before the key see nothing of it
+              float g0, g1;
+              upk2(g2, g0, g1);
+              if (col0 + 2 * e < r) { p0 = 0.f; g0 = 0.f; }
+              if (col0 + 2 * e + 1 < r) { p1 = 0.f; g1 = 0.f; }
+              g2 = pk2(g0, g1);
+            }
+            gq[16 * c + e] = g2;
+            preg[e] = Pack16<T>::pack(p0, p1);
           }
-          gq[e] = g2;
-          preg[e] = Pack16<T>::pack(p0, p1);
+          tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
         }
-        tmem_st16(tmem_addr(tS0 + bf * QH, lane_base, col0), preg);
       };
       if (diag) phase_a(std::true_type{}); else phase_a(std::false_type{});
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&sm.p_full[bf]);
+      mbar_arrive(&sm.p_full);
       TR_WORKED();
-      TR_STAMP(128 + 16 * (i - 10) + 7, tid == 0 && i >= 10 && i < 13);
-      // ---- phase B
-      if (!(ok = g.wait(&sm.dp_full, i & 1, 132))) break;
-      TR_STAMP(128 + 16 * (i - 10) + 8, tid == 0 && i >= 10 && i < 13);
-      if (!(ok = g.wait(&sm.ds_empty[bf], bph ^ 1, 133))) break;
+      TR_STAMP(128 + 24 * (i - 10) + 7, tid == 0 && i >= 10 && i < 13);
+      // ---- phase B: dS^T = g (dP^T - Delta[q]) -> shared memory
+      // dP^T(i) was committed by the issuer of dQ^T(i-1) and dK(i-1), after them: its barrier also says that those
+      // have finished reading the dS^T tile
+      if (!(ok = g.wait(&sm.dp_full, i & 1, 172))) break;
+      TR_STAMP(128 + 24 * (i - 10) + 8, tid == 0 && i >= 10 && i < 13);
       TR_WAITED2();
-      TR_STAMP(128 + 16 * (i - 10) + 9, tid == 0 && i >= 10 && i < 13);
       tc_fence_after();
-      {
+      const float* dl = sm.delta[st];
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t dreg[32], preg[16];
+        const int col0 = kColsPerGroup * w + 32 * c;
         tmem_ld32(tmem_addr(tP, lane_base, col0), dreg);
         tmem_wait_ld_regs(dreg);
-        const float* dl = sm.delta[qs];
+        float4 dq4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float2 d2 = *reinterpret_cast<const float2*>(dl + col0 + 2 * e);
-          const f32x2 ds2 = mul2(gq[e], add2(pk2(__uint_as_float(dreg[2 * e]), __uint_as_float(dreg[2 * e + 1])), pk2(-d2.x, -d2.y)));
+          if (e % 2 == 0) dq4 = *reinterpret_cast<const float4*>(dl + col0 + 2 * e);
+          const float2 d2 = e % 2 == 0 ? make_float2(dq4.x, dq4.y) : make_float2(dq4.z, dq4.w);
+          const f32x2 ds2 = mul2(gq[16 * c + e], add2(pk2(__uint_as_float(dreg[2 * e]), __uint_as_float(dreg[2 * e + 1])), pk2(-d2.x, -d2.y)));
           float d0, d1;
           upk2(ds2, d0, d1);
           preg[e] = Pack16<T>::pack(d0, d1);
         }
 #pragma unroll
-        for (int sgm = 0; sgm < 4; ++sgm)
-          *reinterpret_cast<uint4*>(sm.ds[bf] + sw128_offset(r, 4 * w + sgm)) =
+        for (int sgm = 0; sgm < 4; ++sgm)        // 64-query chunk w of the tile, 16-byte segments 4c..4c+3 of this key's row
+          *reinterpret_cast<uint4*>(sm.ds + w * (BLK * 128) + sw128_offset(r, 4 * c + sgm)) =
               make_uint4(preg[4 * sgm], preg[4 * sgm + 1], preg[4 * sgm + 2], preg[4 * sgm + 3]);
       }
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(&sm.ds_full[bf]);
+      mbar_arrive(&sm.ds_full);
       TR_WORKED2();
-      TR_STAMP(128 + 16 * (i - 10) + 10, tid == 0 && i >= 10 && i < 13);
+      TR_STAMP(128 + 24 * (i - 10) + 10, tid == 0 && i >= 10 && i < 13);
     }
 #ifdef FAT_TRACE
     if (traced && (tid & 127) == 0) { long long* o = trace + 16 + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
 #endif
-    if (ok) ok = g.wait(&sm.acc_full, 0, 134);
+    if (ok) ok = g.wait(&sm.acc_full, 0, 174);
     named_barrier(1, kEwThreads);
     if (!g.aborted()) {
-      // d_v (staged in q[0..1]) and d_k (staged in dout[0..1]); the multipliers undo the 16x (F16) and 8x (g8) units
+      // d_v (staged in q[0]) and d_k (staged in dout[0]); the multipliers undo the 16x (F16) and 8x (g8) units
       tc_fence_after();
       for (int ch = w; ch < 2 * D / 32; ch += kEwGroups) {
         const bool is_dk = ch >= D / 32;
@@ -908,7 +926,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
         uint32_t oreg[32];
         tmem_ld32(tmem_addr(is_dk ? tK : tV, lane_base, c0), oreg);
         tmem_wait_ld_regs(oreg);
-        stage_row32<T>(is_dk ? sm.dout[0] : sm.q[0], r, c0, oreg, is_dk ? 0.25f * scale / kOpScale : 0.0625f / kOpScale);
+        stage_row32<T>(is_dk ? sm.dout : sm.q[0], r, c0, oreg, is_dk ? 0.25f * scale / kOpScale : 0.0625f / kOpScale);
       }
       fence_async_smem();
       named_barrier(1, kEwThreads);
@@ -916,7 +934,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
           tma_store_4d(&maps.dv, sm.q[0] + c * (BLK * 128), c * 64, kt * BLK, h, b);
-          tma_store_4d(&maps.dk, sm.dout[0] + c * (BLK * 128), c * 64, kt * BLK, h, b);
+          tma_store_4d(&maps.dk, sm.dout + c * (BLK * 128), c * 64, kt * BLK, h, b);
         }
         tma_store_commit();
         tma_store_wait_all();
@@ -996,18 +1014,26 @@ int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
   constexpr int D = 128;
   float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.delta) + stats_bytes(p.B, p.H, p.T));
   const size_t acc_bytes = size_t(p.B) * p.H * p.T * D * sizeof(float);
+  auto kern = attn_bwd_fused_tc_kernel<T, D>;
+  cudaFuncAttributes fa;
+  if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
+      fa.numRegs * kFusedThreads < 256 * kFusedRegsEw + 128 * kFusedRegsDrain + 128 * kFusedRegsAux) {
+    // the warpgroups could never collect their register shares: refuse instead of letting setmaxnreg.inc wait
+    set_error("attn_bwd_fused: built with %d registers per thread, the register hand-over needs %d", fa.numRegs, kFusedRegsLaunch);
+    return FAT_ERR_LAUNCH;
+  }
   FusedMaps m;
-  if (!make_tmap_bhtd(&m.qh, p.q, p.B, p.H, p.T, D, p.qs, 64, QH) ||
-      !make_tmap_bhtd(&m.doh, p.d_out, p.B, p.H, p.T, D, p.dos, 64, QH) ||
+  if (!make_tmap_bhtd(&m.q, p.q, p.B, p.H, p.T, D, p.qs, 64, BLK) ||
+      !make_tmap_bhtd(&m.dout, p.d_out, p.B, p.H, p.T, D, p.dos, 64, BLK) ||
       !make_tmap_bhtd(&m.k, p.k, p.B, p.H, p.T, D, p.ks, 64, BLK) ||
       !make_tmap_bhtd(&m.v, p.v, p.B, p.H, p.T, D, p.vs, 64, BLK) ||
       !make_tmap_bhtd(&m.dk, p.d_k, p.B, p.H, p.T, D, p.dks, 64, BLK) ||
       !make_tmap_bhtd(&m.dv, p.d_v, p.B, p.H, p.T, D, p.dvs, 64, BLK) ||
-      !make_tmap_bhtd_f32(&m.dq_acc, dq_acc, p.B, p.H, p.T, D, D, QH))
+      !make_tmap_bhtd_f32(&m.dq_acc, dq_acc, p.B, p.H, p.T, D, D, 32))
     return FAT_ERR_LAUNCH;
   if (int rc = launch_prepare<T, D>(p, st)) return rc;
   if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) { set_error("attn_bwd_fused: clearing the d_q accumulator failed"); return FAT_ERR_LAUNCH; }
-  if (int rc = launch_main(attn_bwd_fused_tc_kernel<T, D>, m, p, sizeof(FusedSmem<D>) + 1024, kFusedThreads, st, "attn_bwd_fused_tc")) return rc;
+  if (int rc = launch_main(kern, m, p, sizeof(FusedSmem<D>), kFusedThreads, st, "attn_bwd_fused_tc")) return rc;
   const int64_t packs = int64_t(p.B) * p.H * p.T * (D / 8);
   int64_t blocks = (packs + 255) / 256;
   if (blocks > 16 * kNumSM) blocks = 16 * kNumSM;

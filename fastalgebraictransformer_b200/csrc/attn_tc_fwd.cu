@@ -1,7 +1,7 @@
 // Causal rational attention forward on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
 //
 // One CTA owns 256 consecutive queries of one (batch, head): two 128-row query tiles, each
-// served by one "softmax" warpgroup (one thread per query row).  A producer warp streams
+// served by kSplit "softmax" warpgroups (one thread per query row and share of the score columns).  A producer warp streams
 // 128-key K and V tiles through a two-stage shared-memory ring with TMA; an issuer warp
 // drives the tensor core:   S_t = Q_t K^T  (smem x smem -> TMEM, fp32)
 //                           O_t += P_t V   (TMEM x smem -> TMEM, fp32)
@@ -21,7 +21,25 @@ using namespace tc;
 using namespace tcattn;
 
 constexpr int kStages = 2;
-constexpr int kFwdThreads = 320;         // warps 0-3: tile 0, warps 4-7: tile 1, warp 8: TMA, warp 9: MMA
+#ifdef FAT_TRACE
+#define FAT_TRACE_ARG , long long& tr_ld
+#define FAT_TRACE_PASS , tr_ld
+#define FAT_TRACE_T0() const long long tr_c0 = clock64()
+#define FAT_TRACE_T1() tr_ld += clock64() - tr_c0
+#else
+#define FAT_TRACE_ARG
+#define FAT_TRACE_PASS
+#define FAT_TRACE_T0()
+#define FAT_TRACE_T1()
+#endif
+#ifndef FAT_FWD_SPLIT
+#define FAT_FWD_SPLIT 1
+#endif
+constexpr int kSplit = FAT_FWD_SPLIT;                 // softmax warpgroups per query tile (each takes 128/kSplit score columns)
+constexpr int kEwWarps = 8 * kSplit;                  // softmax warps; then one TMA warp and one MMA warp
+constexpr int kFwdThreads = 32 * kEwWarps + 64;
+constexpr int kColsPerWg = BLK / kSplit;
+constexpr int kChunks = kColsPerWg / 32;
 
 template <int D>
 struct FwdSmem {
@@ -31,46 +49,57 @@ struct FwdSmem {
   alignas(1024) unsigned char v[kStages][kTileBytes];
   uint64_t q_full[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
   uint64_t s_full[2], p_full[2], o_full[2];
+  float l_part[2][kSplit][BLK];                           // row sums of each warpgroup's column share
   uint32_t tmem_base;
   int abort_flag;
 };
 
 struct FwdMaps { CUtensorMap q, k, v, out, out_lo; };
 
-// One thread's row of a 128x128 score tile: S (fp32, TMEM columns [0,128) from `trow`) ->
-// P = (2 sigma(S*scale + bias))^4 = 16 sigma^4 written back packed 16-bit over columns [0,64) (the factor
-// 16 cancels in O = P V / sum P); adds the row sum to l2.  `half2` holds the packed constant 1.
-// MASK: diagonal tile, keys with column index > r get no weight.  The chunk loop is kept rolled
-// (the body is ~400 instructions; unrolled four times it no longer fits the instruction cache).
+// One 32-column chunk of a thread's score row: S (fp32, registers sreg) -> P = (2 sigma(S*scale + bias))^4 = 16 sigma^4
+// as packed 16-bit pairs in preg (the factor 16 cancels in O = P V / sum P); adds the chunk's row sum to l2.
+// `half2` holds the packed constant 1.  MASK: diagonal tile, keys with column index > r get no weight.
 template <typename T, bool MASK>
-__device__ __forceinline__ void softmax_tile(uint32_t trow, int r, f32x2 scale2, f32x2 half2, f32x2 step2,
-                                             float slope, float base, f32x2& l2) {
+__device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32_t (&preg)[16], int c, int r, f32x2 scale2,
+                                              f32x2 half2, f32x2 step2, float slope, float base, f32x2& l2) {
+  f32x2 bias2 = pk2(fmaf(slope, float(c * 32), base), fmaf(slope, float(c * 32 + 1), base));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const f32x2 s2 = fma2(pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), scale2, bias2);
+    bias2 = add2(bias2, step2);
+    f32x2 r2, w2;
+    if (rcp_shared(i, FAT_RCP_SHARE_FWD)) sigma_terms2<true>(s2, half2, r2, w2); else sigma_terms2<false>(s2, half2, r2, w2);
+    const f32x2 q2 = mul2(w2, w2);
+    f32x2 f2 = mul2(q2, q2);                               // (2 sigma)^4 = 16 sigma^4
+    float f0, f1;
+    upk2(f2, f0, f1);
+    if (MASK) {
+      if (c * 32 + 2 * i > r) f0 = 0.f;
+      if (c * 32 + 2 * i + 1 > r) f1 = 0.f;
+      f2 = pk2(f0, f1);
+    }
+    l2 = add2(l2, f2);
+    preg[i] = Pack16<T>::pack(f0, f1);
+  }
+}
+
+// A thread's share of one score row: kChunks 32-column chunks starting at TMEM address `trow` (absolute chunk
+// index c0).  The packed P of chunk c lands on columns [16 c, 16 c + 16) counted from `trow`, i.e. over scores
+// this thread has already taken into registers.  The chunk loop is kept rolled (the body is ~400 instructions;
+// unrolled four times it no longer fits the instruction cache).
+template <typename T, bool MASK>
+__device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int r, f32x2 scale2, f32x2 half2, f32x2 step2,
+                                             float slope, float base, f32x2& l2 FAT_TRACE_ARG) {
   uint32_t sreg[32];
   tmem_ld32(trow, sreg);
 #pragma unroll 1
-  for (int c = 0; c < BLK / 32; ++c) {
+  for (int c = 0; c < kChunks; ++c) {
+    FAT_TRACE_T0();
     tmem_wait_ld_regs(sreg);
+    FAT_TRACE_T1();
     uint32_t preg[16];
-    f32x2 bias2 = pk2(fmaf(slope, float(c * 32), base), fmaf(slope, float(c * 32 + 1), base));
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const f32x2 s2 = fma2(pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), scale2, bias2);
-      bias2 = add2(bias2, step2);
-      f32x2 r2, w2;
-      if (rcp_shared(i, FAT_RCP_SHARE_FWD)) sigma_terms2<true>(s2, half2, r2, w2); else sigma_terms2<false>(s2, half2, r2, w2);
-      const f32x2 q2 = mul2(w2, w2);
-      f32x2 f2 = mul2(q2, q2);                               // (2 sigma)^4 = 16 sigma^4
-      float f0, f1;
-      upk2(f2, f0, f1);
-      if (MASK) {
-        if (c * 32 + 2 * i > r) f0 = 0.f;
-        if (c * 32 + 2 * i + 1 > r) f1 = 0.f;
-        f2 = pk2(f0, f1);
-      }
-      l2 = add2(l2, f2);
-      preg[i] = Pack16<T>::pack(f0, f1);
-    }
-    if (c + 1 < BLK / 32) tmem_ld32(trow + (c + 1) * 32, sreg);      // next chunk in flight while this one is stored
+    softmax_chunk<T, MASK>(sreg, preg, c0 + c, r, scale2, half2, step2, slope, base, l2);
+    if (c + 1 < kChunks) tmem_ld32(trow + (c + 1) * 32, sreg);      // next chunk in flight while this one is stored
     tmem_st16(trow + c * 16, preg);
   }
 }
@@ -96,20 +125,20 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
   if (tid == 0) {
     sm.abort_flag = 0;
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&sm.q_full[i], 1); mbar_init(&sm.s_full[i], 1); mbar_init(&sm.p_full[i], BLK); mbar_init(&sm.o_full[i], 1);
+      mbar_init(&sm.q_full[i], 1); mbar_init(&sm.s_full[i], 1); mbar_init(&sm.p_full[i], BLK * kSplit); mbar_init(&sm.o_full[i], 1);
     }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1);
     }
     mbar_fence_init();
   }
-  if (warp == 8) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
+  if (warp == kEwWarps) { tmem_alloc(&sm.tmem_base, kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
 
-  if (warp == 8) {
+  if (warp == kEwWarps) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       tma_prefetch_desc(&maps.q); tma_prefetch_desc(&maps.k); tma_prefetch_desc(&maps.v);
@@ -124,7 +153,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
         load_tile_tma<D>(sm.v[st], &maps.v, &sm.v_full[st], j * BLK, h, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kEwWarps + 1) {
     // ------------------------------------------------------------------ tensor-core issuer
     if (elect_one()) {
       constexpr uint32_t idesc_qk = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
@@ -134,7 +163,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       const uint64_t vd[kStages] = {desc_mnmajor(sm.v[0]), desc_mnmajor(sm.v[1])};
       auto issue_qk = [&](int t, int st) { issue_gemm_nt<D>(tmem + t * BLK, qd[t], kd[st], idesc_qk); };          // S_t = Q_t K^T
       auto issue_pv = [&](int t, int st, bool first) {                                                           // O_t += P_t V
-        issue_gemm_tn<BLK>(tmem + 2 * BLK + t * D, tmem + t * BLK, vd[st], idesc_pv, !first);
+        issue_gemm_tn<kColsPerWg>(tmem + 2 * BLK + t * D, tmem + t * BLK, vd[st], idesc_pv, !first);
       };
       bool ok = true;
       // prologue: scores of key tile 0 for both query tiles
@@ -178,7 +207,8 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
-    const int t = warp >> 2;                                 // query tile of this warpgroup
+    const int t = (warp >> 2) / kSplit;                      // query tile of this warpgroup
+    const int part = (warp >> 2) % kSplit;                   // which share of the score columns
     const int r = tid & (BLK - 1);                           // row inside the tile == TMEM lane
     const int row = (2 * qb + t) * BLK + r;                  // query index
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
@@ -188,6 +218,9 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     f32x2 l2 = pk2(0.f, 0.f);
     const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(2.f * slope, 2.f * slope);
     bool ok = true;
+#ifdef FAT_TRACE
+    long long tr_ld = 0, tr_st = 0;
+#endif
     for (int j = 0; j < n; ++j) {
       TR_BEGIN();
       if (!(ok = g.wait(&sm.s_full[t], j & 1, 30))) break;
@@ -195,15 +228,22 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       tc_fence_after();
       const float base = slope * float(j * BLK - row);       // bias of column 0 of this tile: -slope*(row-k0)
       const bool diag = (j == 2 * qb + t);
-      if (diag) softmax_tile<T, true>(tmem_addr(tmem, lane_base, t * BLK), r, scale2, half2, step2, slope, base, l2);
-      else      softmax_tile<T, false>(tmem_addr(tmem, lane_base, t * BLK), r, scale2, half2, step2, slope, base, l2);
+      const uint32_t trow = tmem_addr(tmem, lane_base, t * BLK + part * kColsPerWg);
+      if (diag) softmax_tile<T, true>(trow, part * kChunks, r, scale2, half2, step2, slope, base, l2 FAT_TRACE_PASS);
+      else      softmax_tile<T, false>(trow, part * kChunks, r, scale2, half2, step2, slope, base, l2 FAT_TRACE_PASS);
+#ifdef FAT_TRACE
+      const long long tr_s0 = clock64();
+#endif
       tmem_wait_st();
+#ifdef FAT_TRACE
+      tr_st += clock64() - tr_s0;
+#endif
       tc_fence_before();
       mbar_arrive(&sm.p_full[t]);
       TR_WORKED();
     }
 #ifdef FAT_TRACE
-    if (traced && r == 0) { trace[4 + 4 * t] = tr_wait; trace[5 + 4 * t] = tr_work; trace[6 + 4 * t] = clock64() - tr_t0; trace[7 + 4 * t] = n; }
+    if (traced && r == 0 && part == 0) { trace[12 + 2 * t] = tr_ld; trace[13 + 2 * t] = tr_st; trace[4 + 4 * t] = tr_wait; trace[5 + 4 * t] = tr_work; trace[6 + 4 * t] = clock64() - tr_t0; trace[7 + 4 * t] = n; }
 #endif
     float l_sum;
     {
@@ -211,18 +251,25 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       upk2(l2, la, lb);
       l_sum = (la + lb) * 0.0625f;                             // back to sum of sigma^4
     }
+    if (kSplit > 1) sm.l_part[t][part][r] = l_sum;
     if (ok && n > 0) ok = g.wait(&sm.o_full[t], 0, 31);
-    named_barrier(1 + t, BLK);                               // reached by all 128 threads, aborted or not
+    named_barrier(1 + t, BLK * kSplit);                      // reached by all of the tile's threads, aborted or not
+    if (kSplit > 1) {
+      l_sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < kSplit; ++i) l_sum += sm.l_part[t][i][r];
+    }
     if (n > 0 && !g.aborted()) {
       // -------------------------------------------------------------- epilogue: O / (L + eps), hi + residual
       tc_fence_after();
       const float inv = 0.0625f / (l_sum + p.eps);             // the accumulator holds 16 sigma^4 V
-      if (row < p.T) p.L[(int64_t(b) * p.H + h) * p.T + row] = l_sum;
+      if (part == 0 && row < p.T) p.L[(int64_t(b) * p.H + h) * p.T + row] = l_sum;
       unsigned char* stage = sm.q[t];
       const bool want_lo = p.out_lo != nullptr;
       for (int pass = 0; pass < (want_lo ? 2 : 1); ++pass) {
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int cc = 0; cc < D / 32 / kSplit; ++cc) {
+          const int c = part * (D / 32 / kSplit) + cc;       // each warpgroup converts its share of the D columns
           uint32_t oreg[32];
           tmem_ld32(tmem_addr(tmem, lane_base, 2 * BLK + t * D + c * 32), oreg);
           tmem_wait_ld();
@@ -242,22 +289,22 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
           }
         }
         fence_async_smem();
-        named_barrier(1 + t, BLK);
-        if (r == 0) {
+        named_barrier(1 + t, BLK * kSplit);
+        if (r == 0 && part == 0) {
           const CUtensorMap* m = pass == 0 ? &maps.out : &maps.out_lo;
 #pragma unroll
           for (int c = 0; c < D / 64; ++c) tma_store_4d(m, stage + c * (BLK * 128), c * 64, (2 * qb + t) * BLK, h, b);
           tma_store_commit();
           tma_store_wait_read();
         }
-        named_barrier(1 + t, BLK);
+        named_barrier(1 + t, BLK * kSplit);
       }
-      if (r == 0) tma_store_wait_all();
+      if (r == 0 && part == 0) tma_store_wait_all();
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem, kTmemCols);
+  if (warp == kEwWarps) tmem_dealloc(tmem, kTmemCols);
 }
 
 template <typename T, int D>

@@ -31,21 +31,38 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 }
 // One try: the hardware parks the thread until the phase completes or about `kWaitHintNs` pass, so a
 // waiting warp does not compete for issue slots with the warps that are doing arithmetic.
-constexpr uint32_t kWaitHintNs = 100000;
+#ifndef FAT_WAIT_HINT_NS
+#define FAT_WAIT_HINT_NS 100000
+#endif
+constexpr uint32_t kWaitHintNs = FAT_WAIT_HINT_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+#if FAT_WAIT_HINT_NS > 0
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitHintNs) : "memory");
+#else
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+#endif
   return ok != 0;
 }
 
 // Every wait in these kernels is bounded.  When the bound is hit the kernel records a status
 // word, raises a CTA-wide abort flag that makes all later waits fall through, and runs to
 // its normal teardown (TMEM is released, the launch ends, the context stays usable).
+#if FAT_WAIT_HINT_NS >= 100000
 constexpr uint32_t kWaitSpins = 1u << 15;      // x kWaitHintNs: a few seconds at most
+#elif FAT_WAIT_HINT_NS > 0
+constexpr uint32_t kWaitSpins = (1u << 15) * (100000u / FAT_WAIT_HINT_NS);
+#else
+constexpr uint32_t kWaitSpins = 1u << 26;      // polls of a few dozen cycles each: a second or so
+#endif
 
 struct Guard {
   volatile int* abort_flag;   // shared memory, zeroed at kernel start
@@ -92,6 +109,7 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const vo
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }   // all but the newest group
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA store, tcgen05.mma operands)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
