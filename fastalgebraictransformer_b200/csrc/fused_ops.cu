@@ -288,25 +288,27 @@ norm_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ x, const T* _
   }
 }
 
-// d_weight[c] = sum over the n_part partial rows.  Block = 32 columns x 8 slices.
+// d_weight[c] = sum over the n_part partial rows.  Block = 32 columns x kReduceSlices slices of the partial rows,
+// so that a thread has only a handful of (independent) loads to wait for.
+constexpr int kReduceSlices = 32;
 template <typename T>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(32 * kReduceSlices)
 norm_bwd_reduce_kernel(const typename Elem<T>::C* __restrict__ partial, T* __restrict__ d_weight,
                        int n_part, int n_cols) {
   using C = typename Elem<T>::C;
-  __shared__ C sm[8][33];
+  __shared__ C sm[kReduceSlices][33];
   const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + lane;
   C s = C(0);
   if (c < n_cols) {
-#pragma unroll 4
-    for (int r = slice; r < n_part; r += 8) s += partial[int64_t(r) * n_cols + c];
+#pragma unroll 8
+    for (int r = slice; r < n_part; r += kReduceSlices) s += partial[int64_t(r) * n_cols + c];
   }
   sm[slice][lane] = s;
   __syncthreads();
   if (slice == 0 && c < n_cols) {
 #pragma unroll
-    for (int r = 1; r < 8; ++r) s += sm[r][lane];
+    for (int r = 1; r < kReduceSlices; ++r) s += sm[r][lane];
     d_weight[c] = Elem<T>::from_c(s);
   }
 }
@@ -609,7 +611,7 @@ int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mea
   }
   int rc = check_launch("norm_bwd");
   if (rc) return rc;
-  norm_bwd_reduce_kernel<T><<<unsigned((n_cols + 31) / 32), kThreads, 0, st>>>(partial, (T*)d_w, p.grid, int(n_cols));
+  norm_bwd_reduce_kernel<T><<<unsigned((n_cols + 31) / 32), 32 * kReduceSlices, 0, st>>>(partial, (T*)d_w, p.grid, int(n_cols));
   return check_launch("norm_bwd_reduce");
 }
 
