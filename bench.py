@@ -221,7 +221,7 @@ def bench_attn(args, rank, world, device):
         # (the capture's summary is kept with the other profiler summaries of this repository)
         "roofline": {"bound": "tensor", "kernel": "attention backward (prepare + fused d_k/d_v/d_q + d_q convert launches)", "achieved": bwd_tfl,
                      "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": bwd_tfl / peaks["bf16_tflops"],
-                     "traffic": 471.9e6 * cfg["B"] / 2, "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                     "traffic": 472.8e6 * cfg["B"] / 2, "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
                      "fwd_achieved": fwd_flops / (ms_fwd * 1e-3) / 1e12},
         "clocks": clocks.summary(),
     }
