@@ -41,32 +41,35 @@ constexpr int kDqKStages = 3;
 __host__ __device__ inline int64_t pad_rows(int T) { return int64_t((T + BLK - 1) / BLK) * BLK; }
 
 // ------------------------------------------------------------------------------------- 1. prepare
+// One block = kPrepRows consecutive (padded) rows of one (batch, head): the only divisions are one 32-bit pair per
+// block (the kernel is bound by instruction issue as much as by memory; per-row 64-bit divisions doubled its time).
+constexpr int kPrepRows = 64;
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
 attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out) {
   constexpr int LPR = D / 8;                      // lanes per row, 16 bytes each
   constexpr int RPW = 32 / LPR;                   // rows per warp
-  const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
-  const int64_t Tp = pad_rows(p.T);
-  const int64_t n_rows = int64_t(p.B) * p.H * Tp;
-  const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t n_warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
-  const T* ob = static_cast<const T*>(p.out);
-  const T* lob = static_cast<const T*>(p.out_lo);
-  const T* dob = static_cast<const T*>(p.d_out);
-  for (int64_t r0 = warp_global * RPW; r0 < n_rows; r0 += n_warps * RPW) {
-    const int64_t row = r0 + sub;
-    const int64_t bh = row / Tp;
-    const int t = int(row - bh * Tp);
-    const int b = int(bh / p.H), h = int(bh % p.H);
-    const bool live = row < n_rows && t < p.T;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane / LPR, l = lane % LPR;
+  const int Tp = int(pad_rows(p.T));
+  const unsigned chunks = unsigned(Tp / kPrepRows);
+  const int bh = int(blockIdx.x / chunks), t0 = int(blockIdx.x % chunks) * kPrepRows;
+  const int b = bh / p.H, h = bh % p.H;
+  const T* ob = static_cast<const T*>(p.out) + b * p.os[0] + h * p.os[1] + l * 8;
+  const T* lob = p.out_lo ? static_cast<const T*>(p.out_lo) + b * p.os[0] + h * p.os[1] + l * 8 : nullptr;
+  const T* dob = static_cast<const T*>(p.d_out) + b * p.dos[0] + h * p.dos[1] + l * 8;
+  const float* Lrow = p.L + int64_t(bh) * p.T;
+  float* delta_row = p.delta + int64_t(bh) * Tp;
+  float* inv_row = inv_out + int64_t(bh) * Tp;
+#pragma unroll 2
+  for (int t = t0 + warp * RPW + sub; t < t0 + kPrepRows; t += 8 * RPW) {
+    const bool live = t < p.T;
     float g[8] = {}, o[8] = {};
     if (live) {
-      load_pack_cached<T, 8>(dob + b * p.dos[0] + h * p.dos[1] + int64_t(t) * p.dos[2] + l * 8, g);
-      load_pack_cached<T, 8>(ob + b * p.os[0] + h * p.os[1] + int64_t(t) * p.os[2] + l * 8, o);
+      load_pack_cached<T, 8>(dob + int64_t(t) * p.dos[2], g);
+      load_pack_cached<T, 8>(ob + int64_t(t) * p.os[2], o);
       if (lob) {
         float lo[8];
-        load_pack_cached<T, 8>(lob + b * p.os[0] + h * p.os[1] + int64_t(t) * p.os[2] + l * 8, lo);
+        load_pack_cached<T, 8>(lob + int64_t(t) * p.os[2], lo);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] += lo[i];
       }
@@ -76,9 +79,9 @@ attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out) {
     for (int i = 0; i < 8; ++i) dot = fmaf(g[i], o[i], dot);
 #pragma unroll
     for (int m = LPR / 2; m > 0; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
-    if (row < n_rows) {
-      const float inv = live ? 1.0f / (p.L[(int64_t(b) * p.H + h) * p.T + t] + p.eps) : 0.f;
-      if (l == 0) { p.delta[row] = dot; inv_out[row] = inv * kOpScale; }   // rows in the padding get 0
+    if (l == 0) {                                 // rows in the padding get 0
+      delta_row[t] = dot;
+      inv_row[t] = live ? kOpScale / (Lrow[t] + p.eps) : 0.f;
     }
   }
 }
@@ -155,11 +158,13 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
   using S = DqSmem<D>;
   S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int b = blockIdx.z, h = blockIdx.y;
-  const int qt = gridDim.x - 1 - blockIdx.x;                 // long rows first
+  int rank, bh;
+  if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, rank, bh)) return;   // padding block of the banded order
+  const int b = bh / p.H, h = bh % p.H;
+  const int qt = (p.T + BLK - 1) / BLK - 1 - rank;           // long rows first
   const int n = qt + 1;                                      // key tiles 0..qt (causal)
   Guard g{&sm.abort_flag, p.status};
-  FAT_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+  FAT_TRACE_DECL(blockIdx.x == 0);
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -374,12 +379,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
   using S = DkvSmem<D>;
   S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int b = blockIdx.z, h = blockIdx.y;
-  const int kt = blockIdx.x;                                 // early key tiles see the most queries: first
+  int kt, bh;                                                // rank = key tile: early key tiles see the most queries
+  if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kt, bh)) return;     // padding block of the banded order
+  const int b = bh / p.H, h = bh % p.H;
   const int n_q_total = (p.T + BLK - 1) / BLK;
   const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
   Guard g{&sm.abort_flag, p.status};
-  FAT_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+  FAT_TRACE_DECL(blockIdx.x == 0);
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -622,11 +628,13 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   using S = FusedSmem<D>;
   S& sm = *reinterpret_cast<S*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int b = blockIdx.z, h = blockIdx.y, kt = blockIdx.x;
+  int kt, bh;                                                // rank = key tile: early key tiles see the most queries
+  if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kt, bh)) return;     // padding block of the banded order
+  const int b = bh / p.H, h = bh % p.H;
   const int n_q_total = (p.T + BLK - 1) / BLK;
   const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
   Guard g{&sm.abort_flag, p.status};
-  FAT_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+  FAT_TRACE_DECL(blockIdx.x == 0);
   if ((smem_u32(smem_raw) & 1023u) != 0) {                   // the swizzled tiles need a 1024-byte aligned base
     if (tid == 0 && p.status) atomicOr(p.status, 0x40000000);
     return;                                                  // uniform: nobody has touched a barrier or TMEM yet
@@ -947,21 +955,27 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
 }
 
 // d_q = round(dq_acc * mul): float32 accumulator (dense [B,H,T,D]) -> tensor dtype with the caller's strides.
+// One block = kConvRows rows of one (batch, head); a thread converts 8 values of kConvRows / (256 / (D/8)) rows.
+constexpr int kConvRows = 64;
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
 attn_bwd_dq_convert_kernel(const AttnParams p, const float* __restrict__ dq_acc, float mul) {
-  const int64_t n_packs = int64_t(p.B) * p.H * p.T * (D / 8);
-  T* dq = static_cast<T*>(p.d_q);
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_packs; i += int64_t(gridDim.x) * blockDim.x) {
-    const int c = int(i % (D / 8)) * 8;
-    const int64_t row = i / (D / 8);
-    const int t = int(row % p.T);
-    const int64_t bh = row / p.T;
-    const int h = int(bh % p.H), b = int(bh / p.H);
-    const float4 lo = __ldcs(reinterpret_cast<const float4*>(dq_acc + row * D + c));
-    const float4 hi = __ldcs(reinterpret_cast<const float4*>(dq_acc + row * D + c + 4));
-    const float v[8] = {lo.x * mul, lo.y * mul, lo.z * mul, lo.w * mul, hi.x * mul, hi.y * mul, hi.z * mul, hi.w * mul};
-    store_pack<T, 8>(dq + b * p.dqs[0] + h * p.dqs[1] + int64_t(t) * p.dqs[2] + c, v);
+  constexpr int PPR = D / 8, RPP = 256 / PPR;     // packs per row, rows per pass of the block
+  const unsigned chunks = unsigned((p.T + kConvRows - 1) / kConvRows);
+  const int bh = int(blockIdx.x / chunks), t0 = int(blockIdx.x % chunks) * kConvRows;
+  const int b = bh / p.H, h = bh % p.H;
+  const int c = int(threadIdx.x % PPR) * 8, tr = int(threadIdx.x / PPR);
+  const float* src = dq_acc + int64_t(bh) * p.T * D + c;
+  T* dst = static_cast<T*>(p.d_q) + b * p.dqs[0] + h * p.dqs[1] + c;
+#pragma unroll
+  for (int i = 0; i < kConvRows / RPP; ++i) {
+    const int t = t0 + tr + i * RPP;
+    if (t < p.T) {
+      const float4 lo = __ldcs(reinterpret_cast<const float4*>(src + int64_t(t) * D));
+      const float4 hi = __ldcs(reinterpret_cast<const float4*>(src + int64_t(t) * D + 4));
+      const float v[8] = {lo.x * mul, lo.y * mul, lo.z * mul, lo.w * mul, hi.x * mul, hi.y * mul, hi.z * mul, hi.w * mul};
+      store_pack<T, 8>(dst + int64_t(t) * p.dqs[2], v);
+    }
   }
 }
 
@@ -970,11 +984,8 @@ size_t stats_bytes(int B, int H, int T) { return (2 * size_t(B) * H * pad_rows(T
 template <typename T, int D>
 int launch_prepare(const AttnParams& p, cudaStream_t st) {
   float* inv_rows = p.delta + int64_t(p.B) * p.H * pad_rows(p.T);
-  constexpr int RPW = 32 / (D / 8);
-  const int64_t rows = int64_t(p.B) * p.H * pad_rows(p.T);
-  int64_t blocks = (rows + RPW * 8 - 1) / (RPW * 8);
-  if (blocks > 16 * kNumSM) blocks = 16 * kNumSM;
-  attn_bwd_prepare_kernel<T, D><<<unsigned(blocks), 256, 0, st>>>(p, inv_rows);
+  const unsigned blocks = unsigned(p.B) * p.H * unsigned(pad_rows(p.T) / kPrepRows);
+  attn_bwd_prepare_kernel<T, D><<<blocks, 256, 0, st>>>(p, inv_rows);
   return check_launch("attn_bwd_prepare");
 }
 
@@ -984,7 +995,7 @@ int launch_main(Kern kern, const Maps& maps, const AttnParams& p, size_t smem, i
     set_error("%s: cannot reserve %zu bytes of shared memory", what, smem);
     return FAT_ERR_LAUNCH;
   }
-  dim3 grid((p.T + BLK - 1) / BLK, p.H, p.B);
+  const dim3 grid(banded_grid((p.T + BLK - 1) / BLK, p.B * p.H));
   kern<<<grid, threads, smem, st>>>(maps, p);
   return check_launch(what);
 }
@@ -1034,10 +1045,8 @@ int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
   if (int rc = launch_prepare<T, D>(p, st)) return rc;
   if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) { set_error("attn_bwd_fused: clearing the d_q accumulator failed"); return FAT_ERR_LAUNCH; }
   if (int rc = launch_main(kern, m, p, sizeof(FusedSmem<D>), kFusedThreads, st, "attn_bwd_fused_tc")) return rc;
-  const int64_t packs = int64_t(p.B) * p.H * p.T * (D / 8);
-  int64_t blocks = (packs + 255) / 256;
-  if (blocks > 16 * kNumSM) blocks = 16 * kNumSM;
-  attn_bwd_dq_convert_kernel<T, D><<<unsigned(blocks), 256, 0, st>>>(p, dq_acc, 0.25f * p.scale / kOpScale);
+  const unsigned blocks = unsigned(p.B) * p.H * unsigned((p.T + kConvRows - 1) / kConvRows);
+  attn_bwd_dq_convert_kernel<T, D><<<blocks, 256, 0, st>>>(p, dq_acc, 0.25f * p.scale / kOpScale);
   return check_launch("attn_bwd_dq_convert");
 }
 

@@ -63,6 +63,28 @@ __device__ __forceinline__ void load_tile_tma(unsigned char* dst, const CUtensor
   for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + c * (BLK * 128), m, bar, c * 64, row0, h, b);
 }
 
+// ------------------------------------------------------------------ CTA work order of the causal kernels
+// Per (batch, head) there are n_tiles CTAs whose cost falls with their rank (rank 0 sees the most tiles of the other
+// side).  Blocks are dispatched in index order; with all ranks of one (batch, head) adjacent, the last (batch, head)
+// starts its longest CTA when almost nothing else is left and the GPU idles behind it (5-8 % of the launch at
+// B*H = 128, S = 4096).  The 1-D grid is therefore ordered in kBands bands of ranks: band 0 holds the longest
+// quarter of the ranks of every (batch, head), the last band the shortest.  Inside a band the ranks of one
+// (batch, head) stay adjacent so that CTAs running together still share its tiles in L2.
+constexpr int kBands = 4;
+__host__ __device__ inline int band_size(int n_tiles) { return (n_tiles + kBands - 1) / kBands; }
+inline unsigned banded_grid(int n_tiles, int n_bh) {
+  const int bs = band_size(n_tiles);
+  return unsigned((n_tiles + bs - 1) / bs) * unsigned(n_bh) * unsigned(bs);
+}
+// false: this block is padding (rank beyond n_tiles) and must return at once
+__device__ __forceinline__ bool banded_tile(int n_tiles, int n_bh, int& rank, int& bh) {
+  const unsigned bs = unsigned(band_size(n_tiles)), per_band = unsigned(n_bh) * bs;
+  const unsigned band = blockIdx.x / per_band, rem = blockIdx.x % per_band;
+  bh = int(rem / bs);
+  rank = int(band * bs + rem % bs);
+  return rank < n_tiles;
+}
+
 // ------------------------------------------------------------------ GEMM issue helpers (one thread)
 // Descriptors are built once per shared-memory buffer; inside the loops a K-step only adds a constant
 // to the address field, so issuing a whole 128x128x128 GEMM costs a few dozen instructions.

@@ -111,8 +111,11 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
   using S = FwdSmem<D>;
   S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int b = blockIdx.z, h = blockIdx.y;
-  const int qb = gridDim.x - 1 - blockIdx.x;                 // long query blocks first
+  const int n_qb = (p.T + 2 * BLK - 1) / (2 * BLK);
+  int rank, bh;
+  if (!banded_tile(n_qb, p.B * p.H, rank, bh)) return;      // padding block of the banded order
+  const int b = bh / p.H, h = bh % p.H;
+  const int qb = n_qb - 1 - rank;                            // long query blocks first
   const int n_kv_total = (p.T + BLK - 1) / BLK;
   // query tile t covers rows [(2qb+t)*128, +128); it needs key tiles 0..(2qb+t) (causal)
   int n_tiles[2];
@@ -120,7 +123,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
   for (int t = 0; t < 2; ++t) n_tiles[t] = (2 * qb + t) * BLK < p.T ? min(2 * qb + t + 1, n_kv_total) : 0;
   const int n_max = max(n_tiles[0], n_tiles[1]);
   Guard g{&sm.abort_flag, p.status};
-  FAT_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+  FAT_TRACE_DECL(blockIdx.x == 0);
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -324,7 +327,7 @@ int launch_fwd(const AttnParams& p, cudaStream_t st) {
   const size_t smem = sizeof(FwdSmem<D>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) { set_error("attn_fwd_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return FAT_ERR_LAUNCH; }
-  dim3 grid((p.T + 2 * BLK - 1) / (2 * BLK), p.H, p.B);
+  const dim3 grid(banded_grid((p.T + 2 * BLK - 1) / (2 * BLK), p.B * p.H));
   kern<<<grid, kFwdThreads, smem, st>>>(maps, p);
   return check_launch("attn_fwd_tc");
 }
