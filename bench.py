@@ -135,6 +135,48 @@ def time_steps(step, steps: int, warmup: int, world: int, device):
     return max_over_ranks(e0.elapsed_time(e1), world, device) / steps
 
 
+def make_pipelined_e2e(device, host_inputs, compute):
+    """End-to-end step over host buffers: every call uploads `host_inputs` (pinned) into one of two device buffer sets,
+    runs `compute(device_inputs) -> results` (the public autograd API) and downloads the results into one of two pinned
+    host sets.  The three stages run on three streams, so step i's upload, step i-1's arithmetic and step i-2's download
+    overlap and share the two directions of the host link; the current stream waits for each download (the timing
+    events sit there).  The first two calls also allocate the pinned result buffers: keep them in the warm-up."""
+    dins = [[torch.empty_like(h, device=device) for h in host_inputs] for _ in range(2)]
+    houts = [None, None]
+    s_in, s_comp, s_out = (torch.cuda.Stream(device) for _ in range(3))
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_comp = [torch.cuda.Event() for _ in range(2)]       # arithmetic of the step that used buffer set i has finished
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    counter = [0]
+
+    def step():
+        i = counter[0] & 1
+        counter[0] += 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_comp[i])                     # the step two back has read these device buffers
+            for d, h in zip(dins[i], host_inputs):
+                d.copy_(h, non_blocking=True)
+            ev_in[i].record(s_in)
+        with torch.cuda.stream(s_comp):
+            s_comp.wait_event(ev_in[i])
+            results = compute(dins[i])
+            ev_comp[i].record(s_comp)
+        if houts[i] is None:
+            houts[i] = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in results]
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp[i])
+            s_out.wait_event(ev_out[i])                     # host set i is free again (its previous download is done)
+            for h, d in zip(houts[i], results):
+                h.copy_(d, non_blocking=True)
+                d.record_stream(s_out)
+            ev_out[i].record(s_out)
+        torch.cuda.current_stream(device).wait_stream(s_out)
+
+    return step
+
+E2E_OVERLAP = "upload, arithmetic and download of consecutive steps on three streams, two buffer sets"
+
+
 # ------------------------------------------------------------------------------------------ workloads
 ATTN = dict(B=8, H=16, S=4096, D=128)
 
@@ -186,19 +228,18 @@ def bench_attn(args, rank, world, device):
     ms_bwd = time_steps(bwd, max(3, args.steps // 2), 1, world, device)
 
     # end to end through the public autograd API with host buffers (pinned), copies inside the timed region
-    (hq, hk, hv, hgo), _ = make_attn_inputs(cfg, 1234 + 1 + rank, pin=True)
-    houts = [torch.empty_like(hq).pin_memory() for _ in range(4)]
+    host_in, _ = make_attn_inputs(cfg, 1234 + 1 + rank, pin=True)
+    hq = host_in[0]
 
-    def e2e_step():
-        dq, dk, dv, dgo = (t.to(device, non_blocking=True) for t in (hq, hk, hv, hgo))
-        dq.requires_grad_(True); dk.requires_grad_(True); dv.requires_grad_(True)
+    def e2e_compute(d):
+        dq, dk, dv = (t.detach().requires_grad_(True) for t in d[:3])
         out = fat.rational_attention(dq, dk, dv, slopes, scale)
-        out.backward(dgo)
-        for h, d in zip(houts, (out.detach(), dq.grad, dk.grad, dv.grad)):
-            h.copy_(d, non_blocking=True)
+        out.backward(d[3])
+        return (out.detach(), dq.grad, dk.grad, dv.grad)
 
-    e2e_steps = max(2, min(args.steps, 5))
-    ms_e2e = time_steps(e2e_step, e2e_steps, 1, world, device)
+    e2e_step = make_pipelined_e2e(device, host_in, e2e_compute)
+    e2e_steps = max(4, min(args.steps, 8))
+    ms_e2e = time_steps(e2e_step, e2e_steps, 2, world, device)
     nbytes = hq.numel() * hq.element_size()
 
     peaks = measured_peaks()
@@ -215,7 +256,8 @@ def bench_attn(args, rank, world, device):
                    "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
                    "pct_of_bf16_peak": 100.0 * tfl / world / peaks["bf16_tflops"]},
         "e2e": {"value": (fwd_flops + bwd_flops) * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "ms_per_step": ms_e2e},
+                "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "ms_per_step": ms_e2e,
+                "overlap": E2E_OVERLAP},
         "gpu_launches": launches_per_step * args.steps,
         # traffic: dram bytes of the three backward launches, ncu capture at B=2 scaled by the units processed
         # (the capture's summary is kept with the other profiler summaries of this repository)
@@ -293,24 +335,20 @@ def bench_fused(args, rank, world, device, name):
 
     # end to end: host (pinned) -> device -> forward+backward through the autograd API -> host
     hs = [t.detach().cpu().pin_memory() for t in sets[0]]
-    houts = [torch.empty(shape, dtype=torch.bfloat16).pin_memory() for _ in range(3)]
 
-    def e2e_step():
-        d = [t.to(device, non_blocking=True) for t in hs]
+    def e2e_compute(dd):
+        d = [t.detach() for t in dd]
         if name == "swiglu":
             a, b = d[0].requires_grad_(True), d[1].requires_grad_(True)
-            o = fat.rational_swiglu(a, b); o.backward(d[2]); res = (o.detach(), a.grad, b.grad)
-        elif name == "norm":
+            o = fat.rational_swiglu(a, b); o.backward(d[2]); return (o.detach(), a.grad, b.grad)
+        if name == "norm":
             a, w = d[0].requires_grad_(True), d[1].requires_grad_(True)
-            o = fat.mean_error_norm(a, w); o.backward(d[2]); res = (o.detach(), a.grad)
-        else:
-            a = d[0].requires_grad_(True)
-            o = fat.rational_softmax(a); o.backward(d[1]); res = (o.detach(), a.grad)
-        for h, r in zip(houts, res):
-            h.copy_(r, non_blocking=True)
-        return len(res)
+            o = fat.mean_error_norm(a, w); o.backward(d[2]); return (o.detach(), a.grad)
+        a = d[0].requires_grad_(True)
+        o = fat.rational_softmax(a); o.backward(d[1]); return (o.detach(), a.grad)
 
-    ms_e2e = time_steps(e2e_step, 3, 1, world, device)
+    e2e_step = make_pipelined_e2e(device, hs, e2e_compute)
+    ms_e2e = time_steps(e2e_step, 6, 2, world, device)
     n_out = {"swiglu": 3, "norm": 2, "softmax": 2}[name]
     return {
         "metric": f"rational_{name}_fwd_bwd_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "dtype": "bf16",
@@ -320,7 +358,7 @@ def bench_fused(args, rank, world, device, name):
                    "l2": "tensors exceed L2" if nset == 1 else f"{nset} rotating input sets (each pass touches > 126 MB before reuse)"},
         "e2e": {"value": cfg["bytes"] * world / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in hs),
-                "d2h_bytes_per_step": n_out * shape[0] * shape[1] * 2, "ms_per_step": ms_e2e},
+                "d2h_bytes_per_step": n_out * shape[0] * shape[1] * 2, "ms_per_step": ms_e2e, "overlap": E2E_OVERLAP},
         "gpu_launches": (3 if name == "norm" else 2) * args.steps,
         "roofline": {"bound": "hbm", "kernel": f"{name} fwd+bwd", "achieved": gbs / world, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": gbs / world / peaks["hbm_gbs"], "traffic": cfg["traffic"],
