@@ -3,8 +3,8 @@
 Same public names as the reference package (``__init__.py:7-63``); the implementation is
 hand-written sm_100a CUDA behind a C ABI (``libfat_b200.so``, ``include/fat_b200.h``).
 """
-from .fused_ops import (rational_softmax, rational_swiglu, mean_error_norm, RationalSoftmax, RationalSwiGLU,
-                        MeanErrorNorm, EPS)
+from .fused_ops import (rational_softmax, rational_swiglu, mean_error_norm, add_mean_error_norm, RationalSoftmax,
+                        RationalSwiGLU, MeanErrorNorm, AddMeanErrorNorm, EPS)
 from .forward import rational_attention_forward, compute_alibi_slopes
 from .backward import rational_attention, rational_attention_backward, RationalAttentionFunction
 from .algebraic_model import (AlgebraicTransformerLM, RationalMR, RationalSwiGLU as RationalSwiGLUModule,
@@ -13,7 +13,8 @@ from .algebraic_model import (AlgebraicTransformerLM, RationalMR, RationalSwiGLU
 from ._lib import check_device_status, PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_TENSOR_DETERMINISTIC
 
 __all__ = [
-    "rational_softmax", "rational_swiglu", "mean_error_norm", "RationalSoftmax", "RationalSwiGLU", "MeanErrorNorm", "EPS",
+    "rational_softmax", "rational_swiglu", "mean_error_norm", "add_mean_error_norm", "RationalSoftmax", "RationalSwiGLU",
+    "MeanErrorNorm", "AddMeanErrorNorm", "EPS",
     "rational_attention_forward", "compute_alibi_slopes",
     "rational_attention", "rational_attention_backward", "RationalAttentionFunction",
     "AlgebraicTransformerLM", "RationalMR", "AlgebraicAttention", "AlgebraicBlock",

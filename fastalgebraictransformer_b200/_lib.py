@@ -34,6 +34,8 @@ PROTOTYPES = {
     "fat_norm_fwd": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),
     "fat_norm_bwd_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "fat_norm_bwd": (_int, [_ptr] * 7 + [_sz] + [_i64] * 5 + [_dbl, _int, _ptr]),
+    "fat_add_norm_fwd": (_int, [_ptr] * 6 + [_i64] * 6 + [_dbl, _int, _ptr]),
+    "fat_add_norm_bwd": (_int, [_ptr] * 8 + [_sz] + [_i64] * 6 + [_dbl, _int, _ptr]),
     "fat_norm_bwd_static_capacity": (_sz, []),
     "fat_norm_bwd_static": (_int, [_ptr] * 6 + [_i64] * 5 + [_dbl, _int, _ptr]),
     "fat_softmax_fwd": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),

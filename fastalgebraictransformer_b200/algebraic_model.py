@@ -21,7 +21,7 @@ from torch.utils.checkpoint import checkpoint
 
 from .backward import RationalAttentionPackedFunction
 from .forward import compute_alibi_slopes
-from .fused_ops import EPS, RationalSwiGLUPacked, mean_error_norm
+from .fused_ops import EPS, RationalSwiGLUPacked, add_mean_error_norm, mean_error_norm
 
 
 class RationalMR(nn.Module):
@@ -93,6 +93,19 @@ class AlgebraicBlock(nn.Module):
         x = x + self.attn(self.norm1(x), mask)
         return x + self.ffn(self.norm2(x))
 
+    def forward_deferred(self, x: torch.Tensor, pending: Optional[torch.Tensor],
+                         mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The same block with every residual addition fused into the normalisation that follows it.  ``pending`` is
+        the previous block's feed-forward output that has not been added to ``x`` yet (None for the first block);
+        returns (x, pending) in the same convention: the caller adds the last pending term (or fuses it into the
+        final norm).  Same numbers as ``forward``: the sums are rounded to the tensor dtype before they are normalised."""
+        if pending is None:
+            y = self.norm1(x)
+        else:
+            x, y = add_mean_error_norm(x, pending, self.norm1.weight, self.norm1.eps)
+        x, y = add_mean_error_norm(x, self.attn(y, mask), self.norm2.weight, self.norm2.eps)
+        return x, self.ffn(y)
+
 
 class AlgebraicTransformerLM(nn.Module):
     """Algebraic Transformer language model (reference algebraic_model.py:155-265)."""
@@ -126,12 +139,20 @@ class AlgebraicTransformerLM(nn.Module):
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 attention_mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         x = self.embed(input_ids)
-        for block in self.blocks:
-            if self.gradient_checkpointing and self.training:
+        if self.gradient_checkpointing and self.training:
+            for block in self.blocks:
                 x = checkpoint(block, x, attention_mask, use_reentrant=False)
+            y = self.norm(x)
+        else:
+            # residual additions travel with the next normalisation (one pass instead of two per sublayer)
+            pending = None
+            for block in self.blocks:
+                x, pending = block.forward_deferred(x, pending, attention_mask)
+            if pending is None:
+                y = self.norm(x)
             else:
-                x = block(x, attention_mask)
-        logits = self.head(self.norm(x))
+                _, y = add_mean_error_norm(x, pending, self.norm.weight, self.norm.eps)
+        logits = self.head(y)
         loss = None
         if labels is not None:
             shift_logits = logits[..., :-1, :].contiguous()

@@ -161,11 +161,14 @@ struct RowRegs {
   }
 };
 
-template <typename T, int W, int VPT>
+// ADD: the normalised row is h = x + res, rounded to the tensor dtype and also written to h_out (the residual stream
+// of a pre-norm block: one pass instead of an addition pass followed by a normalisation pass).
+template <typename T, int W, int VPT, bool ADD = false>
 __global__ void __launch_bounds__(kThreads)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ weight, T* __restrict__ y,
                 float* __restrict__ mean, int64_t n_rows, int n_cols, int64_t xs, int64_t ys,
-                double eps_d, int G) {
+                double eps_d, int G, const T* __restrict__ res = nullptr, T* __restrict__ h_out = nullptr,
+                int64_t rs = 0, int64_t hs = 0) {
   using C = typename Elem<T>::C;
   __shared__ C red[2 * (kThreads / 32)];
   int phase = 0;
@@ -178,14 +181,28 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ weight, T* __rest
     if (pk < npk) load_pack_cached<T, W>(weight + int64_t(pk) * W, w[i]);
   }
   const int64_t row_step = int64_t(gridDim.x) * rpc, first_row = int64_t(blockIdx.x) * rpc + g;
-  RawRow<T, VPT> next_x;
+  RawRow<T, VPT> next_x, next_r;
   next_x.fetch(x + first_row * xs, t, G, npk, first_row < n_rows);
+  if (ADD) next_r.fetch(res + first_row * rs, t, G, npk, first_row < n_rows);
   for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += int64_t(gridDim.x) * rpc) {
     const int64_t row = row0 + g;
     const bool ok = row < n_rows;
     RowRegs<T, W, VPT> xr;
     xr.from_raw(next_x);
     next_x.fetch(x + (row + row_step) * xs, t, G, npk, row + row_step < n_rows);
+    if (ADD) {
+      RowRegs<T, W, VPT> rr;
+      rr.from_raw(next_r);
+      next_r.fetch(res + (row + row_step) * rs, t, G, npk, row + row_step < n_rows);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+        for (int j = 0; j < W; ++j)      // the sum as it is stored: the normalisation sees exactly what the next reader of h_out sees
+          xr.v[i][j] = Elem<T>::to_c(Elem<T>::from_c(xr.v[i][j] + rr.v[i][j]));
+        const int pk = t + i * G;
+        if (ok && pk < npk) store_pack<T, W>(h_out + row * hs + int64_t(pk) * W, xr.v[i]);
+      }
+    }
     C s[1] = {C(0)};
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
@@ -214,13 +231,14 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ weight, T* __rest
 // partial[blockIdx.x][0..n_cols) (compute type).  To leave registers for rows in flight the weight stays
 // packed (converted where used) and the running column sums live in thread-private shared-memory slots.
 // dyn smem: NT * VPT * W values.
-template <typename T, int W, int VPT, int NT>
+// ADD: d_x additionally receives d_add (the gradient that reached the normalised tensor along the residual path).
+template <typename T, int W, int VPT, int NT, bool ADD = false>
 __global__ void __launch_bounds__(NT)
 norm_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ x, const T* __restrict__ weight,
                 const float* __restrict__ mean, T* __restrict__ d_x,
                 typename Elem<T>::C* __restrict__ partial,
                 int64_t n_rows, int n_cols, int64_t dos, int64_t xs, int64_t dxs,
-                double eps_d, int G) {
+                double eps_d, int G, const T* __restrict__ d_add = nullptr, int64_t das = 0) {
   using C = typename Elem<T>::C;
   __shared__ C red[2 * (NT / 32)];
   extern __shared__ __align__(16) unsigned char dyn_smem[];
@@ -272,6 +290,12 @@ norm_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ x, const T* _
 #pragma unroll
           for (int j = 0; j < W; ++j)
             o[j] = gr.v[i][j] * Elem<T>::to_c(we[j]) * inv - sgn(xr.v[i][j]) * corr;
+          if (ADD) {
+            C a[W];
+            load_pack<T, W>(d_add + row * das + int64_t(pk) * W, a);
+#pragma unroll
+            for (int j = 0; j < W; ++j) o[j] = Elem<T>::to_c(Elem<T>::from_c(o[j])) + a[j];   // rounded like the separate norm backward, then added
+          }
           store_pack<T, W>(d_x + row * dxs + int64_t(pk) * W, o);
         }
       }
@@ -563,10 +587,43 @@ int swiglu_bwd_t(const void* d_out, const void* gate, const void* value, void* d
   return check_launch("swiglu_bwd");
 }
 
+// out[r][c] = a[r][c] + b[r][c] (rounded once, like a tensor addition): the shapes the register kernels do not take
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+add_rows_kernel(const T* a, const T* b, T* out, int64_t n_rows, int64_t n_cols,        // out may be a
+                int64_t as, int64_t bs, int64_t os) {
+  using C = typename Elem<T>::C;
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x)
+    for (int64_t c = threadIdx.x; c < n_cols; c += kThreads)
+      out[row * os + c] = Elem<T>::from_c(Elem<T>::to_c(a[row * as + c]) + Elem<T>::to_c(b[row * bs + c]));
+}
+
+template <typename T>
+int add_rows_t(const void* a, const void* b, void* out, int64_t n_rows, int64_t n_cols, int64_t as, int64_t bs, int64_t os,
+               cudaStream_t st) {
+  const int64_t cap = 32 * kNumSM;
+  add_rows_kernel<T><<<unsigned(n_rows < cap ? n_rows : cap), kThreads, 0, st>>>((const T*)a, (const T*)b, (T*)out, n_rows,
+                                                                                n_cols, as, bs, os);
+  return check_launch("add_rows");
+}
+
+// res != nullptr: y = norm(x + res), h_out = x + res
 template <typename T>
 int norm_fwd_t(const void* x, const void* w, void* y, float* mean, int64_t n_rows, int64_t n_cols,
-               int64_t xs, int64_t ys, double eps, cudaStream_t st) {
+               int64_t xs, int64_t ys, double eps, cudaStream_t st,
+               const void* res = nullptr, void* h_out = nullptr, int64_t rs = 0, int64_t hs = 0) {
   constexpr int W = 16 / sizeof(T);
+  if (res) {
+    RowPlan p = plan_rows<T>(n_rows, n_cols, {x, w, y, res, h_out}, {xs, ys, rs, hs}, FAT_NORM_FWD_BPS, FAT_NORM_FWD_PPT);
+    if (p.fast) {
+      FAT_VPT_SWITCH(p.vpt, (norm_fwd_kernel<T, W, VPT, true><<<p.grid, kThreads, 0, st>>>(
+          (const T*)x, (const T*)w, (T*)y, mean, n_rows, int(n_cols), xs, ys, eps, p.G, (const T*)res, (T*)h_out, rs, hs)));
+      return check_launch("add_norm_fwd");
+    }
+    if (int rc = add_rows_t<T>(x, res, h_out, n_rows, n_cols, xs, rs, hs, st)) return rc;
+    x = h_out;
+    xs = hs;
+  }
   RowPlan p = plan_rows<T>(n_rows, n_cols, {x, w, y}, {xs, ys}, FAT_NORM_FWD_BPS, FAT_NORM_FWD_PPT);
   if (p.fast) {
     FAT_VPT_SWITCH(p.vpt, (norm_fwd_kernel<T, W, VPT><<<p.grid, kThreads, 0, st>>>(
@@ -581,7 +638,7 @@ int norm_fwd_t(const void* x, const void* w, void* y, float* mean, int64_t n_row
 template <typename T>
 int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mean, void* d_x, void* d_w,
                void* ws, size_t ws_bytes, int64_t n_rows, int64_t n_cols, int64_t dos, int64_t xs, int64_t dxs,
-               double eps, cudaStream_t st) {
+               double eps, cudaStream_t st, const void* d_add = nullptr, int64_t das = 0) {
   using C = typename Elem<T>::C;
   constexpr int W = 16 / sizeof(T);
   // wide rows run with 512-thread blocks so that a thread owns one or two packs of a row: the per-thread
@@ -589,7 +646,7 @@ int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mea
   constexpr int kWide = 512;
   const bool wide = n_cols / W > kThreads;
   const int threads = wide ? kWide : kThreads;
-  RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, w, d_x}, {dos, xs, dxs}, FAT_NORM_BWD_BPS, FAT_NORM_BWD_PPT, threads);
+  RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, w, d_x, d_add}, {dos, xs, dxs, das}, FAT_NORM_BWD_BPS, FAT_NORM_BWD_PPT, threads);
   if (p.grid > kNormBwdMaxBlocks) p.grid = kNormBwdMaxBlocks;
   if (size_t(p.grid) * size_t(n_cols) * sizeof(C) > ws_bytes) {
     set_error("norm_bwd: workspace of %zu bytes is smaller than the %zu needed", ws_bytes,
@@ -601,16 +658,24 @@ int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mea
     auto go = [&](auto kern, size_t smem) {
       if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
       kern<<<p.grid, threads, smem, st>>>((const T*)d_out, (const T*)x, (const T*)w, mean, (T*)d_x, partial,
-                                         n_rows, int(n_cols), dos, xs, dxs, eps, p.G);
+                                         n_rows, int(n_cols), dos, xs, dxs, eps, p.G, (const T*)d_add, das);
     };
-    if (wide) { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kWide>, size_t(kWide) * VPT * W * sizeof(C))); }
-    else      { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kThreads>, size_t(kThreads) * VPT * W * sizeof(C))); }
+    if (d_add) {
+      if (wide) { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kWide, true>, size_t(kWide) * VPT * W * sizeof(C))); }
+      else      { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kThreads, true>, size_t(kThreads) * VPT * W * sizeof(C))); }
+    } else {
+      if (wide) { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kWide>, size_t(kWide) * VPT * W * sizeof(C))); }
+      else      { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kThreads>, size_t(kThreads) * VPT * W * sizeof(C))); }
+    }
   } else {
     row_slow_kernel<T, kNormBwd><<<p.grid, kThreads, 0, st>>>((const T*)x, (const T*)d_out, (const T*)w, nullptr, mean,
                                                                (T*)d_x, partial, n_rows, n_cols, xs, dos, dxs, eps);
   }
   int rc = check_launch("norm_bwd");
   if (rc) return rc;
+  if (d_add && !p.fast) {                                   // the generic kernel wrote the plain gradient: add in a second pass
+    if ((rc = add_rows_t<T>(d_x, d_add, d_x, n_rows, n_cols, dxs, das, dxs, st))) return rc;
+  }
   norm_bwd_reduce_kernel<T><<<unsigned((n_cols + 31) / 32), 32 * kReduceSlices, 0, st>>>(partial, (T*)d_w, p.grid, int(n_cols));
   return check_launch("norm_bwd_reduce");
 }
@@ -727,6 +792,27 @@ int fat_norm_fwd(const void* x, const void* weight, void* y, float* mean, int64_
   if (n_rows == 0) return FAT_OK;
   if (!x || !weight || !y || !mean) { set_error("norm_fwd: null pointer"); return FAT_ERR_NULL; }
   FAT_DTYPE_SWITCH(dtype, norm_fwd_t<T>(x, weight, y, mean, n_rows, n_cols, xs, ys, eps, (cudaStream_t)stream));
+}
+
+int fat_add_norm_fwd(const void* x, const void* residual, const void* weight, void* h_out, void* y, float* mean,
+                     int64_t n_rows, int64_t n_cols, int64_t xs, int64_t rs, int64_t hs, int64_t ys, double eps, int dtype,
+                     void* stream) {
+  if (int rc = check_2d("add_norm_fwd", n_rows, n_cols)) return rc;
+  if (n_rows == 0) return FAT_OK;
+  if (!x || !residual || !weight || !h_out || !y || !mean) { set_error("add_norm_fwd: null pointer"); return FAT_ERR_NULL; }
+  FAT_DTYPE_SWITCH(dtype, norm_fwd_t<T>(x, weight, y, mean, n_rows, n_cols, xs, ys, eps, (cudaStream_t)stream, residual,
+                                        h_out, rs, hs));
+}
+
+int fat_add_norm_bwd(const void* d_y, const void* d_h, const void* h, const void* weight, const float* mean, void* d_sum,
+                     void* d_weight, void* workspace, size_t workspace_bytes, int64_t n_rows, int64_t n_cols,
+                     int64_t dys, int64_t dhs, int64_t hs, int64_t dss, double eps, int dtype, void* stream) {
+  if (int rc = check_2d("add_norm_bwd", n_rows, n_cols)) return rc;
+  if (!d_weight || !weight) { set_error("add_norm_bwd: null pointer"); return FAT_ERR_NULL; }
+  if (n_rows > 0 && (!d_y || !h || !mean || !d_sum)) { set_error("add_norm_bwd: null pointer"); return FAT_ERR_NULL; }
+  if (!workspace) { set_error("add_norm_bwd: null workspace"); return FAT_ERR_WORKSPACE; }
+  FAT_DTYPE_SWITCH(dtype, norm_bwd_t<T>(d_y, h, weight, mean, d_sum, d_weight, workspace, workspace_bytes, n_rows, n_cols,
+                                        dys, hs, dss, eps, (cudaStream_t)stream, d_h, dhs));
 }
 
 size_t fat_norm_bwd_workspace_bytes(int64_t n_rows, int64_t n_cols, int dtype) {

@@ -89,6 +89,29 @@ class MeanErrorNorm(torch.autograd.Function):
         return d_x, d_w, None
 
 
+class AddMeanErrorNorm(torch.autograd.Function):
+    """(h, y) with h = x + residual and y = mean_error_norm(h, weight): the residual addition of a pre-norm block fused
+    with the normalisation that follows it (reference algebraic_model.py:149-152 does the two in separate passes).
+    backward returns (d_sum, d_sum, d_weight, None) with d_sum = d_h + d(norm)/dh."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = EPS):
+        assert x.is_cuda and residual.is_cuda, "Input must be on CUDA"
+        h, y, mean = _alg.add_norm_fwd(x, residual, weight, eps)
+        ctx.save_for_backward(h, weight, mean)
+        ctx.eps = eps
+        ctx.set_materialize_grads(False)             # an unused result arrives as None, not as a tensor of zeros
+        return h, y
+
+    @staticmethod
+    def backward(ctx, d_h, d_y):
+        h, weight, mean = ctx.saved_tensors
+        if d_y is None:                              # only the sum was used downstream
+            return d_h, d_h, None, None
+        d_sum, d_w = _alg.add_norm_bwd(d_y, d_h, h, weight, mean, ctx.eps)
+        return d_sum, d_sum, d_w, None
+
+
 def _require_cuda(t: torch.Tensor, what: str) -> None:
     if not t.is_cuda:
         raise RuntimeError(f"{what}: CUDA tensor required — this build has no CPU fallback")
@@ -104,6 +127,12 @@ def rational_swiglu(gate: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
     """Apply the rational SwiGLU activation (reference fused_ops.py:618-626)."""
     _require_cuda(gate, "rational_swiglu")
     return RationalSwiGLU.apply(gate, value)
+
+
+def add_mean_error_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = EPS):
+    """(x + residual, mean_error_norm(x + residual, weight)) in one pass over the tensors."""
+    _require_cuda(x, "add_mean_error_norm")
+    return AddMeanErrorNorm.apply(x, residual, weight, eps)
 
 
 def mean_error_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = EPS) -> torch.Tensor:

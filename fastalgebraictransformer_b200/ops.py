@@ -8,7 +8,7 @@ Autograd formulas are registered on the forward operators, so they compose with
 from __future__ import annotations
 
 import ctypes as C
-from typing import Tuple
+from typing import Optional, Tuple
 
 import torch
 from torch import Tensor
@@ -21,6 +21,8 @@ _libdef.define("swiglu_fwd(Tensor gate, Tensor value) -> Tensor")
 _libdef.define("swiglu_bwd(Tensor d_out, Tensor gate, Tensor value) -> (Tensor, Tensor)")
 _libdef.define("norm_fwd(Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)")
 _libdef.define("norm_bwd(Tensor d_out, Tensor x, Tensor weight, Tensor mean, float eps) -> (Tensor, Tensor)")
+_libdef.define("add_norm_fwd(Tensor x, Tensor residual, Tensor weight, float eps) -> (Tensor, Tensor, Tensor)")
+_libdef.define("add_norm_bwd(Tensor d_y, Tensor? d_h, Tensor h, Tensor weight, Tensor mean, float eps) -> (Tensor, Tensor)")
 _libdef.define("softmax_fwd(Tensor x, float eps) -> Tensor")
 _libdef.define("softmax_bwd(Tensor d_out, Tensor x, float eps) -> Tensor")
 _libdef.define("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor slopes, float scale, bool causal, float eps, "
@@ -140,6 +142,48 @@ def _norm_bwd(d_out: Tensor, x: Tensor, weight: Tensor, mean: Tensor, eps: float
     return d_x, d_w.to(weight.dtype)
 
 
+def _add_norm_fwd(x: Tensor, residual: Tensor, weight: Tensor, eps: float) -> Tuple[Tensor, Tensor, Tensor]:
+    """h = x + residual, y = mean_error_norm(h, weight), in one pass.  Returns (h, y, mean)."""
+    _cuda_check(x, residual, weight)
+    assert x.shape == residual.shape and x.dtype == residual.dtype, "x and residual must match"
+    n = x.shape[-1]
+    assert weight.shape == (n,), "weight must be [n_cols]"
+    w = weight.to(x.dtype).contiguous()
+    h = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    xr, rr = _rows(x), _rows(residual)
+    mean = torch.empty(xr.shape[0], dtype=torch.float32, device=x.device)
+    if x.numel():
+        hr, yr = h.view(-1, n), y.view(-1, n)
+        with _lib.device_guard(x.device):
+            _lib.check(_lib.lib().fat_add_norm_fwd(_p(xr), _p(rr), _p(w), _p(hr), _p(yr), _p(mean), xr.shape[0], n,
+                                                   xr.stride(0), rr.stride(0), n, n, eps, _lib.dtype_tag(x),
+                                                   _lib.stream_ptr(x.device)))
+    return h, y, mean
+
+
+def _add_norm_bwd(d_y: Tensor, d_h: Optional[Tensor], h: Tensor, weight: Tensor, mean: Tensor,
+                  eps: float) -> Tuple[Tensor, Tensor]:
+    """Gradient of the sum (shared by x and residual) and of the weight."""
+    _cuda_check(d_y, h, weight, mean)
+    n = h.shape[-1]
+    w = weight.to(h.dtype).contiguous()
+    d_sum = torch.empty(h.shape, dtype=h.dtype, device=h.device)
+    d_w = torch.empty(n, dtype=h.dtype, device=h.device)
+    go, hr, dsr = _rows(d_y), _rows(h), d_sum.view(-1, n)
+    dh = _rows(d_h.to(h.dtype)) if d_h is not None else None
+    tag = _lib.dtype_tag(h)
+    L = _lib.lib()
+    ws_bytes = L.fat_norm_bwd_workspace_bytes(hr.shape[0], n, tag)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=h.device)
+    with _lib.device_guard(h.device):
+        _lib.check(L.fat_add_norm_bwd(_p(go), _p(dh) if dh is not None and dh.numel() else None, _p(hr), _p(w), _p(mean),
+                                      _p(dsr), _p(d_w), _p(ws), ws_bytes, hr.shape[0], n,
+                                      go.stride(0) if go.numel() else n, dh.stride(0) if dh is not None and dh.numel() else n,
+                                      hr.stride(0) if hr.numel() else n, n, eps, tag, _lib.stream_ptr(h.device)))
+    return d_sum, d_w.to(weight.dtype)
+
+
 # ----------------------------------------------------------------------------- rational softmax
 def _softmax_fwd(x: Tensor, eps: float) -> Tensor:
     _cuda_check(x)
@@ -249,7 +293,8 @@ def attn_bwd_packed(qkv: Tensor, out: Tensor, out_lo: Tensor, L: Tensor, d_out: 
 
 
 for _name, _fn in (("swiglu_fwd", _swiglu_fwd), ("swiglu_bwd", _swiglu_bwd), ("norm_fwd", _norm_fwd),
-                   ("norm_bwd", _norm_bwd), ("softmax_fwd", _softmax_fwd), ("softmax_bwd", _softmax_bwd),
+                   ("norm_bwd", _norm_bwd), ("add_norm_fwd", _add_norm_fwd), ("add_norm_bwd", _add_norm_bwd),
+                   ("softmax_fwd", _softmax_fwd), ("softmax_bwd", _softmax_bwd),
                    ("attn_fwd", _attn_fwd), ("attn_bwd", _attn_bwd)):
     _libdef.impl(_name, _fn, "CUDA")
 
@@ -275,6 +320,17 @@ def _(x, weight, eps):
 @torch.library.register_fake(f"{_NS}::norm_bwd")
 def _(d_out, x, weight, mean, eps):
     return torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(weight)
+
+
+@torch.library.register_fake(f"{_NS}::add_norm_fwd")
+def _(x, residual, weight, eps):
+    return (torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(x, memory_format=torch.contiguous_format),
+            x.new_empty(x.numel() // x.shape[-1], dtype=torch.float32))
+
+
+@torch.library.register_fake(f"{_NS}::add_norm_bwd")
+def _(d_y, d_h, h, weight, mean, eps):
+    return torch.empty_like(h, memory_format=torch.contiguous_format), torch.empty_like(weight)
 
 
 @torch.library.register_fake(f"{_NS}::softmax_fwd")
@@ -322,6 +378,20 @@ def _norm_backward(ctx, d_y, d_mean):
     return d_x, d_w, None
 
 
+def _add_norm_setup(ctx, inputs, output):
+    x, residual, weight, eps = inputs
+    ctx.save_for_backward(output[0], weight, output[2])      # h, not x and residual: the backward only needs their sum
+    ctx.eps = eps
+
+
+def _add_norm_backward(ctx, d_h, d_y, d_mean):
+    h, weight, mean = ctx.saved_tensors
+    if d_y is None:                                          # only the sum was used downstream
+        return d_h, d_h, None, None
+    d_sum, d_w = torch.ops.algebraic.add_norm_bwd(d_y, d_h, h, weight, mean, ctx.eps)
+    return d_sum, d_sum, d_w, None
+
+
 def _softmax_setup(ctx, inputs, output):
     ctx.save_for_backward(inputs[0])
     ctx.eps = inputs[1]
@@ -346,5 +416,6 @@ def _attn_backward(ctx, d_out, d_L, d_lo):
 
 torch.library.register_autograd(f"{_NS}::swiglu_fwd", _swiglu_backward, setup_context=_swiglu_setup)
 torch.library.register_autograd(f"{_NS}::norm_fwd", _norm_backward, setup_context=_norm_setup)
+torch.library.register_autograd(f"{_NS}::add_norm_fwd", _add_norm_backward, setup_context=_add_norm_setup)
 torch.library.register_autograd(f"{_NS}::softmax_fwd", _softmax_backward, setup_context=_softmax_setup)
 torch.library.register_autograd(f"{_NS}::attn_fwd", _attn_backward, setup_context=_attn_setup)

@@ -106,6 +106,23 @@ FAT_API int fat_norm_bwd(const void* d_out, const void* x, const void* weight, c
                  int64_t d_out_row_stride, int64_t x_row_stride, int64_t d_x_row_stride,
                  double eps, int dtype, void* stream);
 
+/* Residual addition fused with the normalisation that follows it in a pre-norm block:
+ *   h = x + residual (rounded to the tensor dtype, written to h_out), y = norm(h) * weight, mean = mean|h|.
+ * Replaces the pair `x = x + sublayer(...)` / `self.norm(x)` of AlgebraicBlock.forward and of the model's final
+ * norm (algebraic_model.py:149-152, 224): one pass over four tensors instead of an addition pass over three and a
+ * normalisation pass over two.  Results are bit-identical to fat_norm_fwd applied to the rounded sum.
+ * Backward: d_sum = d_h + [gradient of the normalisation w.r.t. h] (d_h may be NULL: no gradient reached h
+ * along the residual path); d_sum is the gradient of both x and residual.  Workspace as for fat_norm_bwd.
+ * Rows the register kernels do not take (unaligned, odd widths) run as two passes. */
+FAT_API int fat_add_norm_fwd(const void* x, const void* residual, const void* weight, void* h_out, void* y, float* mean,
+                 int64_t n_rows, int64_t n_cols, int64_t x_row_stride, int64_t residual_row_stride,
+                 int64_t h_row_stride, int64_t y_row_stride, double eps, int dtype, void* stream);
+
+FAT_API int fat_add_norm_bwd(const void* d_y, const void* d_h, const void* h, const void* weight, const float* mean,
+                 void* d_sum, void* d_weight, void* workspace, size_t workspace_bytes,
+                 int64_t n_rows, int64_t n_cols, int64_t d_y_row_stride, int64_t d_h_row_stride,
+                 int64_t h_row_stride, int64_t d_sum_row_stride, double eps, int dtype, void* stream);
+
 /* Mean-error-norm backward for callers that cannot provide scratch memory.
  * (No counterpart in the reference: its backward lets PyTorch allocate whatever it needs.)
  *

@@ -57,6 +57,13 @@ def mean_error_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = EPS) -> 
     return x / (m + eps) * weight
 
 
+def add_mean_error_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = EPS):
+    """(h, y): h = x + residual, y = mean_error_norm(h, weight) — the residual addition of a pre-norm block
+    and the normalisation that follows it (algebraic_model.py:149-152, with the norm of 26-39)."""
+    h = x + residual
+    return h, mean_error_norm(h, weight, eps)
+
+
 def compute_alibi_slopes(n_heads: int) -> torch.Tensor:
     """ALiBi slopes (forward.py:21-42).
 

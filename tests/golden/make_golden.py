@@ -21,7 +21,12 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+ONLY = None       # set by --only: write just the fixtures whose name starts with this prefix
+
+
 def save(name, **arrays):
+    if ONLY and not name.startswith(ONLY):
+        return
     out = {k: (v.detach().numpy() if torch.is_tensor(v) else np.asarray(v)) for k, v in arrays.items()}
     np.savez(os.path.join(HERE, name + ".npz"), **out)
     print(name, {k: tuple(v.shape) for k, v in out.items()})
@@ -37,7 +42,10 @@ def grads(fn, inputs, d_out):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root", help="directory that contains the 'reference' package")
+    ap.add_argument("--only", default=None, help="write only the fixtures whose name starts with this prefix")
     args = ap.parse_args()
+    global ONLY
+    ONLY = args.only
     sys.path.insert(0, args.reference)
     ref_tests = importlib.import_module("reference.tests")
     ref_fwd = importlib.import_module("reference.forward")
@@ -73,6 +81,22 @@ def main():
         out, (dx, dw) = grads(ref_tests.ref_mean_error_norm, [x, w], go)
         save(f"norm_{tag}", x=x, weight=w, d_out=go, out=out, dx=dx, dweight=dw,
              mean=x.abs().mean(-1))
+
+    # --- residual addition followed by the norm, as a pre-norm block does it (algebraic_model.py:149-152): both the sum
+    #     and the normalised sum are used downstream, so both receive a gradient
+    g = torch.Generator().manual_seed(107)
+    for tag, shape in (("a", (2, 16, 96)), ("b", (7, 50))):
+        x = torch.randn(*shape, generator=g)
+        r = torch.randn(*shape, generator=g)
+        w = torch.randn(shape[-1], generator=g)
+        d_h = torch.randn(*shape, generator=g)
+        d_y = torch.randn(*shape, generator=g)
+        leaves = [t.clone().requires_grad_(True) for t in (x, r, w)]
+        h = leaves[0] + leaves[1]
+        y = ref_tests.ref_mean_error_norm(h, leaves[2])
+        ((h * d_h).sum() + (y * d_y).sum()).backward()
+        save(f"add_norm_{tag}", x=x, residual=r, weight=w, d_h=d_h, d_y=d_y, h=h.detach(), y=y.detach(),
+             dx=leaves[0].grad, dresidual=leaves[1].grad, dweight=leaves[2].grad)
 
     # --- attention: the reference's own test shapes (tests.py:183) and a ragged one
     g = torch.Generator().manual_seed(104)

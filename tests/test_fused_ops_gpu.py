@@ -145,6 +145,58 @@ def test_norm_vs_oracle(shape, dtype):
         assert norm_max_err(dw.float(), wdw) < 1e-2
 
 
+def run_add_norm(x, r, w, d_h, d_y):
+    """(h, y, dx, dr, dw) of the fused residual addition + norm on the GPU."""
+    leaves = [t.detach().to(DEV).requires_grad_(True) for t in (x, r, w)]
+    h, y = fat().add_mean_error_norm(*leaves)
+    torch.autograd.backward([h, y], [d_h.to(DEV), d_y.to(DEV)])
+    return h.detach(), y.detach(), leaves[0].grad, leaves[1].grad, leaves[2].grad
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_add_norm_golden(tag):
+    g = load_golden(f"add_norm_{tag}")
+    got = run_add_norm(g["x"], g["residual"], g["weight"], g["d_h"], g["d_y"])
+    for t, key in zip(got, ("h", "y", "dx", "dresidual", "dweight")):
+        assert norm_max_err(t, g[key]) < FP32_TOL, key
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+@pytest.mark.parametrize("shape", [(2, 512, 768), (2, 3), (7, 50), (300, 2048), (64, 4096), (3, 20000)])
+def test_add_norm_equals_the_two_separate_operators(shape, dtype):
+    """The fused pass rounds the sum to the tensor dtype before normalising it and rounds the norm gradient before
+    adding the residual gradient, exactly as the two separate passes do: bit-identical results, every dtype, including
+    the shapes that fall back to the generic kernels."""
+    x, r, d_h, d_y = gen(41, shape, shape, shape, shape, dtype=dtype)
+    (w,) = gen(42, (shape[-1],), dtype=dtype)
+    w = (1 + 0.1 * w.float()).to(dtype)
+    h, y, dx, dr, dw = run_add_norm(x, r, w, d_h, d_y)
+    leaves = [t.detach().to(DEV).requires_grad_(True) for t in (x, r, w)]
+    h2 = leaves[0] + leaves[1]
+    y2 = fat().mean_error_norm(h2, leaves[2])
+    torch.autograd.backward([h2, y2], [d_h.to(DEV), d_y.to(DEV)])
+    assert torch.equal(h, h2.detach()) and torch.equal(y, y2.detach())
+    assert torch.equal(dx, leaves[0].grad) and torch.equal(dr, leaves[1].grad) and torch.equal(dw, leaves[2].grad)
+
+
+def test_add_norm_only_one_result_used():
+    """Gradients when only the sum or only the normalised sum feeds the loss."""
+    x, r, d = gen(43, (6, 256), (6, 256), (6, 256))
+    (w,) = gen(44, (256,))
+    for use_h in (True, False):
+        leaves = [t.to(DEV).requires_grad_(True) for t in (x, r, w)]
+        h, y = fat().add_mean_error_norm(*leaves)
+        ((h if use_h else y) * d.to(DEV)).sum().backward()
+        ref = [t.clone().requires_grad_(True) for t in (x, r, w)]
+        ho, yo = oracle.add_mean_error_norm(*ref)
+        ((ho if use_h else yo) * d).sum().backward()
+        assert norm_max_err(leaves[0].grad, ref[0].grad) < FP32_TOL and norm_max_err(leaves[1].grad, ref[1].grad) < FP32_TOL
+        if use_h:
+            assert leaves[2].grad is None or float(leaves[2].grad.abs().max()) == 0.0
+        else:
+            assert norm_max_err(leaves[2].grad, ref[2].grad) < FP32_TOL
+
+
 def test_norm_weight_randn_like_reference_test():
     """tests.py:141-173 draws the weight from randn; thresholds fwd 1e-4, grads 1e-3 (max abs)."""
     x, go = gen(16, (4, 1024, 1024), (4, 1024, 1024))

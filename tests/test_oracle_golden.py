@@ -55,6 +55,18 @@ def test_norm(tag):
     assert norm_max_err(g["x"].abs().mean(-1), g["mean"]) < TOL
 
 
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_add_norm(tag):
+    """Residual addition + norm as the reference's block composes them; both results carry a gradient."""
+    g = load_golden(f"add_norm_{tag}")
+    leaves = [g[k].clone().requires_grad_(True) for k in ("x", "residual", "weight")]
+    h, y = oracle.add_mean_error_norm(*leaves)
+    ((h * g["d_h"]).sum() + (y * g["d_y"]).sum()).backward()
+    assert norm_max_err(h.detach(), g["h"]) < TOL and norm_max_err(y.detach(), g["y"]) < TOL
+    for leaf, key in zip(leaves, ("dx", "dresidual", "dweight")):
+        assert norm_max_err(leaf.grad, g[key]) < TOL, key
+
+
 @pytest.mark.parametrize("tag", ["a", "b", "c", "d", "e"])
 def test_attention(tag):
     g = load_golden(f"attention_{tag}")
