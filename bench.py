@@ -461,7 +461,9 @@ def bench_lm(args, rank, world, device, name):
                    "parallelism": f"dp{world}", "launch": launch, "loss": float(last["loss"].item())},
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * hids.numel() * 8,
                 "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e},
-        "gpu_launches": cfg["n_layers"] * 9 * args.steps,
+        # this library's kernels per step: per layer 2 (add-)norm forward, attention forward, SwiGLU forward, 2 x 2 norm
+        # backward (+ d_weight reduce), 3 attention backward, SwiGLU backward = 12; final add-norm (1 + 2), loss head (1 + 1)
+        "gpu_launches": (cfg["n_layers"] * 12 + 5) * args.steps,
         "roofline": {"bound": "tensor", "kernel": "whole step (GEMMs in cuBLAS + this library's kernels)",
                      "achieved": flops / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], "traffic": None,

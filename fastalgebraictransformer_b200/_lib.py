@@ -38,6 +38,8 @@ PROTOTYPES = {
     "fat_add_norm_bwd": (_int, [_ptr] * 8 + [_sz] + [_i64] * 6 + [_dbl, _int, _ptr]),
     "fat_norm_bwd_static_capacity": (_sz, []),
     "fat_norm_bwd_static": (_int, [_ptr] * 6 + [_i64] * 5 + [_dbl, _int, _ptr]),
+    "fat_shifted_ce_fwd": (_int, [_ptr] * 5 + [_int] * 3 + [_i64] * 5 + [_int, _ptr]),
+    "fat_scale_unless_one": (_int, [_ptr, _i64, _ptr, _int, _ptr]),
     "fat_softmax_fwd": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),
     "fat_softmax_bwd": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),
     "fat_attn_fwd": (_int, [_ptr] * 7 + [_int] * 4 + [_p64] * 4 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),

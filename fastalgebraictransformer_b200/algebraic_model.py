@@ -21,7 +21,7 @@ from torch.utils.checkpoint import checkpoint
 
 from .backward import RationalAttentionPackedFunction
 from .forward import compute_alibi_slopes
-from .fused_ops import EPS, RationalSwiGLUPacked, add_mean_error_norm, mean_error_norm
+from .fused_ops import EPS, RationalSwiGLUPacked, add_mean_error_norm, mean_error_norm, shifted_cross_entropy
 
 
 class RationalMR(nn.Module):
@@ -155,10 +155,14 @@ class AlgebraicTransformerLM(nn.Module):
         logits = self.head(y)
         loss = None
         if labels is not None:
-            shift_logits = logits[..., :-1, :].contiguous()
-            shift_labels = labels[..., 1:].contiguous()
-            loss = F.cross_entropy(shift_logits.view(-1, shift_logits.size(-1)), shift_labels.view(-1),
-                                   ignore_index=-100)
+            if logits.dim() == 3 and logits.dtype in (torch.float32, torch.bfloat16, torch.float16):
+                # one pass over the logits yields the loss and its gradient (no shifted copy, no log-softmax tensor)
+                loss = shifted_cross_entropy(logits, labels, -100)
+            else:
+                shift_logits = logits[..., :-1, :].contiguous()
+                shift_labels = labels[..., 1:].contiguous()
+                loss = F.cross_entropy(shift_logits.view(-1, shift_logits.size(-1)), shift_labels.view(-1),
+                                       ignore_index=-100)
         return logits, loss
 
     @torch.no_grad()

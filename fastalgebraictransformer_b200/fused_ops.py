@@ -112,6 +112,30 @@ class AddMeanErrorNorm(torch.autograd.Function):
         return d_sum, d_sum, d_w, None
 
 
+class ShiftedCrossEntropy(torch.autograd.Function):
+    """Mean cross-entropy of logits[:, :-1] against labels[:, 1:] (reference algebraic_model.py:229-235) with the gradient
+    produced by the same pass over the logits; the backward multiplies it by the incoming scalar (a no-op when it is 1)."""
+
+    @staticmethod
+    def forward(ctx, logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+        assert logits.is_cuda, "Input must be on CUDA"
+        loss, d_logits = _alg.shifted_ce_fwd(logits, labels, ignore_index)
+        ctx.save_for_backward(d_logits)
+        return loss.to(logits.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_loss):
+        (d_logits,) = ctx.saved_tensors
+        _alg.scale_unless_one(d_logits, grad_loss.to(torch.float32).reshape(1))
+        return d_logits, None, None
+
+
+def shifted_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """Next-token loss of a [B, T, V] logits tensor against [B, T] labels, as the model computes it."""
+    _require_cuda(logits, "shifted_cross_entropy")
+    return ShiftedCrossEntropy.apply(logits, labels, ignore_index)
+
+
 def _require_cuda(t: torch.Tensor, what: str) -> None:
     if not t.is_cuda:
         raise RuntimeError(f"{what}: CUDA tensor required — this build has no CPU fallback")

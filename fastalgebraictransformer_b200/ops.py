@@ -21,6 +21,8 @@ _libdef.define("swiglu_fwd(Tensor gate, Tensor value) -> Tensor")
 _libdef.define("swiglu_bwd(Tensor d_out, Tensor gate, Tensor value) -> (Tensor, Tensor)")
 _libdef.define("norm_fwd(Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)")
 _libdef.define("norm_bwd(Tensor d_out, Tensor x, Tensor weight, Tensor mean, float eps) -> (Tensor, Tensor)")
+_libdef.define("shifted_ce_fwd(Tensor logits, Tensor labels, int ignore_index) -> (Tensor, Tensor)")
+_libdef.define("scale_unless_one(Tensor(a!) x, Tensor scale) -> ()")
 _libdef.define("add_norm_fwd(Tensor x, Tensor residual, Tensor weight, float eps) -> (Tensor, Tensor, Tensor)")
 _libdef.define("add_norm_bwd(Tensor d_y, Tensor? d_h, Tensor h, Tensor weight, Tensor mean, float eps) -> (Tensor, Tensor)")
 _libdef.define("softmax_fwd(Tensor x, float eps) -> Tensor")
@@ -184,6 +186,36 @@ def _add_norm_bwd(d_y: Tensor, d_h: Optional[Tensor], h: Tensor, weight: Tensor,
     return d_sum, d_w.to(weight.dtype)
 
 
+# ----------------------------------------------------------------------------- shifted cross-entropy (loss head)
+def _shifted_ce_fwd(logits: Tensor, labels: Tensor, ignore_index: int) -> Tuple[Tensor, Tensor]:
+    """(loss, d_logits) of mean cross-entropy between logits[:, :-1] and labels[:, 1:]; loss is a float32 scalar and
+    d_logits ([B, T, V], dtype of logits) is its gradient with respect to logits."""
+    _cuda_check(logits, labels)
+    assert logits.dim() == 3 and labels.shape == logits.shape[:2] and labels.dtype == torch.int64
+    if logits.stride(2) != 1:
+        logits = logits.contiguous()
+    B, T, V = logits.shape
+    counted = labels[:, 1:]
+    n_valid = ((counted != ignore_index) & (counted >= 0) & (counted < V)).sum().to(torch.float32).reshape(1)
+    row_loss = torch.empty(B * T, dtype=torch.float32, device=logits.device)
+    d_logits = torch.empty((B, T, V), dtype=logits.dtype, device=logits.device)
+    if logits.numel():
+        with _lib.device_guard(logits.device):
+            _lib.check(_lib.lib().fat_shifted_ce_fwd(_p(logits), _p(labels), _p(n_valid), _p(row_loss), _p(d_logits), B, T, V,
+                                                     logits.stride(0), logits.stride(1), labels.stride(0), labels.stride(1),
+                                                     ignore_index, _lib.dtype_tag(logits), _lib.stream_ptr(logits.device)))
+    loss = row_loss.sum() / n_valid.clamp_min(1.0).squeeze(0) if logits.numel() else row_loss.sum()
+    return loss, d_logits
+
+
+def _scale_unless_one(x: Tensor, scale: Tensor) -> None:
+    _cuda_check(x, scale)
+    assert x.is_contiguous() and scale.dtype == torch.float32 and scale.numel() == 1
+    if x.numel():
+        with _lib.device_guard(x.device):
+            _lib.check(_lib.lib().fat_scale_unless_one(_p(x), x.numel(), _p(scale), _lib.dtype_tag(x), _lib.stream_ptr(x.device)))
+
+
 # ----------------------------------------------------------------------------- rational softmax
 def _softmax_fwd(x: Tensor, eps: float) -> Tensor:
     _cuda_check(x)
@@ -294,6 +326,7 @@ def attn_bwd_packed(qkv: Tensor, out: Tensor, out_lo: Tensor, L: Tensor, d_out: 
 
 for _name, _fn in (("swiglu_fwd", _swiglu_fwd), ("swiglu_bwd", _swiglu_bwd), ("norm_fwd", _norm_fwd),
                    ("norm_bwd", _norm_bwd), ("add_norm_fwd", _add_norm_fwd), ("add_norm_bwd", _add_norm_bwd),
+                   ("shifted_ce_fwd", _shifted_ce_fwd), ("scale_unless_one", _scale_unless_one),
                    ("softmax_fwd", _softmax_fwd), ("softmax_bwd", _softmax_bwd),
                    ("attn_fwd", _attn_fwd), ("attn_bwd", _attn_bwd)):
     _libdef.impl(_name, _fn, "CUDA")
@@ -320,6 +353,16 @@ def _(x, weight, eps):
 @torch.library.register_fake(f"{_NS}::norm_bwd")
 def _(d_out, x, weight, mean, eps):
     return torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(weight)
+
+
+@torch.library.register_fake(f"{_NS}::shifted_ce_fwd")
+def _(logits, labels, ignore_index):
+    return logits.new_empty((), dtype=torch.float32), torch.empty_like(logits, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{_NS}::scale_unless_one")
+def _(x, scale):
+    return None
 
 
 @torch.library.register_fake(f"{_NS}::add_norm_fwd")

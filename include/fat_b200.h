@@ -85,6 +85,24 @@ FAT_API int fat_swiglu_bwd(const void* d_out, const void* gate, const void* valu
                    int dtype, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Shifted cross-entropy of the language-model head, forward and gradient in one pass.
+ * Replaces the loss of AlgebraicTransformerLM.forward (algebraic_model.py:229-235):
+ *   F.cross_entropy(logits[..., :-1, :].contiguous().view(-1, V), labels[..., 1:].contiguous().view(-1), ignore_index)
+ * logits [B, T, V] (unit stride along V), labels [B, T] int64.  Row (b, t) is scored against labels[b, t+1]; the
+ * last position of every sequence and targets equal to ignore_index (or outside [0, V)) contribute nothing.
+ *   row_loss [B*T] float32: the row's -log softmax(logits)[target], 0 for rows that do not count;
+ *   d_logits [B*T, V] (dtype of logits, dense): (softmax - onehot) / n_valid[0], 0 for rows that do not count;
+ *   n_valid: device pointer to the number of rows that count, as float32 (the caller counts the labels).
+ * loss = sum(row_loss) / n_valid.  fat_scale_unless_one multiplies d_logits by the scalar gradient that reaches the
+ * loss and returns without touching memory when that scalar is exactly 1.  dtypes: F32, BF16, F16.
+ * ---------------------------------------------------------------------------------- */
+FAT_API int fat_shifted_ce_fwd(const void* logits, const int64_t* labels, const float* n_valid, float* row_loss,
+                 void* d_logits, int B, int T, int V, int64_t logits_batch_stride, int64_t logits_token_stride,
+                 int64_t labels_batch_stride, int64_t labels_token_stride, int64_t ignore_index, int dtype, void* stream);
+
+FAT_API int fat_scale_unless_one(void* x, int64_t n, const float* scale, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Mean-error normalisation.  mean_r = mean_c |x_rc| (float32, [n_rows], saved for the
  * backward), y = x / (mean + eps) * weight.
  * Replaces MeanErrorNorm.forward / mean_error_norm_fwd_kernel (fused_ops.py:295-342, 542-569).

@@ -64,6 +64,14 @@ def add_mean_error_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.T
     return h, mean_error_norm(h, weight, eps)
 
 
+def shifted_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """The language-model loss exactly as the reference writes it (algebraic_model.py:229-235)."""
+    shift_logits = logits[..., :-1, :].contiguous()
+    shift_labels = labels[..., 1:].contiguous()
+    return torch.nn.functional.cross_entropy(shift_logits.view(-1, shift_logits.size(-1)), shift_labels.view(-1),
+                                             ignore_index=ignore_index)
+
+
 def compute_alibi_slopes(n_heads: int) -> torch.Tensor:
     """ALiBi slopes (forward.py:21-42).
 

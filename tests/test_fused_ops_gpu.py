@@ -197,6 +197,51 @@ def test_add_norm_only_one_result_used():
             assert norm_max_err(leaves[2].grad, ref[2].grad) < FP32_TOL
 
 
+# ----------------------------------------------------------------------------- shifted cross-entropy (loss head)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2, 32, 128), (3, 17, 1000), (2, 9, 1001), (1, 2, 8), (2, 5, 32000), (1, 3, 50000), (4, 1, 64)])
+def test_shifted_cross_entropy_vs_oracle(shape, dtype):
+    """Loss and d(loss)/d(logits) against the reference's own formulation (algebraic_model.py:229-235) in float32 on the
+    rounded logits; some targets are ignore_index, T = 1 leaves nothing to score.  Covers the register-cached rows, the
+    rows that are re-read (odd V, float32 rows wider than the cache) and a non-unit incoming gradient."""
+    B, T, V = shape
+    g = torch.Generator().manual_seed(51)
+    logits = (torch.randn(B, T, V, generator=g) * 3).to(dtype)
+    labels = torch.randint(0, V, (B, T), generator=g)
+    labels[torch.rand(B, T, generator=g) < 0.2] = -100
+    leaf = logits.to(DEV).requires_grad_(True)
+    loss = fat().shifted_cross_entropy(leaf, labels.to(DEV), -100)
+    (loss.float() * 3.0).backward()
+    ref = logits.float().requires_grad_(True)
+    want = oracle.shifted_cross_entropy(ref, labels, -100)
+    if T == 1 or bool((labels[:, 1:] == -100).all()):
+        assert float(loss.detach()) == 0.0 and float(leaf.grad.abs().max()) == 0.0      # the reference gives nan here (0/0)
+        return
+    (want * 3.0).backward()
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert abs(float(loss.detach()) - float(want.detach())) <= tol * max(1.0, abs(float(want.detach())))
+    gerr = (leaf.grad.float().cpu() - ref.grad).abs().max() / ref.grad.abs().max()
+    assert gerr < (1e-5 if dtype == torch.float32 else 1e-2), gerr
+    assert float(leaf.grad[:, -1].abs().max()) == 0.0                       # the last position is never scored
+
+
+def test_shifted_cross_entropy_strided_logits_and_unit_gradient():
+    """Logits that are a view with a token stride (as a head applied to a padded buffer would give) and the plain
+    loss.backward() path, where the gradient is used exactly as the forward wrote it."""
+    g = torch.Generator().manual_seed(52)
+    big = torch.randn(2, 12, 256, generator=g)
+    labels = torch.randint(0, 256, (2, 6), generator=g)
+    view = big.to(DEV)[:, ::2, :].requires_grad_(True)
+    assert not view.is_contiguous()
+    loss = fat().shifted_cross_entropy(view, labels.to(DEV))
+    (gr,) = torch.autograd.grad(loss, view)
+    ref = big[:, ::2, :].clone().requires_grad_(True)
+    want = oracle.shifted_cross_entropy(ref, labels)
+    want.backward()
+    assert abs(float(loss.detach()) - float(want.detach())) < 1e-5 * float(want.detach())
+    assert norm_max_err(gr, ref.grad) < FP32_TOL
+
+
 def test_norm_weight_randn_like_reference_test():
     """tests.py:141-173 draws the weight from randn; thresholds fwd 1e-4, grads 1e-3 (max abs)."""
     x, go = gen(16, (4, 1024, 1024), (4, 1024, 1024))
