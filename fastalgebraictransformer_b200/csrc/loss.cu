@@ -18,8 +18,13 @@ namespace fat {
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kCeThreads = 512;
 constexpr int kCePacks = 16;                       // 16-byte packs of one row a thread keeps in registers
+
+__device__ __forceinline__ float fast_exp2(float x) {      // x <= 0 here: flushing tiny results to zero is harmless
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int NT>
 __device__ __forceinline__ float block_reduce(float v, float* buf, bool is_max) {
@@ -38,9 +43,10 @@ __device__ __forceinline__ float block_reduce(float v, float* buf, bool is_max) 
   return r;
 }
 
-// One block per row.  CACHED: the row is aligned and fits in kCePacks packs per thread; otherwise it is re-read from
-// global memory (L2) for each of the three sweeps.
-template <typename T, bool CACHED>
+// One block of NT threads per row.  CACHED: the row is aligned and fits in kCePacks packs per thread; otherwise it is
+// re-read from global memory (L2) for each of the three sweeps.  Rows of up to NT * kCePacks packs take the smaller
+// block size, so that two or three blocks share an SM and fill each other's reduction barriers.
+template <typename T, int kCeThreads, bool CACHED>
 __global__ void __launch_bounds__(kCeThreads)
 shifted_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels, const float* __restrict__ n_valid,
                   float* __restrict__ row_loss, T* __restrict__ d_logits, int B, int Tn, int V,
@@ -90,11 +96,11 @@ shifted_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labe
         if (tid + i * kCeThreads < npk) {
           const T* e = reinterpret_cast<const T*>(&raw[i]);
 #pragma unroll
-          for (int j = 0; j < W; ++j) s += exp2f(fmaf(Elem<T>::to_c(e[j]), kLog2e, -off));
+          for (int j = 0; j < W; ++j) s += fast_exp2(fmaf(Elem<T>::to_c(e[j]), kLog2e, -off));
         }
       }
     } else {
-      for (int c = tid; c < V; c += kCeThreads) s += exp2f(fmaf(Elem<T>::to_c(x[c]), kLog2e, -off));
+      for (int c = tid; c < V; c += kCeThreads) s += fast_exp2(fmaf(Elem<T>::to_c(x[c]), kLog2e, -off));
     }
     s = block_reduce<kCeThreads>(s, buf, false);
     const float inv = scale / s;                   // softmax normaliser and 1/n_valid in one factor
@@ -108,7 +114,7 @@ shifted_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labe
           float o[W];
 #pragma unroll
           for (int j = 0; j < W; ++j) {
-            o[j] = exp2f(fmaf(Elem<T>::to_c(e[j]), kLog2e, -off)) * inv;
+            o[j] = fast_exp2(fmaf(Elem<T>::to_c(e[j]), kLog2e, -off)) * inv;
             if (pk * W + j == tgt) o[j] -= scale;
           }
           store_pack<T, W>(dx + int64_t(pk) * W, o);
@@ -116,7 +122,7 @@ shifted_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labe
       }
     } else {
       for (int c = tid; c < V; c += kCeThreads) {
-        float o = exp2f(fmaf(Elem<T>::to_c(x[c]), kLog2e, -off)) * inv;
+        float o = fast_exp2(fmaf(Elem<T>::to_c(x[c]), kLog2e, -off)) * inv;
         if (c == tgt) o -= scale;
         dx[c] = Elem<T>::from_c(o);
       }
@@ -140,16 +146,17 @@ int shifted_ce_t(const void* logits, const int64_t* labels, const float* n_valid
                  int B, int Tn, int V, int64_t ls_b, int64_t ls_t, int64_t lab_b, int64_t lab_t, int64_t ignore_index,
                  cudaStream_t st) {
   constexpr int W = 16 / sizeof(T);
-  const bool cached = V % W == 0 && V / W <= kCeThreads * kCePacks && ls_b % W == 0 && ls_t % W == 0 &&
-                      reinterpret_cast<uintptr_t>(logits) % 16 == 0 && reinterpret_cast<uintptr_t>(d_logits) % 16 == 0;
+  const bool aligned = V % W == 0 && ls_b % W == 0 && ls_t % W == 0 && reinterpret_cast<uintptr_t>(logits) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(d_logits) % 16 == 0;
   const int64_t rows = int64_t(B) * Tn;
   const unsigned grid = unsigned(rows < 64 * kNumSM ? rows : 64 * kNumSM);
-  if (cached)
-    shifted_ce_kernel<T, true><<<grid, kCeThreads, 0, st>>>((const T*)logits, labels, n_valid, row_loss, (T*)d_logits, B, Tn, V,
-                                                            ls_b, ls_t, lab_b, lab_t, ignore_index);
-  else
-    shifted_ce_kernel<T, false><<<grid, kCeThreads, 0, st>>>((const T*)logits, labels, n_valid, row_loss, (T*)d_logits, B, Tn, V,
-                                                             ls_b, ls_t, lab_b, lab_t, ignore_index);
+  auto go = [&](auto kern, int threads) {
+    kern<<<grid, threads, 0, st>>>((const T*)logits, labels, n_valid, row_loss, (T*)d_logits, B, Tn, V, ls_b, ls_t, lab_b, lab_t,
+                                   ignore_index);
+  };
+  if (aligned && V / W <= 256 * kCePacks) go(shifted_ce_kernel<T, 256, true>, 256);
+  else if (aligned && V / W <= 512 * kCePacks) go(shifted_ce_kernel<T, 512, true>, 512);
+  else go(shifted_ce_kernel<T, 512, false>, 512);
   return check_launch("shifted_ce");
 }
 
