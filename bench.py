@@ -395,7 +395,11 @@ def bench_lm(args, rank, world, device, name):
     net = model
     if world > 1:
         from torch.nn.parallel import DistributedDataParallel as DDP
-        net = DDP(model, device_ids=[device.index], gradient_as_bucket_view=True, bucket_cap_mb=64)
+        ddp_stream = torch.cuda.Stream(device)            # DDP is built on a side stream so that its step can be captured
+        ddp_stream.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(ddp_stream):
+            net = DDP(model, device_ids=[device.index], gradient_as_bucket_view=True, bucket_cap_mb=64)
+        torch.cuda.current_stream(device).wait_stream(ddp_stream)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True, capturable=True)
     g = torch.Generator().manual_seed(1234 + 3 + rank)
     hids = torch.randint(0, cfg["vocab_size"], (cfg["batch"], cfg["seq"]), generator=g).pin_memory()
@@ -418,16 +422,17 @@ def bench_lm(args, rank, world, device, name):
         opt.step()
         last["loss_host"] = loss.item()
 
-    # One GPU: the whole step (forward, loss, backward, AdamW) is captured once in a CUDA graph, because issuing
-    # its ~1000 launches from Python takes about as long as executing them.  Several GPUs: eager DDP.
+    # The whole step (forward, loss, backward with DDP's bucketed all-reduces, AdamW) is captured once in a CUDA graph,
+    # because issuing its ~1000 launches from Python takes longer than executing them.  DDP wants 11 eager steps on a
+    # side stream before a capture.
     launch = "eager"
     timed = step
-    if world == 1 and not args.no_graph:
+    if not args.no_graph:
         try:
             side = torch.cuda.Stream(device)
             side.wait_stream(torch.cuda.current_stream(device))
             with torch.cuda.stream(side):
-                for _ in range(3):
+                for _ in range(3 if world == 1 else 11):
                     step()
             torch.cuda.current_stream(device).wait_stream(side)
             graph = torch.cuda.CUDAGraph()
@@ -574,6 +579,9 @@ def main():
     torch.cuda.set_device(device)
     if world > 1:
         import torch.distributed as dist
+        if args.workload in LM and not args.no_graph:
+            # the DDP step is captured in a CUDA graph: the watchdog must not poll work objects captured there
+            os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")
         dist.init_process_group("nccl", device_id=device)
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE", file=sys.stderr)
