@@ -276,6 +276,8 @@ FUSED = {
     "softmax": dict(rows=4096, cols=4096, bytes=150994944, traffic=106e6),   # backward reads d_out and x only (p is recomputed)
     # residual addition fused with the norm: forward x, residual in, sum, y out; backward d_y, d_sum_in, sum in, d_sum out
     "add_norm": dict(rows=16384, cols=4096, bytes=8 * 16384 * 4096 * 2, traffic=None),
+    # loss head of the small LM: logits [8, 1024, 32000] read once, their gradient written once
+    "loss_head": dict(rows=8 * 1024, cols=32000, bytes=2 * 8 * 1024 * 32000 * 2, traffic=None),
 }
 
 
@@ -299,6 +301,9 @@ def bench_fused(args, rank, world, device, name):
         elif name == "add_norm":
             w = (1 + 0.1 * torch.randn(cfg["cols"], generator=g, device=device)).to(torch.bfloat16)
             sets.append((rnd(), w, rnd(), rnd(), rnd()))                       # x, weight, residual, d_y, d_h
+        elif name == "loss_head":
+            labels = torch.randint(0, cfg["cols"], (8, 1024), generator=g, device=device)
+            sets.append((rnd(2.0).view(8, 1024, cfg["cols"]), labels))
         else:
             sets.append((rnd(math.sqrt(2.0)).requires_grad_(True), rnd()))
     it = [0]
@@ -314,6 +319,8 @@ def bench_fused(args, rank, world, device, name):
         elif name == "add_norm":
             h, y, mean = alg.add_norm_fwd(s[0], s[2], s[1], 1e-6)
             alg.add_norm_bwd(s[3], s[4], h, s[1], mean, 1e-6)
+        elif name == "loss_head":
+            alg.shifted_ce_fwd(s[0], s[1], -100)
         else:
             alg.softmax_fwd(s[0].detach(), 1e-6); alg.softmax_bwd(s[1], s[0].detach(), 1e-6)
 
@@ -352,6 +359,9 @@ def bench_fused(args, rank, world, device, name):
         if name == "norm":
             a, w = d[0].requires_grad_(True), d[1].requires_grad_(True)
             o = fat.mean_error_norm(a, w); o.backward(d[2]); return (o.detach(), a.grad)
+        if name == "loss_head":
+            a = d[0].requires_grad_(True)
+            loss = fat.shifted_cross_entropy(a, d[1]); loss.backward(); return (loss.detach().reshape(1), a.grad)
         if name == "add_norm":
             a, w, r = d[0].requires_grad_(True), d[1].requires_grad_(True), d[2].requires_grad_(True)
             h, y = fat.add_mean_error_norm(a, r, w)
@@ -361,7 +371,7 @@ def bench_fused(args, rank, world, device, name):
 
     e2e_step = make_pipelined_e2e(device, hs, e2e_compute)
     ms_e2e = time_steps(e2e_step, 6, 2, world, device)
-    n_out = {"swiglu": 3, "norm": 2, "softmax": 2, "add_norm": 3}[name]
+    n_out = {"swiglu": 3, "norm": 2, "softmax": 2, "add_norm": 3, "loss_head": 1}[name]
     return {
         "metric": f"rational_{name}_fwd_bwd_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "dtype": "bf16",
         "config": {"workload": f"{name} fwd+bwd bf16 [{cfg['rows']},{cfg['cols']}] (bandwidth-sweep configuration)",
@@ -371,7 +381,7 @@ def bench_fused(args, rank, world, device, name):
         "e2e": {"value": cfg["bytes"] * world / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in hs),
                 "d2h_bytes_per_step": n_out * shape[0] * shape[1] * 2, "ms_per_step": ms_e2e, "overlap": E2E_OVERLAP},
-        "gpu_launches": (3 if name in ("norm", "add_norm") else 2) * args.steps,
+        "gpu_launches": {"norm": 3, "add_norm": 3, "loss_head": 1}.get(name, 2) * args.steps,
         "roofline": {"bound": "hbm", "kernel": f"{name} fwd+bwd", "achieved": gbs / world, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": gbs / world / peaks["hbm_gbs"], "traffic": cfg["traffic"],
                      "peak_source": peaks["source"]},
@@ -558,7 +568,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "add_norm", "lm_small", "lm_xl"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "add_norm", "loss_head", "lm_small", "lm_xl"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0,
                     help="attn workload: override the batch size (profiling captures use a smaller case)")
