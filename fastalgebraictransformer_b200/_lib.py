@@ -108,6 +108,10 @@ def check_device_status(device=None) -> None:
         v = int(word.item())
         if v:
             word.zero_()
+            if v & 0x40000000:
+                raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x}: the fused attention backward found its "
+                                   "dynamic shared memory not 1024-byte aligned and did nothing; request path 3 "
+                                   "(PATH_TENSOR_DETERMINISTIC) on this platform")
             raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x} "
                                f"(code {v >> 24}: a bounded wait inside a kernel ran out, detail {v & 0xffffff})")
 
