@@ -1,8 +1,8 @@
 // Causal rational attention backward on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
 //
-// Default for D = 128: prepare (1), a float32 d_q accumulator cleared with a memset, the fused key-major
+// Default: prepare (1), a float32 d_q accumulator cleared with a memset, the fused key-major
 // kernel (4) that produces d_k, d_v and adds its d_q contributions with TMA reduce-add, and a convert pass.
-// Deterministic variant (and D = 64): three launches, no atomics, bit-reproducible:
+// Deterministic variant: three launches, no atomics, bit-reproducible:
 //   1. prepare:  per query row  inv = 1/(L+eps) and Delta = dO . O  (two padded float32 arrays)
 //   2. d_q kernel, query-major (one 128-query tile per CTA, key tiles streamed):
 //                S = Q K^T, dP = dO V^T -> dS = g inv (dP - Delta) (16-bit, packed into TMEM over dP)
@@ -608,7 +608,7 @@ struct FusedSmem {
   alignas(1024) unsigned char v[kTileBytes];
   alignas(1024) unsigned char q[2][kTileBytes];             // q[0] doubles as d_v staging in the epilogue
   alignas(1024) unsigned char dout[kTileBytes];             // doubles as d_k staging in the epilogue
-  alignas(1024) unsigned char ds[kTileBytes];               // dS^T, 16-bit [128 keys][128 queries]
+  alignas(1024) unsigned char ds[BLK * BLK * 2];            // dS^T, 16-bit [128 keys][128 queries]
   alignas(1024) float dq_stage[64 * D];                     // d_q staging tile [64 query rows][D]
   alignas(16) float delta[2][BLK];
   alignas(16) float inv[2][BLK];
@@ -623,7 +623,7 @@ struct FusedMaps { CUtensorMap q, dout, k, v, dk, dv, dq_acc; };    // dq_acc: f
 template <typename T, int D>
 __global__ void __launch_bounds__(kFusedThreads, 1)
 attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParams p) {
-  static_assert(D == 128 && kEwGroups == 2, "laid out for D = 128 and two element-wise warpgroups");
+  static_assert((D == 128 || D == 64) && kEwGroups == 2, "laid out for D = 64 or 128 and two element-wise warpgroups");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   using S = FusedSmem<D>;
   S& sm = *reinterpret_cast<S*>(smem_raw);
@@ -653,7 +653,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t tS = tmem, tP = tmem + BLK, tV = tmem + 2 * BLK, tK = tmem + 3 * BLK;
+  const uint32_t tS = tmem, tP = tmem + BLK, tV = tmem + 2 * BLK, tK = tV + D;
 
   if (warp >= kFusedTmaWarp) {
     reg_share_dec<kFusedRegsAux>();                             // warps 12..15 (15 only takes part in this)
@@ -729,8 +729,11 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
             if (!(ok = g.wait(&sm.ds_full, i & 1, 156))) break;                          // phase B done: dS^T in smem, dP^T read
             TR_STAMP(128 + 24 * (i - 10) + 3, i >= 10 && i < 13);
             tc_fence_after();
+            // dQ^T = K^T dS^T over the keys.  The MMA is always 128 rows tall: with D = 64 the second 64-row chunk of the
+            // MN-major A operand is the tile that follows K in shared memory (V), so TMEM lanes 64..127 receive numbers
+            // nobody reads; the tensor pipe has the time, and M = 64 would use another accumulator layout.
 #pragma unroll
-            for (int s = 0; s < BLK / 16; ++s)                                           // dQ^T = K^T dS^T over the keys
+            for (int s = 0; s < BLK / 16; ++s)
               mma_ss(tP, kd_mn + ((s * 2048) >> 4), dsd_mn + ((s * 2048) >> 4), idesc_dq, s > 0);
             mma_commit(&sm.dq_full);
 #pragma unroll
@@ -768,8 +771,10 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
         if (dl == 0) tma_store_wait_read1();
         named_barrier(3, 128);
       }
+      if (dl < D) {
 #pragma unroll
-      for (int qi = 0; qi < 32; ++qi) stage[qi * D + dl] = __uint_as_float(v[qi]);
+        for (int qi = 0; qi < 32; ++qi) stage[qi * D + dl] = __uint_as_float(v[qi]);
+      }
       fence_async_smem();
       named_barrier(3, 128);
       if (dl == 0 && row < p.T) {
@@ -791,10 +796,12 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
       tmem_wait_ld_regs(c);
       if (dl == 0) tma_store_wait_read();                     // both staging tiles are free (the previous step's reduces were issued long ago)
       named_barrier(3, 128);
+      if (dl < D) {                                           // lanes beyond the head dimension hold nothing (D = 64)
 #pragma unroll
-      for (int qi = 0; qi < 32; ++qi) {
-        stage0[qi * D + dl] = __uint_as_float(a[qi]);
-        stage1[qi * D + dl] = __uint_as_float(c[qi]);
+        for (int qi = 0; qi < 32; ++qi) {
+          stage0[qi * D + dl] = __uint_as_float(a[qi]);
+          stage1[qi * D + dl] = __uint_as_float(c[qi]);
+        }
       }
       tmem_ld32(tmem_addr(tP, lane_base, 64), a);            // second half into the same registers: dQ^T leaves TMEM early
       tmem_ld32(tmem_addr(tP, lane_base, 96), c);
@@ -1019,10 +1026,9 @@ int launch_bwd_split(const AttnParams& p, cudaStream_t st) {
   return launch_main(attn_bwd_dkv_tc_kernel<T, D>, mk, p, sizeof(DkvSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dkv_tc");
 }
 
-// Fused backward (D = 128): prepare, clear the float32 d_q accumulator, fused kernel, convert d_q.
-template <typename T>
+// Fused backward: prepare, clear the float32 d_q accumulator, fused kernel, convert d_q.
+template <typename T, int D>
 int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
-  constexpr int D = 128;
   float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.delta) + stats_bytes(p.B, p.H, p.T));
   const size_t acc_bytes = size_t(p.B) * p.H * p.T * D * sizeof(float);
   auto kern = attn_bwd_fused_tc_kernel<T, D>;
@@ -1052,15 +1058,15 @@ int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
 
 template <typename T>
 int launch_bwd(const AttnParams& p, cudaStream_t st) {
-  if (p.D == 128) return p.deterministic ? launch_bwd_split<T, 128>(p, st) : launch_bwd_fused<T>(p, st);
-  return launch_bwd_split<T, 64>(p, st);
+  if (p.D == 128) return p.deterministic ? launch_bwd_split<T, 128>(p, st) : launch_bwd_fused<T, 128>(p, st);
+  return p.deterministic ? launch_bwd_split<T, 64>(p, st) : launch_bwd_fused<T, 64>(p, st);
 }
 
 }  // namespace
 
 size_t attn_bwd_tc_workspace_bytes(int B, int H, int T, int D) {
   // Delta and 1/(L+eps) (rows padded to whole tiles), then the float32 d_q accumulator of the fused kernel
-  return stats_bytes(B, H, T) + (D == 128 ? size_t(B) * H * T * D * sizeof(float) : 0);
+  return stats_bytes(B, H, T) + size_t(B) * H * T * D * sizeof(float);
 }
 
 int attn_bwd_tc(const AttnParams& p, int dtype, cudaStream_t st) {

@@ -157,20 +157,24 @@ def test_low_precision_vs_oracle(shape, dtype, path):
 
 
 def test_deterministic():
-    """No atomics anywhere: two runs give bit-identical outputs and gradients."""
+    """The CUDA-core path and the deterministic tensor path (no atomics anywhere): two runs give bit-identical outputs
+    and gradients."""
+    from fastalgebraictransformer_b200 import PATH_SIMT, PATH_TENSOR_DETERMINISTIC
     B, H, T, D = 1, 4, 300, 64
     q, k, v, go = gen_qkv(27, B, H, T, D, torch.bfloat16)
     slopes = oracle.compute_alibi_slopes(H)
-    a = run_attention(q, k, v, go, slopes, 0.125)
-    b = run_attention(q, k, v, go, slopes, 0.125)
-    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    for path in (PATH_SIMT, PATH_TENSOR_DETERMINISTIC):
+        a = run_attention(q, k, v, go, slopes, 0.125, path=path)
+        b = run_attention(q, k, v, go, slopes, 0.125, path=path)
+        assert all(torch.equal(x, y) for x, y in zip(a, b)), path
 
 
-def test_deterministic_tensor_path_d128():
-    """D=128: the default backward accumulates d_q across key tiles with reduce-adds (order varies between runs, so its
-    last bits may); path 3 selects the two-kernel backward, which is bit-reproducible."""
+@pytest.mark.parametrize("D", [64, 128])
+def test_deterministic_tensor_path(D):
+    """The default tensor-core backward accumulates d_q across key tiles with reduce-adds (order varies between runs, so
+    its last bits may); path 3 selects the two-kernel backward, which is bit-reproducible."""
     from fastalgebraictransformer_b200 import PATH_TENSOR_DETERMINISTIC
-    B, H, T, D = 1, 4, 700, 128
+    B, H, T = 1, 4, 700
     q, k, v, go = gen_qkv(29, B, H, T, D, torch.bfloat16)
     slopes = oracle.compute_alibi_slopes(H)
     a = run_attention(q, k, v, go, slopes, 0.09, path=PATH_TENSOR_DETERMINISTIC)
