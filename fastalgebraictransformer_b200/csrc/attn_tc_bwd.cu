@@ -582,13 +582,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
 
 
 // ------------------------------------------------------------------------------------- 4. fused d_k / d_v / d_q kernel
-// Key-major: one CTA owns a 128-key tile and walks the 128-query tiles that see it.  Every GEMM is a full
-// 128x128x128 (tcgen05.mma below N = 128 runs at about half rate).  TMEM is exactly full:
+// Key-major: one CTA owns a 128-key tile and walks the 128-query tiles that see it.  With D = 128 every GEMM is a
+// full 128x128x128 (tcgen05.mma below N = 128 runs at about half rate) and TMEM is exactly full:
 //   R1 [0,128)    S^T, then the packed P^T over it         R2 [128,256)  dP^T, then dQ^T over it
-//   dV [256,384)  dK [384,512)
+//   dV [256,256+D)  dK [256+D,256+2D)
 // dS^T goes to shared memory ([128 keys][128 queries], 16-bit): K-major A operand of dK += dS^T Q and MN-major B
 // operand of dQ^T = K^T dS^T.  Four drain warps move dQ^T (head dimension on the TMEM lanes) through shared
-// memory, transposed, into a float32 accumulator in global memory with TMA reduce-add, 64 query rows at a time.
+// memory, transposed, into a float32 accumulator in global memory with TMA reduce-add, 32 query rows at a time.
 // dO has a single buffer: dO(i+1) is only needed once dQ^T(i) has been drained, long after dV(i) released dO(i).
 // The element-wise warps keep g for 64 score columns in registers between phase A and phase B, which needs
 // about 168 registers per thread; the other warps need far fewer, so the warpgroups trade registers with
