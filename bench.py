@@ -243,7 +243,7 @@ def bench_attn(args, rank, world, device):
     nbytes = hq.numel() * hq.element_size()
 
     peaks = measured_peaks()
-    launches_per_step = {1: 3, 2: 5}.get(path, 3)       # tensor path: forward, prepare, memset, fused backward, d_q convert
+    launches_per_step = {1: 3, 2: 4}.get(path, 3)       # tensor path: forward, prepare (+ accumulator clear), fused backward, d_q convert
     tfl = (fwd_flops + bwd_flops) * world / (ms * 1e-3) / 1e12
     bwd_tfl = bwd_flops / (ms_bwd * 1e-3) / 1e12
     return {

@@ -1,6 +1,6 @@
 // Causal rational attention backward on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
 //
-// Default: prepare (1), a float32 d_q accumulator cleared with a memset, the fused key-major
+// Default: prepare (1), which also clears a float32 d_q accumulator, the fused key-major
 // kernel (4) that produces d_k, d_v and adds its d_q contributions with TMA reduce-add, and a convert pass.
 // Deterministic variant: three launches, no atomics, bit-reproducible:
 //   1. prepare:  per query row  inv = 1/(L+eps) and Delta = dO . O  (two padded float32 arrays)
@@ -46,7 +46,7 @@ __host__ __device__ inline int64_t pad_rows(int T) { return int64_t((T + BLK - 1
 constexpr int kPrepRows = 64;
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
-attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out) {
+attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out, float* __restrict__ dq_zero) {
   constexpr int LPR = D / 8;                      // lanes per row, 16 bytes each
   constexpr int RPW = 32 / LPR;                   // rows per warp
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane / LPR, l = lane % LPR;
@@ -60,6 +60,11 @@ attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out) {
   const float* Lrow = p.L + int64_t(bh) * p.T;
   float* delta_row = p.delta + int64_t(bh) * Tp;
   float* inv_row = inv_out + int64_t(bh) * Tp;
+  if (dq_zero) {                                  // clear this block's rows of the float32 d_q accumulator (dense [B,H,T,D])
+    const int rows = min(kPrepRows, p.T - t0);
+    float4* z = reinterpret_cast<float4*>(dq_zero + (int64_t(bh) * p.T + t0) * D);
+    for (int i = threadIdx.x; i < rows * (D / 4); i += 256) __stcs(z + i, make_float4(0.f, 0.f, 0.f, 0.f));
+  }
 #pragma unroll 2
   for (int t = t0 + warp * RPW + sub; t < t0 + kPrepRows; t += 8 * RPW) {
     const bool live = t < p.T;
@@ -988,11 +993,12 @@ attn_bwd_dq_convert_kernel(const AttnParams p, const float* __restrict__ dq_acc,
 
 size_t stats_bytes(int B, int H, int T) { return (2 * size_t(B) * H * pad_rows(T) * sizeof(float) + 1023) / 1024 * 1024; }
 
+// dq_zero: the fused backward's float32 d_q accumulator, cleared by the same pass (nullptr: nothing to clear)
 template <typename T, int D>
-int launch_prepare(const AttnParams& p, cudaStream_t st) {
+int launch_prepare(const AttnParams& p, cudaStream_t st, float* dq_zero = nullptr) {
   float* inv_rows = p.delta + int64_t(p.B) * p.H * pad_rows(p.T);
   const unsigned blocks = unsigned(p.B) * p.H * unsigned(pad_rows(p.T) / kPrepRows);
-  attn_bwd_prepare_kernel<T, D><<<blocks, 256, 0, st>>>(p, inv_rows);
+  attn_bwd_prepare_kernel<T, D><<<blocks, 256, 0, st>>>(p, inv_rows, dq_zero);
   return check_launch("attn_bwd_prepare");
 }
 
@@ -1026,11 +1032,10 @@ int launch_bwd_split(const AttnParams& p, cudaStream_t st) {
   return launch_main(attn_bwd_dkv_tc_kernel<T, D>, mk, p, sizeof(DkvSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dkv_tc");
 }
 
-// Fused backward: prepare, clear the float32 d_q accumulator, fused kernel, convert d_q.
+// Fused backward: prepare (which also clears the float32 d_q accumulator), fused kernel, convert d_q.
 template <typename T, int D>
 int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
   float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.delta) + stats_bytes(p.B, p.H, p.T));
-  const size_t acc_bytes = size_t(p.B) * p.H * p.T * D * sizeof(float);
   auto kern = attn_bwd_fused_tc_kernel<T, D>;
   cudaFuncAttributes fa;
   if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
@@ -1048,8 +1053,7 @@ int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
       !make_tmap_bhtd(&m.dv, p.d_v, p.B, p.H, p.T, D, p.dvs, 64, BLK) ||
       !make_tmap_bhtd_f32(&m.dq_acc, dq_acc, p.B, p.H, p.T, D, D, 32))
     return FAT_ERR_LAUNCH;
-  if (int rc = launch_prepare<T, D>(p, st)) return rc;
-  if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) { set_error("attn_bwd_fused: clearing the d_q accumulator failed"); return FAT_ERR_LAUNCH; }
+  if (int rc = launch_prepare<T, D>(p, st, dq_acc)) return rc;
   if (int rc = launch_main(kern, m, p, sizeof(FusedSmem<D>), kFusedThreads, st, "attn_bwd_fused_tc")) return rc;
   const unsigned blocks = unsigned(p.B) * p.H * unsigned((p.T + kConvRows - 1) / kConvRows);
   attn_bwd_dq_convert_kernel<T, D><<<blocks, 256, 0, st>>>(p, dq_acc, 0.25f * p.scale / kOpScale);
