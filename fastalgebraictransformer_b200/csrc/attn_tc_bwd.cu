@@ -164,7 +164,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
   S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5;
   int rank, bh;
-  if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, rank, bh)) return;   // padding block of the banded order
+  if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kBwdBands, rank, bh)) return;   // padding block of the banded order
   const int b = bh / p.H, h = bh % p.H;
   const int qt = (p.T + BLK - 1) / BLK - 1 - rank;           // long rows first
   const int n = qt + 1;                                      // key tiles 0..qt (causal)
@@ -385,7 +385,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
   S& sm = *reinterpret_cast<S*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5;
   int kt, bh;                                                // rank = key tile: early key tiles see the most queries
-  if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kt, bh)) return;     // padding block of the banded order
+  if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kBwdBands, kt, bh)) return;     // padding block of the banded order
   const int b = bh / p.H, h = bh % p.H;
   const int n_q_total = (p.T + BLK - 1) / BLK;
   const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
@@ -634,7 +634,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   S& sm = *reinterpret_cast<S*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5;
   int kt, bh;                                                // rank = key tile: early key tiles see the most queries
-  if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kt, bh)) return;     // padding block of the banded order
+  if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kBwdBands, kt, bh)) return;     // padding block of the banded order
   const int b = bh / p.H, h = bh % p.H;
   const int n_q_total = (p.T + BLK - 1) / BLK;
   const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
@@ -1008,7 +1008,7 @@ int launch_main(Kern kern, const Maps& maps, const AttnParams& p, size_t smem, i
     set_error("%s: cannot reserve %zu bytes of shared memory", what, smem);
     return FAT_ERR_LAUNCH;
   }
-  const dim3 grid(banded_grid((p.T + BLK - 1) / BLK, p.B * p.H));
+  const dim3 grid(banded_grid((p.T + BLK - 1) / BLK, p.B * p.H, kBwdBands));
   kern<<<grid, threads, smem, st>>>(maps, p);
   return check_launch(what);
 }

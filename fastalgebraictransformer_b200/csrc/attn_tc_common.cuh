@@ -66,19 +66,25 @@ __device__ __forceinline__ void load_tile_tma(unsigned char* dst, const CUtensor
 // ------------------------------------------------------------------ CTA work order of the causal kernels
 // Per (batch, head) there are n_tiles CTAs whose cost falls with their rank (rank 0 sees the most tiles of the other
 // side).  Blocks are dispatched in index order; with all ranks of one (batch, head) adjacent, the last (batch, head)
-// starts its longest CTA when almost nothing else is left and the GPU idles behind it (5-8 % of the launch at
-// B*H = 128, S = 4096).  The 1-D grid is therefore ordered in kBands bands of ranks: band 0 holds the longest
-// quarter of the ranks of every (batch, head), the last band the shortest.  Inside a band the ranks of one
-// (batch, head) stay adjacent so that CTAs running together still share its tiles in L2.
-constexpr int kBands = 4;
-__host__ __device__ inline int band_size(int n_tiles) { return (n_tiles + kBands - 1) / kBands; }
-inline unsigned banded_grid(int n_tiles, int n_bh) {
-  const int bs = band_size(n_tiles);
+// starts its longest CTA when almost nothing else is left and the GPU idles behind it.  The 1-D grid can therefore be
+// ordered in bands of ranks: band 0 holds the longest ranks of every (batch, head), the last band the shortest; inside
+// a band the ranks of one (batch, head) stay adjacent so that CTAs running together still share its tiles in L2.
+// More bands shorten the tail but spread each (batch, head) over more of the launch; measured at B*H = 128, S = 4096:
+// two bands are best for the forward (-2 %), four and more lose to L2 misses, and the backward kernels are best
+// with one band (all ranks of a (batch, head) adjacent, long ranks first).
+#ifndef FAT_FWD_BANDS
+#define FAT_FWD_BANDS 2
+#define FAT_BWD_BANDS 1
+#endif
+constexpr int kFwdBands = FAT_FWD_BANDS, kBwdBands = FAT_BWD_BANDS;
+__host__ __device__ inline int band_size(int n_tiles, int bands) { return (n_tiles + bands - 1) / bands; }
+inline unsigned banded_grid(int n_tiles, int n_bh, int bands) {
+  const int bs = band_size(n_tiles, bands);
   return unsigned((n_tiles + bs - 1) / bs) * unsigned(n_bh) * unsigned(bs);
 }
 // false: this block is padding (rank beyond n_tiles) and must return at once
-__device__ __forceinline__ bool banded_tile(int n_tiles, int n_bh, int& rank, int& bh) {
-  const unsigned bs = unsigned(band_size(n_tiles)), per_band = unsigned(n_bh) * bs;
+__device__ __forceinline__ bool banded_tile(int n_tiles, int n_bh, int bands, int& rank, int& bh) {
+  const unsigned bs = unsigned(band_size(n_tiles, bands)), per_band = unsigned(n_bh) * bs;
   const unsigned band = blockIdx.x / per_band, rem = blockIdx.x % per_band;
   bh = int(rem / bs);
   rank = int(band * bs + rem % bs);

@@ -113,7 +113,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n_qb = (p.T + 2 * BLK - 1) / (2 * BLK);
   int rank, bh;
-  if (!banded_tile(n_qb, p.B * p.H, rank, bh)) return;      // padding block of the banded order
+  if (!banded_tile(n_qb, p.B * p.H, kFwdBands, rank, bh)) return;      // padding block of the banded order
   const int b = bh / p.H, h = bh % p.H;
   const int qb = n_qb - 1 - rank;                            // long query blocks first
   const int n_kv_total = (p.T + BLK - 1) / BLK;
@@ -327,7 +327,7 @@ int launch_fwd(const AttnParams& p, cudaStream_t st) {
   const size_t smem = sizeof(FwdSmem<D>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) { set_error("attn_fwd_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return FAT_ERR_LAUNCH; }
-  const dim3 grid(banded_grid((p.T + 2 * BLK - 1) / (2 * BLK), p.B * p.H));
+  const dim3 grid(banded_grid((p.T + 2 * BLK - 1) / (2 * BLK), p.B * p.H, kFwdBands));
   kern<<<grid, kFwdThreads, smem, st>>>(maps, p);
   return check_launch("attn_fwd_tc");
 }
