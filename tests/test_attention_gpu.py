@@ -195,9 +195,9 @@ def test_deterministic_tensor_path(D):
 @pytest.mark.parametrize("T", [640, 1280, 1408])
 @pytest.mark.parametrize("D", [64, 128])
 def test_tile_counts_that_leave_padding_blocks(T, D):
-    """The causal kernels order their blocks in four bands of tile ranks; tile counts that are no multiple of the band
-    size (5, 10 and 11 key tiles; 3, 5 and 6 query blocks) leave padding blocks that must return without touching
-    anything, and every real tile must still be visited exactly once.  Tensor path against the CUDA-core path."""
+    """The causal kernels run on 1-D grids ordered in bands of tile ranks; tile counts that are no multiple of the band
+    size (here odd numbers of query blocks in the forward's two bands) leave padding blocks that must return without
+    touching anything, and every real tile must still be visited exactly once.  Tensor path against the CUDA-core path."""
     B, H = 1, 3
     q, k, v, go = gen_qkv(31 + T // 128, B, H, T, D, torch.bfloat16)
     slopes = oracle.compute_alibi_slopes(H)
