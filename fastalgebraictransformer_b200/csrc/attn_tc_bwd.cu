@@ -169,7 +169,6 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
   const int qt = (p.T + BLK - 1) / BLK - 1 - rank;           // long rows first
   const int n = qt + 1;                                      // key tiles 0..qt (causal)
   Guard g{&sm.abort_flag, p.status};
-  FAT_TRACE_DECL(blockIdx.x == 0);
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -218,37 +217,22 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
         if (j + 1 < n) {
           // S(j+1) as soon as phase A has read S(j); dP(j+1) into the other dP buffer (its previous tenant dS(j-1)
           // was consumed by dQ(j-1), issued before this point), so phase B of the next tile never waits for it
-          TR_BEGIN();
           if (!(ok = g.wait(&sm.s_free, j & 1, 53))) break;
-          TR_WAITED();
-          TR_STAMP(64 + 8 * (j - 10) + 0, j >= 10 && j < 13);
           if (!(ok = g.wait(&sm.k_full[ks1], kph1, 54))) break;
-          TR_WORKED();                                         // (trace builds: time spent waiting for K)
           tc_fence_after();
           issue_gemm_nt<D>(tS, qd, kd[ks1], idesc_s);
           mma_commit(&sm.s_full);
-          TR_BEGIN();
           if (!(ok = g.wait(&sm.v_full[vs1], vph1, 56))) break;
-          TR_WAITED2();                                        // (trace builds: time spent waiting for V)
           tc_fence_after();
-          TR_STAMP(64 + 8 * (j - 10) + 1, j >= 10 && j < 13);
           issue_gemm_nt<D>(tP0 + ((j + 1) & 1) * BLK, dod, vd[vs1], idesc_s);
           mma_commit(&sm.dp_full[(j + 1) & 1]);
-          TR_STAMP(64 + 8 * (j - 10) + 2, j >= 10 && j < 13);
           mma_commit(&sm.v_empty[vs1]);
         }
-        TR_BEGIN();
         if (!(ok = g.wait(&sm.ds_full[j & 1], (j >> 1) & 1, 55))) break;
-        TR_MARK();
-        TR_WORKED2();                                          // (trace builds: time spent waiting for dS)
-        TR_STAMP(64 + 8 * (j - 10) + 3, j >= 10 && j < 13);
         tc_fence_after();
         issue_gemm_tn<kColsPerGroup>(tQ, tP0 + (j & 1) * BLK, kd_mn[ks], idesc_dq, j > 0);       // dQ += dS K
         mma_commit(&sm.k_empty[ks]);
       }
-#ifdef FAT_TRACE
-      if (traced) { long long* o = trace + 32; o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
-#endif
       if (ok) mma_commit(&sm.dq_full);
     }
   } else {
@@ -266,10 +250,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
     for (int j = 0; j < n; ++j) {
       f32x2 gq[kColsPerGroup / 2];
       // ---- phase A: g = sigma^3 r^2 / (L+eps) from the scores
-      TR_BEGIN();
       if (!(ok = g.wait(&sm.s_full, j & 1, 60))) break;
-      TR_WAITED();
-      TR_STAMP(64 + 8 * (j - 10) + 4, tid == 0 && j >= 10 && j < 13);
       tc_fence_after();
       const float base = slope * float(j * BLK - row);       // bias of key column 0 of this tile
 #pragma unroll
@@ -291,12 +272,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       }
       tc_fence_before();
       mbar_arrive(&sm.s_free);
-      TR_WORKED();
-      TR_STAMP(64 + 8 * (j - 10) + 5, tid == 0 && j >= 10 && j < 13);
       // ---- phase B: dS = g (dP - Delta), packed over dP
       if (!(ok = g.wait(&sm.dp_full[j & 1], (j >> 1) & 1, 61))) break;
-      TR_WAITED2();
-      TR_STAMP(64 + 8 * (j - 10) + 6, tid == 0 && j >= 10 && j < 13);
       tc_fence_after();
       const bool diag = (j == qt);
       const uint32_t tP = tP0 + (j & 1) * BLK;
@@ -326,12 +303,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.ds_full[j & 1]);
-      TR_WORKED2();
-      TR_STAMP(64 + 8 * (j - 10) + 7, tid == 0 && j >= 10 && j < 13);
     }
-#ifdef FAT_TRACE
-    if (traced && (tid & 127) == 0 && tid < 256) { long long* o = trace + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
-#endif
     if (ok) ok = g.wait(&sm.dq_full, 0, 62);
     named_barrier(1, kEwThreads);
     if (!g.aborted()) {
@@ -390,7 +362,6 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
   const int n_q_total = (p.T + BLK - 1) / BLK;
   const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
   Guard g{&sm.abort_flag, p.status};
-  FAT_TRACE_DECL(blockIdx.x == 0);
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -479,10 +450,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       const bool diag = (it == 0);
       f32x2 gq[kColsPerGroup / 2];
       // ---- phase A: p = sigma^4 / (L+eps) -> packed P^T over S^T; g / (L+eps) kept in registers
-      TR_BEGIN();
       if (!(ok = g.wait(&sm.q_full[st], (it / kBwdStages) & 1, 93))) break;       // Delta / inv arrived with the Q tile
       if (!(ok = g.wait(&sm.s_full, it & 1, 90))) break;
-      TR_WAITED();
       tc_fence_after();
       const float base = slope * float(key - qi * BLK);      // bias of query column 0: -slope*(q-key)
       const float* iv = sm.inv[st];
@@ -524,10 +493,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full);
-      TR_WORKED();
       // ---- phase B: dS^T = g (dP^T - Delta[q]) -> packed over dP^T
       if (!(ok = g.wait(&sm.dp_full, it & 1, 91))) break;
-      TR_WAITED2();
       tc_fence_after();
       const float* dl = sm.delta[st];
 #pragma unroll
@@ -548,11 +515,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.ds_full);
-      TR_WORKED2();
     }
-#ifdef FAT_TRACE
-    if (traced && (tid & 127) == 0 && tid < 256) { long long* o = trace + 16 + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
-#endif
     if (ok) ok = g.wait(&sm.acc_full, 0, 92);
     named_barrier(1, kEwThreads);
     if (!g.aborted()) {
@@ -639,7 +602,6 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   const int n_q_total = (p.T + BLK - 1) / BLK;
   const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
   Guard g{&sm.abort_flag, p.status};
-  FAT_TRACE_DECL(blockIdx.x == 0);
   if ((smem_u32(smem_raw) & 1023u) != 0) {                   // the swizzled tiles need a 1024-byte aligned base
     if (tid == 0 && p.status) atomicOr(p.status, 0x40000000);
     return;                                                  // uniform: nobody has touched a barrier or TMEM yet
@@ -703,18 +665,15 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
           for (int i = 0; i < n && ok; ++i) {
             const int st = i & 1, st1 = st ^ 1;
             if (!(ok = g.wait(&sm.p_full, i & 1, 152))) break;
-            TR_STAMP(128 + 24 * (i - 10) + 0, i >= 10 && i < 13);
             if (!(ok = g.wait(&sm.do_full, i & 1, 153))) break;
             tc_fence_after();
             issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn, idesc_acc, i > 0);              // dV += P^T dO
             mma_commit(&sm.do_empty);                                                // X's share of releasing dO(i)
-            TR_STAMP(128 + 24 * (i - 10) + 1, i >= 10 && i < 13);
             if (i + 1 < n) {
               if (!(ok = g.wait(&sm.q_full[st1], ((i + 1) >> 1) & 1, 154))) break;
               tc_fence_after();
               issue_gemm_nt<D>(tS, kd, qd[st1], idesc_s);                                // S^T of the next query tile
               mma_commit(&sm.s_full);
-              TR_STAMP(128 + 24 * (i - 10) + 2, i >= 10 && i < 13);
             }
           }
         } else {
@@ -732,7 +691,6 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
           for (int i = 0; i < n && ok; ++i) {
             const int st = i & 1;
             if (!(ok = g.wait(&sm.ds_full, i & 1, 156))) break;                          // phase B done: dS^T in smem, dP^T read
-            TR_STAMP(128 + 24 * (i - 10) + 3, i >= 10 && i < 13);
             tc_fence_after();
             // dQ^T = K^T dS^T over the keys.  The MMA is always 128 rows tall: with D = 64 the second 64-row chunk of the
             // MN-major A operand is the tile that follows K in shared memory (V), so TMEM lanes 64..127 receive numbers
@@ -745,16 +703,13 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
             for (int s = 0; s < BLK / 16; ++s)                                           // dK += dS^T Q over the queries
               mma_ss(tK, dsd_k + ((((s / 4) * (BLK * 128) + (s % 4) * 32)) >> 4), qd_mn[st] + ((s * 2048) >> 4), idesc_acc, i > 0 || s > 0);
             mma_commit(&sm.q_empty[st]);
-            TR_STAMP(128 + 24 * (i - 10) + 4, i >= 10 && i < 13);
             if (i + 1 < n) {
               if (!(ok = g.wait(&sm.dq_free, i & 1, 157))) break;                        // dQ^T(i) has left TMEM
-              TR_STAMP(128 + 24 * (i - 10) + 5, i >= 10 && i < 13);
               if (!(ok = g.wait(&sm.do_full, (i + 1) & 1, 158))) break;
               tc_fence_after();
               issue_gemm_nt<D>(tP, vd, dod, idesc_s);                                    // dP^T of the next query tile
               mma_commit(&sm.dp_full);
               mma_commit(&sm.do_empty);                                             // Y's share of releasing dO(i+1)
-              TR_STAMP(128 + 24 * (i - 10) + 12, i >= 10 && i < 13);
             }
           }
         }
@@ -789,10 +744,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
     };
     for (int i = 0; i < n; ++i) {
       const int row0 = (kt + i) * BLK;
-      TR_BEGIN();
       if (!(ok = g.wait(&sm.dq_full, i & 1, 160))) break;
-      TR_WAITED();
-      TR_STAMP(128 + 24 * (i - 10) + 11, dl == 0 && i >= 10 && i < 13);
       tc_fence_after();
       uint32_t a[32], c[32];
       tmem_ld32(tmem_addr(tP, lane_base, 0), a);
@@ -814,7 +766,6 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
       tmem_wait_ld_regs(c);
       tc_fence_before();
       mbar_arrive(&sm.dq_free);                               // the next dP^T may be issued
-      TR_STAMP(128 + 24 * (i - 10) + 14, dl == 0 && i >= 10 && i < 13);
       fence_async_smem();
       named_barrier(3, 128);
       if (dl == 0) {
@@ -822,16 +773,10 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
         tma_store_commit();
         if (row0 + 32 < p.T) { tma_reduce_add_4d(&maps.dq_acc, stage1, 0, row0 + 32, h, b); }
         tma_store_commit();
-        TR_STAMP(128 + 24 * (i - 10) + 13, i >= 10 && i < 13);
       }
       flush(a, stage0, row0 + 64, true);                      // waits until only the stage1 group is still reading
-      TR_STAMP(128 + 24 * (i - 10) + 15, dl == 0 && i >= 10 && i < 13);
       flush(c, stage1, row0 + 96, true);
-      TR_WORKED();
     }
-#ifdef FAT_TRACE
-    if (traced && dl == 0) { long long* o = trace + 40; o[0] = tr_wait; o[1] = tr_work; o[2] = clock64() - tr_t0; o[3] = n; }
-#endif
     if (dl == 0) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ element-wise warpgroups
@@ -848,11 +793,8 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
       const bool diag = (i == 0);
       f32x2 gq[kColsPerGroup / 2];
       // ---- phase A: p = sigma^4 / (L+eps) -> packed P^T over S^T; g / (L+eps) kept in registers
-      TR_BEGIN();
       if (!(ok = g.wait(&sm.q_full[st], (i >> 1) & 1, 170))) break;        // Delta / inv arrived with the Q tile
       if (!(ok = g.wait(&sm.s_full, i & 1, 171))) break;
-      TR_WAITED();
-      TR_STAMP(128 + 24 * (i - 10) + 6, tid == 0 && i >= 10 && i < 13);
       tc_fence_after();
       const float base = slope * float(key - qi * BLK);      // bias of query column 0: -slope*(q-key)
       const float* iv = sm.inv[st];
@@ -895,14 +837,10 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full);
-      TR_WORKED();
-      TR_STAMP(128 + 24 * (i - 10) + 7, tid == 0 && i >= 10 && i < 13);
       // ---- phase B: dS^T = g (dP^T - Delta[q]) -> shared memory
       // dP^T(i) was committed by the issuer of dQ^T(i-1) and dK(i-1), after them: its barrier also says that those
       // have finished reading the dS^T tile
       if (!(ok = g.wait(&sm.dp_full, i & 1, 172))) break;
-      TR_STAMP(128 + 24 * (i - 10) + 8, tid == 0 && i >= 10 && i < 13);
-      TR_WAITED2();
       tc_fence_after();
       const float* dl = sm.delta[st];
 #pragma unroll
@@ -929,12 +867,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&sm.ds_full);
-      TR_WORKED2();
-      TR_STAMP(128 + 24 * (i - 10) + 10, tid == 0 && i >= 10 && i < 13);
     }
-#ifdef FAT_TRACE
-    if (traced && (tid & 127) == 0) { long long* o = trace + 16 + 8 * (tid >> 7); o[0] = tr_wait; o[1] = tr_work; o[2] = tr_wait2; o[3] = tr_work2; o[4] = clock64() - tr_t0; o[5] = n; }
-#endif
     if (ok) ok = g.wait(&sm.acc_full, 0, 174);
     named_barrier(1, kEwThreads);
     if (!g.aborted()) {

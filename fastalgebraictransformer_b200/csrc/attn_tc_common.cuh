@@ -119,33 +119,6 @@ __device__ __forceinline__ void issue_gemm_tn(uint32_t d_tmem, uint32_t a_tmem, 
   }
 }
 
-// ------------------------------------------------------------------ optional cycle tracing (-DFAT_TRACE builds only)
-// One chosen CTA accumulates the cycles its roles spend waiting and working and writes them to the buffer
-// registered with fat_debug_set_trace().  Compiled out of the shipped library.
-#ifdef FAT_TRACE
-#define FAT_TRACE_DECL(cond)                                                      \
-  long long* trace = reinterpret_cast<long long*>(p.dq_acc);                      \
-  const bool traced = trace && (cond);                                            \
-  long long tr_wait = 0, tr_work = 0, tr_wait2 = 0, tr_work2 = 0, tr_t0 = clock64(), tr_a = 0, tr_b = 0; \
-  (void)traced; (void)tr_wait; (void)tr_work; (void)tr_wait2; (void)tr_work2; (void)tr_t0; (void)tr_a; (void)tr_b
-#define TR_BEGIN() tr_a = clock64()
-#define TR_WAITED() tr_b = clock64(); tr_wait += tr_b - tr_a
-#define TR_WORKED() tr_a = clock64(); tr_work += tr_a - tr_b
-#define TR_WAITED2() tr_b = clock64(); tr_wait2 += tr_b - tr_a
-#define TR_WORKED2() tr_a = clock64(); tr_work2 += tr_a - tr_b
-#define TR_MARK() tr_b = tr_a
-#define TR_STAMP(idx, cond) do { if (traced && (cond)) trace[idx] = clock64() - tr_t0; } while (0)
-#else
-#define FAT_TRACE_DECL(cond)
-#define TR_BEGIN()
-#define TR_WAITED()
-#define TR_WORKED()
-#define TR_WAITED2()
-#define TR_WORKED2()
-#define TR_MARK()
-#define TR_STAMP(idx, cond)
-#endif
-
 // ------------------------------------------------------------------ packed fp32 pairs (sm_100 FFMA2 / FMUL2 / FADD2)
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 pk2(float lo, float hi) {

@@ -21,17 +21,6 @@ using namespace tc;
 using namespace tcattn;
 
 constexpr int kStages = 2;
-#ifdef FAT_TRACE
-#define FAT_TRACE_ARG , long long& tr_ld
-#define FAT_TRACE_PASS , tr_ld
-#define FAT_TRACE_T0() const long long tr_c0 = clock64()
-#define FAT_TRACE_T1() tr_ld += clock64() - tr_c0
-#else
-#define FAT_TRACE_ARG
-#define FAT_TRACE_PASS
-#define FAT_TRACE_T0()
-#define FAT_TRACE_T1()
-#endif
 #ifndef FAT_FWD_SPLIT
 #define FAT_FWD_SPLIT 1
 #endif
@@ -89,14 +78,12 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32
 // unrolled four times it no longer fits the instruction cache).
 template <typename T, bool MASK>
 __device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int r, f32x2 scale2, f32x2 half2, f32x2 step2,
-                                             float slope, float base, f32x2& l2 FAT_TRACE_ARG) {
+                                             float slope, float base, f32x2& l2) {
   uint32_t sreg[32];
   tmem_ld32(trow, sreg);
 #pragma unroll 1
   for (int c = 0; c < kChunks; ++c) {
-    FAT_TRACE_T0();
     tmem_wait_ld_regs(sreg);
-    FAT_TRACE_T1();
     uint32_t preg[16];
     softmax_chunk<T, MASK>(sreg, preg, c0 + c, r, scale2, half2, step2, slope, base, l2);
     if (c + 1 < kChunks) tmem_ld32(trow + (c + 1) * 32, sreg);      // next chunk in flight while this one is stored
@@ -123,7 +110,6 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
   for (int t = 0; t < 2; ++t) n_tiles[t] = (2 * qb + t) * BLK < p.T ? min(2 * qb + t + 1, n_kv_total) : 0;
   const int n_max = max(n_tiles[0], n_tiles[1]);
   Guard g{&sm.abort_flag, p.status};
-  FAT_TRACE_DECL(blockIdx.x == 0);
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -186,10 +172,8 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
         bool k_next_ready = false;
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_tiles[t]) continue;
-          TR_BEGIN();
           if (!(ok = g.wait(&sm.p_full[t], j & 1, 22))) break;
           if (!(ok = g.wait(&sm.v_full[st], ph, 23))) break;
-          TR_WAITED();
           tc_fence_after();
           issue_pv(t, st, j == 0);
           if (j + 1 < n_tiles[t]) {
@@ -204,9 +188,6 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
         mma_commit(&sm.v_empty[st]);                       // V(j) and, if it was read, K(j+1) are free once these finish
         if (j + 1 < n_max) mma_commit(&sm.k_empty[st1]);
       }
-#ifdef FAT_TRACE
-      if (traced) { trace[0] = tr_wait; trace[1] = clock64() - tr_t0; trace[2] = n_max; }
-#endif
     }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
@@ -221,33 +202,18 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     f32x2 l2 = pk2(0.f, 0.f);
     const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(2.f * slope, 2.f * slope);
     bool ok = true;
-#ifdef FAT_TRACE
-    long long tr_ld = 0, tr_st = 0;
-#endif
     for (int j = 0; j < n; ++j) {
-      TR_BEGIN();
       if (!(ok = g.wait(&sm.s_full[t], j & 1, 30))) break;
-      TR_WAITED();
       tc_fence_after();
       const float base = slope * float(j * BLK - row);       // bias of column 0 of this tile: -slope*(row-k0)
       const bool diag = (j == 2 * qb + t);
       const uint32_t trow = tmem_addr(tmem, lane_base, t * BLK + part * kColsPerWg);
-      if (diag) softmax_tile<T, true>(trow, part * kChunks, r, scale2, half2, step2, slope, base, l2 FAT_TRACE_PASS);
-      else      softmax_tile<T, false>(trow, part * kChunks, r, scale2, half2, step2, slope, base, l2 FAT_TRACE_PASS);
-#ifdef FAT_TRACE
-      const long long tr_s0 = clock64();
-#endif
+      if (diag) softmax_tile<T, true>(trow, part * kChunks, r, scale2, half2, step2, slope, base, l2);
+      else      softmax_tile<T, false>(trow, part * kChunks, r, scale2, half2, step2, slope, base, l2);
       tmem_wait_st();
-#ifdef FAT_TRACE
-      tr_st += clock64() - tr_s0;
-#endif
       tc_fence_before();
       mbar_arrive(&sm.p_full[t]);
-      TR_WORKED();
     }
-#ifdef FAT_TRACE
-    if (traced && r == 0 && part == 0) { trace[12 + 2 * t] = tr_ld; trace[13 + 2 * t] = tr_st; trace[4 + 4 * t] = tr_wait; trace[5 + 4 * t] = tr_work; trace[6 + 4 * t] = clock64() - tr_t0; trace[7 + 4 * t] = n; }
-#endif
     float l_sum;
     {
       float la, lb;

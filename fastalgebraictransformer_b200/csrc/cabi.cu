@@ -62,10 +62,6 @@ int resolve_path(const char* what, int path, int T, int D, int dtype, bool align
 
 using namespace fat;
 
-#ifdef FAT_TRACE
-static void* g_trace = nullptr;
-extern "C" __attribute__((visibility("default"))) void fat_debug_set_trace(void* p) { g_trace = p; }
-#endif
 
 extern "C" {
 
@@ -109,9 +105,6 @@ int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slope
   p.B = B; p.H = H; p.T = T; p.D = D;
   copy3(p.qs, qs); copy3(p.ks, ks); copy3(p.vs, vs); copy3(p.os, os);
   p.scale = float(scale); p.eps = float(eps); p.causal = causal != 0; p.status = status;
-#ifdef FAT_TRACE
-  p.dq_acc = static_cast<float*>(g_trace);
-#endif
   return sel == FAT_PATH_TENSOR ? attn_fwd_tc(p, dtype, (cudaStream_t)stream) : attn_fwd_simt(p, dtype, (cudaStream_t)stream);
 }
 
@@ -155,9 +148,6 @@ int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, c
   copy3(p.dqs, dqs); copy3(p.dks, dks); copy3(p.dvs, dvs);
   p.scale = float(scale); p.eps = float(eps); p.causal = causal != 0; p.status = status;
   p.deterministic = path == FAT_PATH_TENSOR_DETERMINISTIC;
-#ifdef FAT_TRACE
-  p.dq_acc = static_cast<float*>(g_trace);
-#endif
   return sel == FAT_PATH_TENSOR ? attn_bwd_tc(p, dtype, (cudaStream_t)stream) : attn_bwd_simt(p, dtype, (cudaStream_t)stream);
 }
 
