@@ -112,8 +112,13 @@ def check_device_status(device=None) -> None:
                 raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x}: the fused attention backward found its "
                                    "dynamic shared memory not 1024-byte aligned and did nothing; request path 3 "
                                    "(PATH_TENSOR_DETERMINISTIC) on this platform")
+            if v & 0x20000000:
+                raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x}: the tensor-core attention backward met "
+                                   "|q| or |k| >= 65536 in a bfloat16 tensor; it forms d_q and d_k from float16 copies of q and k, "
+                                   "which were clamped to 65504, so those gradients are wrong for this call; request path 1 "
+                                   "(PATH_SIMT) for tensors of that magnitude")
             raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x} "
-                               f"(code {v >> 24}: a bounded wait inside a kernel ran out, detail {v & 0xffffff})")
+                               f"(code {(v >> 24) & 0x1f}: a bounded wait inside a kernel ran out, detail {v & 0xffffff})")
 
 
 class device_guard:

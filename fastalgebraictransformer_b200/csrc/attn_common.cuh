@@ -30,6 +30,6 @@ int attn_bwd_simt(const AttnParams& p, int dtype, cudaStream_t st);
 bool   attn_tc_eligible(int T, int D, int dtype, bool aligned, bool causal, bool backward);
 int    attn_fwd_tc(const AttnParams& p, int dtype, cudaStream_t st);
 int    attn_bwd_tc(const AttnParams& p, int dtype, cudaStream_t st);
-size_t attn_bwd_tc_workspace_bytes(int B, int H, int T, int D);
+size_t attn_bwd_tc_workspace_bytes(int B, int H, int T, int D, int dtype);
 
 }  // namespace fat

@@ -3,7 +3,8 @@
 // Default: prepare (1), which also clears a float32 d_q accumulator, the fused key-major
 // kernel (4) that produces d_k, d_v and adds its d_q contributions with TMA reduce-add, and a convert pass.
 // Deterministic variant: three launches, no atomics, bit-reproducible:
-//   1. prepare:  per query row  inv = 1/(L+eps) and Delta = dO . O  (two padded float32 arrays)
+//   1. prepare:  per query row  inv = 1/(L+eps) and Delta = dO . O  (two padded float32 arrays), max|dO| per
+//                (batch, head), and for bfloat16 tensors float16 copies of q and k
 //   2. d_q kernel, query-major (one 128-query tile per CTA, key tiles streamed):
 //                S = Q K^T, dP = dO V^T -> dS = g inv (dP - Delta) (16-bit, packed into TMEM over dP)
 //                -> dQ += dS K                      with F = sigma^4, g = 2 sigma^3 r^2
@@ -22,12 +23,53 @@ namespace {
 using namespace tc;
 using namespace tcattn;
 
-// The element-wise results that feed the tensor core from TMEM (P^T, dS, dS^T) carry the tensor
-// dtype: tcgen05.mma kind::f16 wants both operands in one format (an f16 A with a bf16 B is an
-// illegal instruction on this hardware).  Power-of-two pre-scales keep small values out of the
-// fp16 subnormals; they are undone exactly in the epilogue multipliers.
-constexpr float kOpScale = 256.0f;       // applied to p (<= 1) and dS (|dS| stays far below 65504/256); the prepare
-                                         // kernel folds it into the per-row normaliser it writes
+// Operand formats.  tcgen05.mma kind::f16 takes both operands of one MMA in ONE 16-bit format (an f16 A
+// with a bf16 B is an illegal instruction).  P^T carries the tensor dtype (it multiplies dO).  dS / dS^T
+// is always float16: rounded to bfloat16 (8 significand bits) it leaves a few elements in 10^4 of d_q and
+// d_k outside the element-wise bar rel 2e-2 / abs 1e-2, with float16's 11 bits none.  Its partners in the
+// d_q and d_k contractions (K and Q) therefore have to be float16 as well: for bfloat16 tensors the prepare
+// pass writes float16 copies of q and k into the workspace (exact for magnitudes in [2^-14, 65504]; smaller
+// ones round to multiples of 2^-24; magnitudes of 65536 and more are clamped to 65504 and reported in bit 29
+// of the status word - the CUDA-core path takes such tensors), and the main kernels load those instead, so
+// S = Q K^T is formed from the copies too.  V and dO are used as they are.
+//
+// Ranges.  dS is proportional to dO, whose magnitude is the caller's (loss scaling, tiny late-training
+// gradients), so the prepare pass also finds max|dO| per (batch, head) and the kernels store
+//     dS_stored = 4 (the "g8" units) * kDsScale * c * dS,   c = 2^-e with  max|dO| c  in [0.5, 1),
+// undone exactly in the epilogue multipliers.  With |dS| <= 4 p |dO_i| |V_j - O_i| the stored value stays below
+// 65504 unless |V_j - O_i| exceeds ~90/sqrt(D) times what it is for unit-normal V; the conversion saturates.
+// P^T is stored as 16 sigma^4 (the "F16" units) times kOpScale/(L+eps): p <= 1, and the power of two keeps small p
+// out of the float16 subnormals.
+constexpr float kOpScale = 256.0f;
+constexpr float kDsScale = 4.0f;         // fused and key-major kernels: dS_stored = 4 kDsScale c dS
+constexpr float kDsScaleQ = 64.0f;       // query-major d_q kernel: dS_stored = 4 kDsScaleQ c (L+eps) dS (1/(L+eps) is applied to the rows of d_q afterwards)
+constexpr int kStatusF16Range = 0x20000000;
+
+// c and 1/c from the bits of max|dO| (a float32 with the sign cleared)
+__device__ __forceinline__ void dout_scale(uint32_t max_bits, float& c, float& rc) {
+  const uint32_t E = min(max((max_bits >> 23) & 0xffu, 32u), 222u);    // zero / denormal / inf / NaN: any finite power of two
+  c = __uint_as_float((253u - E) << 23);
+  rc = __uint_as_float((E + 1u) << 23);
+}
+
+// two float32 -> packed float16, round to nearest even, overflow clamped to +-65504
+__device__ __forceinline__ uint32_t pack_ds(float lo, float hi) {
+  uint32_t y;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(hi), "f"(lo));
+  return y;
+}
+
+// 8 bfloat16 -> 8 float16; `flag` collects whether a magnitude was 65536 or more (or not a number)
+__device__ __forceinline__ uint4 bf16x8_to_f16x8(uint4 v, uint32_t& flag) {
+  uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t x = w[i];
+    flag |= ((x & 0x7fff7fffu) + 0x38803880u) & 0x80008000u;            // either half >= 0x4780 (65536.0)
+    w[i] = pack_ds(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
+  }
+  return v;
+}
 
 constexpr int kEwGroups = 2;                          // element-wise warpgroups per CTA
 constexpr int kEwThreads = 128 * kEwGroups;
@@ -39,6 +81,10 @@ constexpr int kBwdStages = 2;
 constexpr int kDqKStages = 3;
 
 __host__ __device__ inline int64_t pad_rows(int T) { return int64_t((T + BLK - 1) / BLK) * BLK; }
+// Head of the workspace: Delta [B,H,Tp], kOpScale/(L+eps) [B,H,Tp] (Tp = T rounded up to whole tiles), bits of max|dO| [B,H].
+__host__ __device__ inline uint32_t* dmax_of(const AttnParams& p) {
+  return reinterpret_cast<uint32_t*>(p.delta + 2 * int64_t(p.B) * p.H * pad_rows(p.T));
+}
 
 // ------------------------------------------------------------------------------------- 1. prepare
 // One block = kPrepRows consecutive (padded) rows of one (batch, head): the only divisions are one 32-bit pair per
@@ -46,7 +92,13 @@ __host__ __device__ inline int64_t pad_rows(int T) { return int64_t((T + BLK - 1
 constexpr int kPrepRows = 64;
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
-attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out, float* __restrict__ dq_zero) {
+attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out, uint32_t* __restrict__ dmax,
+                        float* __restrict__ dq_zero, __half* __restrict__ q16, __half* __restrict__ k16) {
+  __shared__ uint32_t block_max;
+  if (threadIdx.x == 0) block_max = 0;
+  __syncthreads();
+  float amax = 0.f;
+  uint32_t out_of_range = 0;
   constexpr int LPR = D / 8;                      // lanes per row, 16 bytes each
   constexpr int RPW = 32 / LPR;                   // rows per warp
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane / LPR, l = lane % LPR;
@@ -79,9 +131,16 @@ attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out, float* 
         for (int i = 0; i < 8; ++i) o[i] += lo[i];
       }
     }
+    if (q16 && live) {                            // float16 copies of this row of q and k (dense [B,H,T,D])
+      const uint4 qv = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1] + int64_t(t) * p.qs[2] + l * 8));
+      const uint4 kv = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.k) + b * p.ks[0] + h * p.ks[1] + int64_t(t) * p.ks[2] + l * 8));
+      const int64_t at = (int64_t(bh) * p.T + t) * D + l * 8;
+      *reinterpret_cast<uint4*>(q16 + at) = bf16x8_to_f16x8(qv, out_of_range);
+      *reinterpret_cast<uint4*>(k16 + at) = bf16x8_to_f16x8(kv, out_of_range);
+    }
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dot = fmaf(g[i], o[i], dot);
+    for (int i = 0; i < 8; ++i) { dot = fmaf(g[i], o[i], dot); amax = fmaxf(amax, fabsf(g[i])); }
 #pragma unroll
     for (int m = LPR / 2; m > 0; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
     if (l == 0) {                                 // rows in the padding get 0
@@ -89,6 +148,14 @@ attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out, float* 
       inv_row[t] = live ? kOpScale / (Lrow[t] + p.eps) : 0.f;
     }
   }
+  // max |dO| of this (batch, head): magnitudes compare like their bit patterns
+  uint32_t mb = __float_as_uint(amax);
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, m));
+  if (lane == 0) atomicMax(&block_max, mb);
+  __syncthreads();
+  if (threadIdx.x == 0) atomicMax(dmax + bh, block_max);
+  if (out_of_range && p.status) atomicOr(p.status, kStatusF16Range);
 }
 
 // ------------------------------------------------------------------------------------- element-wise math
@@ -185,6 +252,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const uint32_t tS = tmem, tP0 = tmem + BLK, tQ = tmem + 3 * BLK;            // dP(j) lives at tP0 + (j & 1) * BLK
+  float dscale, dscale_inv;                                  // c and 1/c of this (batch, head), see the top of the file
+  dout_scale(dmax_of(p)[bh], dscale, dscale_inv);
 
   if (warp == kTmaWarp) {
     if (elect_one()) {
@@ -201,8 +270,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
     }
   } else if (warp == kMmaWarp) {
     if (elect_one()) {
-      constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
-      constexpr uint32_t idesc_dq = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
+      constexpr int H16 = Pack16<__half>::kFmt;
+      constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, H16, 0, 0);                  // S = Q K^T, float16 (q and k tiles are float16)
+      constexpr uint32_t idesc_dp = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);     // dP = dO V^T, tensor dtype
+      constexpr uint32_t idesc_dq = idesc_f16(BLK, D, H16, 0, 1);                   // dQ += dS K, float16
       const uint64_t qd = desc_kmajor(sm.q), dod = desc_kmajor(sm.dout);
       const uint64_t kd[kDqKStages] = {desc_kmajor(sm.k[0]), desc_kmajor(sm.k[1]), desc_kmajor(sm.k[2])};
       const uint64_t kd_mn[kDqKStages] = {desc_mnmajor(sm.k[0]), desc_mnmajor(sm.k[1]), desc_mnmajor(sm.k[2])};
@@ -210,7 +281,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       bool ok = g.wait(&sm.qdo_full, 0, 50) && g.wait(&sm.k_full[0], 0, 51);
       if (ok) { tc_fence_after(); issue_gemm_nt<D>(tS, qd, kd[0], idesc_s); mma_commit(&sm.s_full); }
       ok = ok && g.wait(&sm.v_full[0], 0, 52);
-      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tP0, dod, vd[0], idesc_s); mma_commit(&sm.dp_full[0]); mma_commit(&sm.v_empty[0]); }
+      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tP0, dod, vd[0], idesc_dp); mma_commit(&sm.dp_full[0]); mma_commit(&sm.v_empty[0]); }
       for (int j = 0; j < n && ok; ++j) {
         const int ks = j % kDqKStages, ks1 = (j + 1) % kDqKStages, vs1 = (j + 1) % kBwdStages;
         const uint32_t kph1 = ((j + 1) / kDqKStages) & 1, vph1 = ((j + 1) / kBwdStages) & 1;
@@ -224,7 +295,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
           mma_commit(&sm.s_full);
           if (!(ok = g.wait(&sm.v_full[vs1], vph1, 56))) break;
           tc_fence_after();
-          issue_gemm_nt<D>(tP0 + ((j + 1) & 1) * BLK, dod, vd[vs1], idesc_s);
+          issue_gemm_nt<D>(tP0 + ((j + 1) & 1) * BLK, dod, vd[vs1], idesc_dp);
           mma_commit(&sm.dp_full[(j + 1) & 1]);
           mma_commit(&sm.v_empty[vs1]);
         }
@@ -245,7 +316,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
     const float dlt = p.delta[srow];                                               // Delta of this query
     const float ginv = p.delta[int64_t(p.B) * p.H * pad_rows(p.T) + srow] ;              // kOpScale/(L+eps)
     const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(2.f * slope, 2.f * slope);
-    const f32x2 ndlt2 = pk2(-dlt, -dlt);
+    const float cs = kDsScaleQ * dscale;                     // dS_stored = g8 cs (dP - Delta)
+    const f32x2 cs2 = pk2(cs, cs), ndlt2 = pk2(-dlt * cs, -dlt * cs);
     bool ok = true;
     for (int j = 0; j < n; ++j) {
       f32x2 gq[kColsPerGroup / 2];
@@ -287,14 +359,14 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
           tmem_wait_ld_regs(dreg);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const f32x2 ds2 = mul2(gq[16 * c + i], add2(pk2(__uint_as_float(dreg[2 * i]), __uint_as_float(dreg[2 * i + 1])), ndlt2));
+            const f32x2 ds2 = mul2(gq[16 * c + i], fma2(pk2(__uint_as_float(dreg[2 * i]), __uint_as_float(dreg[2 * i + 1])), cs2, ndlt2));
             float d0, d1;
             upk2(ds2, d0, d1);
             if constexpr (decltype(DIAG)::value) {
               if (kColsPerGroup * w + 32 * c + 2 * i > r) d0 = 0.f;
               if (kColsPerGroup * w + 32 * c + 2 * i + 1 > r) d1 = 0.f;
             }
-            preg[i] = Pack16<T>::pack(d0, d1);
+            preg[i] = pack_ds(d0, d1);
           }
           tmem_st16(tmem_addr(tP, lane_base, packed_col(w, c)), preg);
         }
@@ -308,7 +380,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
     named_barrier(1, kEwThreads);
     if (!g.aborted()) {
       tc_fence_after();
-      const float mul = 0.25f * scale * ginv / kOpScale;        // 2 (derivative) / 8 (g8 units) * scale / (L+eps)
+      const float mul = 0.25f * scale * (ginv / kOpScale) * dscale_inv / kDsScaleQ;   // 2 (derivative) / 8 (g8 units) * scale / (L+eps), operand scale undone
       for (int col0 = 32 * w; col0 < D; col0 += 32 * kEwGroups) {   // warpgroups interleave 32-column chunks of d_q
         uint32_t oreg[32];
         tmem_ld32(tmem_addr(tQ, lane_base, col0), oreg);
@@ -378,6 +450,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const uint32_t tS = tmem, tP = tmem + BLK, tV = tmem + 2 * BLK, tK = tmem + 2 * BLK + D;
+  float dscale, dscale_inv;                                  // c and 1/c of this (batch, head), see the top of the file
+  dout_scale(dmax_of(p)[bh], dscale, dscale_inv);
 
   if (warp == kTmaWarp) {
     if (elect_one()) {
@@ -400,8 +474,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
     }
   } else if (warp == kMmaWarp) {
     if (elect_one()) {
-      constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
-      constexpr uint32_t idesc_acc = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
+      constexpr int F = Pack16<T>::kFmt, H16 = Pack16<__half>::kFmt;
+      constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, H16, 0, 0);       // S^T = K Q^T, float16 (q and k tiles are float16)
+      constexpr uint32_t idesc_dp = idesc_f16(BLK, BLK, F, 0, 0);        // dP^T = V dO^T, tensor dtype
+      constexpr uint32_t idesc_dv = idesc_f16(BLK, D, F, 0, 1);          // dV += P^T dO, tensor dtype
+      constexpr uint32_t idesc_dk = idesc_f16(BLK, D, H16, 0, 1);        // dK += dS^T Q, float16
       const uint64_t kd = desc_kmajor(sm.k), vd = desc_kmajor(sm.v);
       const uint64_t qd[kBwdStages] = {desc_kmajor(sm.q[0]), desc_kmajor(sm.q[1])};
       const uint64_t qd_mn[kBwdStages] = {desc_mnmajor(sm.q[0]), desc_mnmajor(sm.q[1])};
@@ -410,13 +487,13 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       bool ok = g.wait(&sm.kv_full, 0, 80) && g.wait(&sm.q_full[0], 0, 81);
       if (ok) { tc_fence_after(); issue_gemm_nt<D>(tS, kd, qd[0], idesc_s); mma_commit(&sm.s_full); }
       ok = ok && g.wait(&sm.do_full[0], 0, 82);
-      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tP, vd, dod[0], idesc_s); mma_commit(&sm.dp_full); }
+      if (ok) { tc_fence_after(); issue_gemm_nt<D>(tP, vd, dod[0], idesc_dp); mma_commit(&sm.dp_full); }
       for (int it = 0; it < n && ok; ++it) {
         const int st = it % kBwdStages, st1 = (it + 1) % kBwdStages;
         const uint32_t ph1 = ((it + 1) / kBwdStages) & 1;
         if (!(ok = g.wait(&sm.p_full, it & 1, 83))) break;
         tc_fence_after();
-        issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn[st], idesc_acc, it > 0);     // dV += P^T dO
+        issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn[st], idesc_dv, it > 0);      // dV += P^T dO
         mma_commit(&sm.do_empty[st]);
         if (it + 1 < n) {
           if (!(ok = g.wait(&sm.q_full[st1], ph1, 84))) break;
@@ -426,12 +503,12 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
         }
         if (!(ok = g.wait(&sm.ds_full, it & 1, 85))) break;
         tc_fence_after();
-        issue_gemm_tn<kColsPerGroup>(tK, tP, qd_mn[st], idesc_acc, it > 0);      // dK += dS^T Q
+        issue_gemm_tn<kColsPerGroup>(tK, tP, qd_mn[st], idesc_dk, it > 0);       // dK += dS^T Q
         mma_commit(&sm.q_empty[st]);
         if (it + 1 < n) {
           if (!(ok = g.wait(&sm.do_full[st1], ph1, 86))) break;
           tc_fence_after();
-          issue_gemm_nt<D>(tP, vd, dod[st1], idesc_s);       // dP^T of the next query tile
+          issue_gemm_nt<D>(tP, vd, dod[st1], idesc_dp);      // dP^T of the next query tile
           mma_commit(&sm.dp_full);
         }
       }
@@ -444,6 +521,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
     const float slope = p.slopes[h], scale = p.scale;
     const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(-2.f * slope, -2.f * slope);
+    const float cs = kDsScale * dscale / kOpScale;           // dS_stored = g8 (kOpScale/(L+eps)) cs (dP - Delta)
+    const f32x2 cs2 = pk2(cs, cs);
     bool ok = true;
     for (int it = 0; it < n; ++it) {
       const int st = it % kBwdStages, qi = kt + it;
@@ -505,10 +584,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const float2 d2 = *reinterpret_cast<const float2*>(dl + kColsPerGroup * w + 32 * c + 2 * i);
-          const f32x2 ds2 = mul2(gq[16 * c + i], add2(pk2(__uint_as_float(dreg[2 * i]), __uint_as_float(dreg[2 * i + 1])), pk2(-d2.x, -d2.y)));
+          const f32x2 ds2 = mul2(gq[16 * c + i], fma2(pk2(__uint_as_float(dreg[2 * i]), __uint_as_float(dreg[2 * i + 1])), cs2, pk2(-cs * d2.x, -cs * d2.y)));
           float d0, d1;
           upk2(ds2, d0, d1);
-          preg[i] = Pack16<T>::pack(d0, d1);
+          preg[i] = pack_ds(d0, d1);
         }
         tmem_st16(tmem_addr(tP, lane_base, packed_col(w, c)), preg);
       }
@@ -528,7 +607,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
         uint32_t oreg[32];
         tmem_ld32(tmem_addr(is_dk ? tK : tV, lane_base, col0), oreg);
         tmem_wait_ld_regs(oreg);
-        stage_row32<T>(sm.q[is_dk ? 1 : 0], r, col0, oreg, is_dk ? 0.25f * scale / kOpScale : 0.0625f / kOpScale);
+        stage_row32<T>(sm.q[is_dk ? 1 : 0], r, col0, oreg, is_dk ? 0.25f * scale * dscale_inv / kDsScale : 0.0625f / kOpScale);
       }
       fence_async_smem();
       named_barrier(1, kEwThreads);
@@ -621,6 +700,8 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const uint32_t tS = tmem, tP = tmem + BLK, tV = tmem + 2 * BLK, tK = tV + D;
+  float dscale, dscale_inv;                                  // c and 1/c of this (batch, head), see the top of the file
+  dout_scale(dmax_of(p)[bh], dscale, dscale_inv);
 
   if (warp >= kFusedTmaWarp) {
     reg_share_dec<kFusedRegsAux>();                             // warps 12..15 (15 only takes part in this)
@@ -647,10 +728,12 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
     } else if (warp == kFusedMmaWarpX || warp == kFusedMmaWarpY) {
       // ---------------------------------------------------------------- tensor-core issuers
       if (elect_one()) {
-        constexpr int F = Pack16<T>::kFmt;
-        constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, F, 0, 0);          // S^T, dP^T: both operands K-major
-        constexpr uint32_t idesc_acc = idesc_f16(BLK, D, F, 0, 1);          // dV, dK: B (dO / Q) MN-major
-        constexpr uint32_t idesc_dq = idesc_f16(BLK, BLK, F, 1, 1);         // dQ^T: A = K (MN-major), B = dS^T (MN-major)
+        constexpr int F = Pack16<T>::kFmt, H16 = Pack16<__half>::kFmt;
+        constexpr uint32_t idesc_s = idesc_f16(BLK, BLK, H16, 0, 0);        // S^T = K Q^T: both operands K-major, float16 (q and k tiles are float16)
+        constexpr uint32_t idesc_dp = idesc_f16(BLK, BLK, F, 0, 0);         // dP^T = V dO^T: tensor dtype
+        constexpr uint32_t idesc_dv = idesc_f16(BLK, D, F, 0, 1);           // dV += P^T dO: B (dO) MN-major, tensor dtype
+        constexpr uint32_t idesc_dk = idesc_f16(BLK, D, H16, 0, 1);         // dK += dS^T Q: B (Q) MN-major, float16
+        constexpr uint32_t idesc_dq = idesc_f16(BLK, BLK, H16, 1, 1);       // dQ^T: A = K (MN-major), B = dS^T (MN-major), float16
         bool ok = g.wait(&sm.kv_full, 0, 150);
         if (warp == kFusedMmaWarpX) {
           // ---- issuer X: dV as soon as P^T is written, then the next S^T into the same columns
@@ -667,7 +750,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
             if (!(ok = g.wait(&sm.p_full, i & 1, 152))) break;
             if (!(ok = g.wait(&sm.do_full, i & 1, 153))) break;
             tc_fence_after();
-            issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn, idesc_acc, i > 0);              // dV += P^T dO
+            issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn, idesc_dv, i > 0);               // dV += P^T dO
             mma_commit(&sm.do_empty);                                                // X's share of releasing dO(i)
             if (i + 1 < n) {
               if (!(ok = g.wait(&sm.q_full[st1], ((i + 1) >> 1) & 1, 154))) break;
@@ -684,7 +767,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
           const uint64_t dod = desc_kmajor(sm.dout);
           if (ok && (ok = g.wait(&sm.do_full, 0, 155))) {
             tc_fence_after();
-            issue_gemm_nt<D>(tP, vd, dod, idesc_s);
+            issue_gemm_nt<D>(tP, vd, dod, idesc_dp);
             mma_commit(&sm.dp_full);
             mma_commit(&sm.do_empty);
           }
@@ -701,13 +784,13 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
             mma_commit(&sm.dq_full);
 #pragma unroll
             for (int s = 0; s < BLK / 16; ++s)                                           // dK += dS^T Q over the queries
-              mma_ss(tK, dsd_k + ((((s / 4) * (BLK * 128) + (s % 4) * 32)) >> 4), qd_mn[st] + ((s * 2048) >> 4), idesc_acc, i > 0 || s > 0);
+              mma_ss(tK, dsd_k + ((((s / 4) * (BLK * 128) + (s % 4) * 32)) >> 4), qd_mn[st] + ((s * 2048) >> 4), idesc_dk, i > 0 || s > 0);
             mma_commit(&sm.q_empty[st]);
             if (i + 1 < n) {
               if (!(ok = g.wait(&sm.dq_free, i & 1, 157))) break;                        // dQ^T(i) has left TMEM
               if (!(ok = g.wait(&sm.do_full, (i + 1) & 1, 158))) break;
               tc_fence_after();
-              issue_gemm_nt<D>(tP, vd, dod, idesc_s);                                    // dP^T of the next query tile
+              issue_gemm_nt<D>(tP, vd, dod, idesc_dp);                                   // dP^T of the next query tile
               mma_commit(&sm.dp_full);
               mma_commit(&sm.do_empty);                                             // Y's share of releasing dO(i+1)
             }
@@ -787,6 +870,8 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
     const float slope = p.slopes[h], scale = p.scale;
     const f32x2 scale2 = pk2(scale, scale), one2 = pk2(1.0f, 1.0f), step2 = pk2(-2.f * slope, -2.f * slope);
+    const float cs = kDsScale * dscale / kOpScale;           // dS_stored = g8 (kOpScale/(L+eps)) cs (dP - Delta)
+    const f32x2 cs2 = pk2(cs, cs);
     bool ok = true;
     for (int i = 0; i < n; ++i) {
       const int st = i & 1, qi = kt + i;
@@ -854,10 +939,10 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
         for (int e = 0; e < 16; ++e) {
           if (e % 2 == 0) dq4 = *reinterpret_cast<const float4*>(dl + col0 + 2 * e);
           const float2 d2 = e % 2 == 0 ? make_float2(dq4.x, dq4.y) : make_float2(dq4.z, dq4.w);
-          const f32x2 ds2 = mul2(gq[16 * c + e], add2(pk2(__uint_as_float(dreg[2 * e]), __uint_as_float(dreg[2 * e + 1])), pk2(-d2.x, -d2.y)));
+          const f32x2 ds2 = mul2(gq[16 * c + e], fma2(pk2(__uint_as_float(dreg[2 * e]), __uint_as_float(dreg[2 * e + 1])), cs2, pk2(-cs * d2.x, -cs * d2.y)));
           float d0, d1;
           upk2(ds2, d0, d1);
-          preg[e] = Pack16<T>::pack(d0, d1);
+          preg[e] = pack_ds(d0, d1);
         }
 #pragma unroll
         for (int sgm = 0; sgm < 4; ++sgm)        // 64-query chunk w of the tile, 16-byte segments 4c..4c+3 of this key's row
@@ -879,7 +964,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
         uint32_t oreg[32];
         tmem_ld32(tmem_addr(is_dk ? tK : tV, lane_base, c0), oreg);
         tmem_wait_ld_regs(oreg);
-        stage_row32<T>(is_dk ? sm.dout : sm.q[0], r, c0, oreg, is_dk ? 0.25f * scale / kOpScale : 0.0625f / kOpScale);
+        stage_row32<T>(is_dk ? sm.dout : sm.q[0], r, c0, oreg, is_dk ? 0.25f * scale * dscale_inv / kDsScale : 0.0625f / kOpScale);
       }
       fence_async_smem();
       named_barrier(1, kEwThreads);
@@ -899,12 +984,12 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   if (warp == kFusedTmaWarp) tmem_dealloc(tmem, kTmemCols);
 }
 
-// d_q = round(dq_acc * mul): float32 accumulator (dense [B,H,T,D]) -> tensor dtype with the caller's strides.
+// d_q = round(dq_acc * scale / (4 kDsScale c)): float32 accumulator (dense [B,H,T,D]) -> tensor dtype with the caller's strides.
 // One block = kConvRows rows of one (batch, head); a thread converts 8 values of kConvRows / (256 / (D/8)) rows.
 constexpr int kConvRows = 64;
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
-attn_bwd_dq_convert_kernel(const AttnParams p, const float* __restrict__ dq_acc, float mul) {
+attn_bwd_dq_convert_kernel(const AttnParams p, const float* __restrict__ dq_acc) {
   constexpr int PPR = D / 8, RPP = 256 / PPR;     // packs per row, rows per pass of the block
   const unsigned chunks = unsigned((p.T + kConvRows - 1) / kConvRows);
   const int bh = int(blockIdx.x / chunks), t0 = int(blockIdx.x % chunks) * kConvRows;
@@ -912,6 +997,9 @@ attn_bwd_dq_convert_kernel(const AttnParams p, const float* __restrict__ dq_acc,
   const int c = int(threadIdx.x % PPR) * 8, tr = int(threadIdx.x / PPR);
   const float* src = dq_acc + int64_t(bh) * p.T * D + c;
   T* dst = static_cast<T*>(p.d_q) + b * p.dqs[0] + h * p.dqs[1] + c;
+  float dscale, dscale_inv;
+  dout_scale(dmax_of(p)[bh], dscale, dscale_inv);
+  const float mul = 0.25f * p.scale * dscale_inv / kDsScale;     // undoes the g8 units and the operand scale of dS
 #pragma unroll
   for (int i = 0; i < kConvRows / RPP; ++i) {
     const int t = t0 + tr + i * RPP;
@@ -924,15 +1012,43 @@ attn_bwd_dq_convert_kernel(const AttnParams p, const float* __restrict__ dq_acc,
   }
 }
 
-size_t stats_bytes(int B, int H, int T) { return (2 * size_t(B) * H * pad_rows(T) * sizeof(float) + 1023) / 1024 * 1024; }
+size_t round1k(size_t n) { return (n + 1023) / 1024 * 1024; }
+size_t stats_bytes(int B, int H, int T) { return round1k((2 * size_t(B) * H * pad_rows(T) + size_t(B) * H) * sizeof(float)); }
+size_t dq_acc_bytes(int B, int H, int T, int D) { return round1k(size_t(B) * H * T * D * sizeof(float)); }
+size_t f16_copy_bytes(int B, int H, int T, int D) { return round1k(size_t(B) * H * T * D * sizeof(__half)); }
+
+// Workspace after the head described at dmax_of(): the float32 d_q accumulator of the fused kernel, then (bfloat16
+// tensors only) the float16 copies of q and k, dense [B,H,T,D].
+float* ws_dq_acc(const AttnParams& p) {
+  return reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.delta) + stats_bytes(p.B, p.H, p.T));
+}
+__half* ws_q16(const AttnParams& p) {
+  return reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(ws_dq_acc(p)) + dq_acc_bytes(p.B, p.H, p.T, p.D));
+}
+__half* ws_k16(const AttnParams& p) {
+  return reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(ws_q16(p)) + f16_copy_bytes(p.B, p.H, p.T, p.D));
+}
 
 // dq_zero: the fused backward's float32 d_q accumulator, cleared by the same pass (nullptr: nothing to clear)
 template <typename T, int D>
 int launch_prepare(const AttnParams& p, cudaStream_t st, float* dq_zero = nullptr) {
   float* inv_rows = p.delta + int64_t(p.B) * p.H * pad_rows(p.T);
   const unsigned blocks = unsigned(p.B) * p.H * unsigned(pad_rows(p.T) / kPrepRows);
-  attn_bwd_prepare_kernel<T, D><<<blocks, 256, 0, st>>>(p, inv_rows, dq_zero);
+  if (cudaMemsetAsync(dmax_of(p), 0, size_t(p.B) * p.H * sizeof(uint32_t), st) != cudaSuccess) return check_launch("attn_bwd_prepare (clear)");
+  constexpr bool kCopies = !std::is_same<T, __half>::value;
+  attn_bwd_prepare_kernel<T, D><<<blocks, 256, 0, st>>>(p, inv_rows, dmax_of(p), dq_zero, kCopies ? ws_q16(p) : nullptr,
+                                                        kCopies ? ws_k16(p) : nullptr);
   return check_launch("attn_bwd_prepare");
+}
+
+// Tensor maps of the q and k operands of the main kernels: the float16 copies (dense) for bfloat16 tensors, the
+// tensors themselves for float16.
+template <typename T, int D>
+bool make_qk_maps(const AttnParams& p, CUtensorMap* mq, CUtensorMap* mk) {
+  if (std::is_same<T, __half>::value)
+    return make_tmap_bhtd(mq, p.q, p.B, p.H, p.T, D, p.qs, 64, BLK) && make_tmap_bhtd(mk, p.k, p.B, p.H, p.T, D, p.ks, 64, BLK);
+  const int64_t dense[3] = {int64_t(p.H) * p.T * D, int64_t(p.T) * D, D};
+  return make_tmap_bhtd(mq, ws_q16(p), p.B, p.H, p.T, D, dense, 64, BLK) && make_tmap_bhtd(mk, ws_k16(p), p.B, p.H, p.T, D, dense, 64, BLK);
 }
 
 template <typename Kern, typename Maps>
@@ -951,9 +1067,8 @@ template <typename T, int D>
 int launch_bwd_split(const AttnParams& p, cudaStream_t st) {
   DqMaps mq;
   DkvMaps mk;
-  if (!make_tmap_bhtd(&mq.q, p.q, p.B, p.H, p.T, D, p.qs, 64, BLK) ||
+  if (!make_qk_maps<T, D>(p, &mq.q, &mq.k) ||
       !make_tmap_bhtd(&mq.dout, p.d_out, p.B, p.H, p.T, D, p.dos, 64, BLK) ||
-      !make_tmap_bhtd(&mq.k, p.k, p.B, p.H, p.T, D, p.ks, 64, BLK) ||
       !make_tmap_bhtd(&mq.v, p.v, p.B, p.H, p.T, D, p.vs, 64, BLK) ||
       !make_tmap_bhtd(&mq.dq, p.d_q, p.B, p.H, p.T, D, p.dqs, 64, BLK) ||
       !make_tmap_bhtd(&mk.dk, p.d_k, p.B, p.H, p.T, D, p.dks, 64, BLK) ||
@@ -968,7 +1083,7 @@ int launch_bwd_split(const AttnParams& p, cudaStream_t st) {
 // Fused backward: prepare (which also clears the float32 d_q accumulator), fused kernel, convert d_q.
 template <typename T, int D>
 int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
-  float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.delta) + stats_bytes(p.B, p.H, p.T));
+  float* dq_acc = ws_dq_acc(p);
   auto kern = attn_bwd_fused_tc_kernel<T, D>;
   cudaFuncAttributes fa;
   if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
@@ -978,9 +1093,8 @@ int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
     return FAT_ERR_LAUNCH;
   }
   FusedMaps m;
-  if (!make_tmap_bhtd(&m.q, p.q, p.B, p.H, p.T, D, p.qs, 64, BLK) ||
+  if (!make_qk_maps<T, D>(p, &m.q, &m.k) ||
       !make_tmap_bhtd(&m.dout, p.d_out, p.B, p.H, p.T, D, p.dos, 64, BLK) ||
-      !make_tmap_bhtd(&m.k, p.k, p.B, p.H, p.T, D, p.ks, 64, BLK) ||
       !make_tmap_bhtd(&m.v, p.v, p.B, p.H, p.T, D, p.vs, 64, BLK) ||
       !make_tmap_bhtd(&m.dk, p.d_k, p.B, p.H, p.T, D, p.dks, 64, BLK) ||
       !make_tmap_bhtd(&m.dv, p.d_v, p.B, p.H, p.T, D, p.dvs, 64, BLK) ||
@@ -989,7 +1103,7 @@ int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
   if (int rc = launch_prepare<T, D>(p, st, dq_acc)) return rc;
   if (int rc = launch_main(kern, m, p, sizeof(FusedSmem<D>), kFusedThreads, st, "attn_bwd_fused_tc")) return rc;
   const unsigned blocks = unsigned(p.B) * p.H * unsigned((p.T + kConvRows - 1) / kConvRows);
-  attn_bwd_dq_convert_kernel<T, D><<<blocks, 256, 0, st>>>(p, dq_acc, 0.25f * p.scale / kOpScale);
+  attn_bwd_dq_convert_kernel<T, D><<<blocks, 256, 0, st>>>(p, dq_acc);
   return check_launch("attn_bwd_dq_convert");
 }
 
@@ -1001,9 +1115,10 @@ int launch_bwd(const AttnParams& p, cudaStream_t st) {
 
 }  // namespace
 
-size_t attn_bwd_tc_workspace_bytes(int B, int H, int T, int D) {
-  // Delta and 1/(L+eps) (rows padded to whole tiles), then the float32 d_q accumulator of the fused kernel
-  return stats_bytes(B, H, T) + size_t(B) * H * T * D * sizeof(float);
+size_t attn_bwd_tc_workspace_bytes(int B, int H, int T, int D, int dtype) {
+  // Delta, kOpScale/(L+eps) (rows padded to whole tiles) and max|dO|; the float32 d_q accumulator of the fused kernel;
+  // for bfloat16 tensors the float16 copies of q and k
+  return stats_bytes(B, H, T) + dq_acc_bytes(B, H, T, D) + (dtype == FAT_BF16 ? 2 * f16_copy_bytes(B, H, T, D) : 0);
 }
 
 int attn_bwd_tc(const AttnParams& p, int dtype, cudaStream_t st) {

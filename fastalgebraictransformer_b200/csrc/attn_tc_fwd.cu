@@ -11,7 +11,18 @@
 // and keep a running row sum.  The two query tiles ping-pong, so the tensor core works on
 // one while the other is in its element-wise phase.
 //
+// P is always float16 (stored as 4096 sigma^4 <= 4096).  Rounded to bfloat16 its error moves the output
+// by ~1e-3 |v| on rows that attend to a few keys: inside the output's own tolerance, but the backward
+// forms Delta = dO . O from this output, where the error is amplified by sqrt(D) |dO| and puts a few
+// elements in 10^4 of d_q outside the bar.  tcgen05.mma wants both operands of one MMA in one 16-bit
+// format, so for bfloat16 tensors two helper warps turn every V tile into float16 in shared memory
+// before O += P V reads it (exact for magnitudes in [2^-14, 65504], absolute error <= 2^-25 below;
+// 65536 and more are clamped to 65504 and reported in bit 29 of the status word).  S = Q K^T uses
+// q and k as they are.
+//
 // TMEM columns: S0/P0 [0,128)  S1/P1 [128,256)  O0 [256,256+D)  O1 [256+D,256+2D).
+#include <type_traits>
+
 #include "attn_tc_common.cuh"
 
 namespace fat {
@@ -25,8 +36,11 @@ constexpr int kStages = 2;
 #define FAT_FWD_SPLIT 1
 #endif
 constexpr int kSplit = FAT_FWD_SPLIT;                 // softmax warpgroups per query tile (each takes 128/kSplit score columns)
-constexpr int kEwWarps = 8 * kSplit;                  // softmax warps; then one TMA warp and one MMA warp
-constexpr int kFwdThreads = 32 * kEwWarps + 64;
+constexpr int kEwWarps = 8 * kSplit;                  // softmax warps; then one TMA warp, one MMA warp and two helper warps
+constexpr int kCvtWarps = 2;
+constexpr int kFwdThreads = 32 * kEwWarps + 64 + 32 * kCvtWarps;
+constexpr float kPUnit = 4096.0f;                     // P_stored = kPUnit sigma^4 = (4 (1 + s r))^4
+constexpr int kStatusF16Range = 0x20000000;
 constexpr int kColsPerWg = BLK / kSplit;
 constexpr int kChunks = kColsPerWg / 32;
 
@@ -37,6 +51,7 @@ struct FwdSmem {
   alignas(1024) unsigned char k[kStages][kTileBytes];
   alignas(1024) unsigned char v[kStages][kTileBytes];
   uint64_t q_full[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+  uint64_t v_ready[kStages];                              // helper warps: the V tile of this stage is float16 now
   uint64_t s_full[2], p_full[2], o_full[2];
   float l_part[2][kSplit][BLK];                           // row sums of each warpgroup's column share
   uint32_t tmem_base;
@@ -45,21 +60,26 @@ struct FwdSmem {
 
 struct FwdMaps { CUtensorMap q, k, v, out, out_lo; };
 
-// One 32-column chunk of a thread's score row: S (fp32, registers sreg) -> P = (2 sigma(S*scale + bias))^4 = 16 sigma^4
-// as packed 16-bit pairs in preg (the factor 16 cancels in O = P V / sum P); adds the chunk's row sum to l2.
-// `half2` holds the packed constant 1.  MASK: diagonal tile, keys with column index > r get no weight.
-template <typename T, bool MASK>
+// One 32-column chunk of a thread's score row: S (fp32, registers sreg) -> P = (8 sigma(S*scale + bias))^4 = 4096 sigma^4
+// as packed float16 pairs in preg (the factor cancels in O = P V / sum P); adds the chunk's row sum to l2.
+// With r' = 1/((|s|+1)/4) = 4 r (one fused multiply-add feeds the reciprocal, as the plain |s|+1 would) and
+// w' = 4 + s r' = 4 (1 + s r) = 8 sigma, the scaling costs no instruction.  `four2` holds the packed constant 4.
+// MASK: diagonal tile, keys with column index > r get no weight.
+template <bool MASK>
 __device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32_t (&preg)[16], int c, int r, f32x2 scale2,
-                                              f32x2 half2, f32x2 step2, float slope, float base, f32x2& l2) {
+                                              f32x2 four2, f32x2 step2, float slope, float base, f32x2& l2) {
   f32x2 bias2 = pk2(fmaf(slope, float(c * 32), base), fmaf(slope, float(c * 32 + 1), base));
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const f32x2 s2 = fma2(pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), scale2, bias2);
     bias2 = add2(bias2, step2);
-    f32x2 r2, w2;
-    if (rcp_shared(i, FAT_RCP_SHARE_FWD)) sigma_terms2<true>(s2, half2, r2, w2); else sigma_terms2<false>(s2, half2, r2, w2);
+    float s0, s1;
+    upk2(s2, s0, s1);
+    const float a0 = fmaf(fabsf(s0), 0.25f, 0.25f), a1 = fmaf(fabsf(s1), 0.25f, 0.25f);
+    const f32x2 r2 = rcp_shared(i, FAT_RCP_SHARE_FWD) ? rcp_pair<true>(a0, a1) : rcp_pair<false>(a0, a1);
+    const f32x2 w2 = fma2(s2, r2, four2);
     const f32x2 q2 = mul2(w2, w2);
-    f32x2 f2 = mul2(q2, q2);                               // (2 sigma)^4 = 16 sigma^4
+    f32x2 f2 = mul2(q2, q2);                               // (8 sigma)^4 = 4096 sigma^4
     float f0, f1;
     upk2(f2, f0, f1);
     if (MASK) {
@@ -68,7 +88,7 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32
       f2 = pk2(f0, f1);
     }
     l2 = add2(l2, f2);
-    preg[i] = Pack16<T>::pack(f0, f1);
+    preg[i] = Pack16<__half>::pack(f0, f1);
   }
 }
 
@@ -76,8 +96,8 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32
 // index c0).  The packed P of chunk c lands on columns [16 c, 16 c + 16) counted from `trow`, i.e. over scores
 // this thread has already taken into registers.  The chunk loop is kept rolled (the body is ~400 instructions;
 // unrolled four times it no longer fits the instruction cache).
-template <typename T, bool MASK>
-__device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int r, f32x2 scale2, f32x2 half2, f32x2 step2,
+template <bool MASK>
+__device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int r, f32x2 scale2, f32x2 four2, f32x2 step2,
                                              float slope, float base, f32x2& l2) {
   uint32_t sreg[32];
   tmem_ld32(trow, sreg);
@@ -85,7 +105,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int r, f32x2
   for (int c = 0; c < kChunks; ++c) {
     tmem_wait_ld_regs(sreg);
     uint32_t preg[16];
-    softmax_chunk<T, MASK>(sreg, preg, c0 + c, r, scale2, half2, step2, slope, base, l2);
+    softmax_chunk<MASK>(sreg, preg, c0 + c, r, scale2, four2, step2, slope, base, l2);
     if (c + 1 < kChunks) tmem_ld32(trow + (c + 1) * 32, sreg);      // next chunk in flight while this one is stored
     tmem_st16(trow + c * 16, preg);
   }
@@ -110,6 +130,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
   for (int t = 0; t < 2; ++t) n_tiles[t] = (2 * qb + t) * BLK < p.T ? min(2 * qb + t + 1, n_kv_total) : 0;
   const int n_max = max(n_tiles[0], n_tiles[1]);
   Guard g{&sm.abort_flag, p.status};
+  constexpr bool kConvertV = !std::is_same<T, __half>::value;
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -118,6 +139,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1);
+      mbar_init(&sm.v_ready[i], 32 * kCvtWarps);
     }
     mbar_fence_init();
   }
@@ -146,7 +168,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     // ------------------------------------------------------------------ tensor-core issuer
     if (elect_one()) {
       constexpr uint32_t idesc_qk = idesc_f16(BLK, BLK, Pack16<T>::kFmt, 0, 0);
-      constexpr uint32_t idesc_pv = idesc_f16(BLK, D, Pack16<T>::kFmt, 0, 1);
+      constexpr uint32_t idesc_pv = idesc_f16(BLK, D, Pack16<__half>::kFmt, 0, 1);      // P and V are float16
       const uint64_t qd[2] = {desc_kmajor(sm.q[0]), desc_kmajor(sm.q[1])};
       const uint64_t kd[kStages] = {desc_kmajor(sm.k[0]), desc_kmajor(sm.k[1])};
       const uint64_t vd[kStages] = {desc_mnmajor(sm.v[0]), desc_mnmajor(sm.v[1])};
@@ -173,7 +195,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_tiles[t]) continue;
           if (!(ok = g.wait(&sm.p_full[t], j & 1, 22))) break;
-          if (!(ok = g.wait(&sm.v_full[st], ph, 23))) break;
+          if (!(ok = g.wait(kConvertV ? &sm.v_ready[st] : &sm.v_full[st], ph, 23))) break;
           tc_fence_after();
           issue_pv(t, st, j == 0);
           if (j + 1 < n_tiles[t]) {
@@ -189,6 +211,39 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
         if (j + 1 < n_max) mma_commit(&sm.k_empty[st1]);
       }
     }
+  } else if (warp >= kEwWarps + 2) {
+    // ------------------------------------------------------------------ helper warps: V tiles bfloat16 -> float16 in place
+    // (every element keeps its place, so the swizzle does not matter).  Each V tile belongs to the CTA whose
+    // query block starts at it; that CTA checks its range.
+    if (kConvertV) {
+      const int part = warp - (kEwWarps + 2), lane = tid & 31;
+      constexpr int kPartBytes = S::kTileBytes / kCvtWarps;
+      uint32_t out_of_range = 0;
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j % kStages;
+        if (!g.wait(&sm.v_full[st], (j / kStages) & 1, 40)) break;
+        unsigned char* base = sm.v[st] + part * kPartBytes;
+        uint32_t flag = 0;
+#pragma unroll 4
+        for (int off = lane * 16; off < kPartBytes; off += 32 * 16) {
+          uint4 v = *reinterpret_cast<uint4*>(base + off);
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t x = w[i];
+            flag |= ((x & 0x7fff7fffu) + 0x38803880u) & 0x80008000u;          // either half >= 0x4780 (65536.0)
+            uint32_t y;
+            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(__uint_as_float(x & 0xffff0000u)), "f"(__uint_as_float(x << 16)));
+            w[i] = y;
+          }
+          *reinterpret_cast<uint4*>(base + off) = v;
+        }
+        if (j / 2 == qb) out_of_range |= flag;
+        fence_async_smem();
+        mbar_arrive(&sm.v_ready[st]);
+      }
+      if (out_of_range && p.status) atomicOr(p.status, kStatusF16Range);
+    }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
     const int t = (warp >> 2) / kSplit;                      // query tile of this warpgroup
@@ -200,7 +255,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     const float scale = p.scale;
     const int n = n_tiles[t];
     f32x2 l2 = pk2(0.f, 0.f);
-    const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(2.f * slope, 2.f * slope);
+    const f32x2 scale2 = pk2(scale, scale), four2 = pk2(4.0f, 4.0f), step2 = pk2(2.f * slope, 2.f * slope);
     bool ok = true;
     for (int j = 0; j < n; ++j) {
       if (!(ok = g.wait(&sm.s_full[t], j & 1, 30))) break;
@@ -208,8 +263,8 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       const float base = slope * float(j * BLK - row);       // bias of column 0 of this tile: -slope*(row-k0)
       const bool diag = (j == 2 * qb + t);
       const uint32_t trow = tmem_addr(tmem, lane_base, t * BLK + part * kColsPerWg);
-      if (diag) softmax_tile<T, true>(trow, part * kChunks, r, scale2, half2, step2, slope, base, l2);
-      else      softmax_tile<T, false>(trow, part * kChunks, r, scale2, half2, step2, slope, base, l2);
+      if (diag) softmax_tile<true>(trow, part * kChunks, r, scale2, four2, step2, slope, base, l2);
+      else      softmax_tile<false>(trow, part * kChunks, r, scale2, four2, step2, slope, base, l2);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full[t]);
@@ -218,7 +273,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     {
       float la, lb;
       upk2(l2, la, lb);
-      l_sum = (la + lb) * 0.0625f;                             // back to sum of sigma^4
+      l_sum = (la + lb) * (1.0f / kPUnit);                     // back to sum of sigma^4
     }
     if (kSplit > 1) sm.l_part[t][part][r] = l_sum;
     if (ok && n > 0) ok = g.wait(&sm.o_full[t], 0, 31);
@@ -231,7 +286,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     if (n > 0 && !g.aborted()) {
       // -------------------------------------------------------------- epilogue: O / (L + eps), hi + residual
       tc_fence_after();
-      const float inv = 0.0625f / (l_sum + p.eps);             // the accumulator holds 16 sigma^4 V
+      const float inv = (1.0f / kPUnit) / (l_sum + p.eps);     // the accumulator holds kPUnit sigma^4 V
       if (part == 0 && row < p.T) p.L[(int64_t(b) * p.H + h) * p.T + row] = l_sum;
       unsigned char* stage = sm.q[t];
       const bool want_lo = p.out_lo != nullptr;

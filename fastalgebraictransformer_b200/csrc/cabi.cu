@@ -112,7 +112,7 @@ size_t fat_attn_bwd_workspace_bytes(int B, int H, int T, int D, int dtype, int p
   if (B <= 0 || H <= 0 || T <= 0 || D <= 0) return 0;
   const size_t delta = size_t(B) * H * T * sizeof(float);
   const bool tc = path != FAT_PATH_SIMT && attn_tc_eligible(T, D, dtype, true, true, true);
-  return tc ? attn_bwd_tc_workspace_bytes(B, H, T, D) : delta;
+  return tc ? attn_bwd_tc_workspace_bytes(B, H, T, D, dtype) : delta;
 }
 
 int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* out_lo, const float* L,
@@ -133,7 +133,7 @@ int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, c
                        strides_aligned(dos, w) && strides_aligned(dqs, w) && strides_aligned(dks, w) && strides_aligned(dvs, w);
   const int sel = resolve_path("attn_bwd", path, T, D, dtype, aligned, causal != 0, true);
   if (sel < 0) return -sel;
-  const size_t need = sel == FAT_PATH_TENSOR ? attn_bwd_tc_workspace_bytes(B, H, T, D) : size_t(B) * H * T * sizeof(float);
+  const size_t need = sel == FAT_PATH_TENSOR ? attn_bwd_tc_workspace_bytes(B, H, T, D, dtype) : size_t(B) * H * T * sizeof(float);
   if (!workspace || workspace_bytes < need || !aligned16(workspace)) {
     set_error("attn_bwd: workspace of %zu bytes (16-byte aligned) required, got %zu at %p", need, workspace_bytes, workspace);
     return FAT_ERR_WORKSPACE;

@@ -54,11 +54,17 @@ enum fat_attn_path {
                                bit-reproducible gradients at the price of recomputing the scores twice */
 };
 
-/* Device-side status word written by kernels whose bounded waits ran out.  Bit layout:
- * 0 = never written; otherwise (code << 24) | detail.  The caller allocates one int32 per
- * device, zeroes it, passes it to the attention entry points and reads it back when it
- * wants to know (reading needs a synchronise, so it is left to the caller). */
-enum fat_device_status { FAT_DEV_OK = 0, FAT_DEV_WAIT_TIMEOUT = 1 };
+/* Device-side status word.  The caller allocates one int32 per device, zeroes it, passes it to the
+ * attention entry points and reads it back when it wants to know (reading needs a synchronise, so it
+ * is left to the caller).  0 = nothing to report.  Otherwise:
+ *   bits 24..28 = FAT_DEV_WAIT_TIMEOUT with a detail in bits 0..23: a bounded wait inside a kernel ran
+ *                 out and the kernel gave up (its outputs are undefined, the context stays usable);
+ *   bit 29      = the tensor-core backward found |q| or |k| >= 65536 in a bfloat16 tensor.  It forms
+ *                 d_q and d_k from float16 copies of q and k (see fat_attn_bwd), which were clamped to
+ *                 65504: those two gradients are wrong for this call; use FAT_PATH_SIMT for such data;
+ *   bit 30      = the fused backward found its shared memory misaligned and did nothing. */
+enum fat_device_status { FAT_DEV_OK = 0, FAT_DEV_WAIT_TIMEOUT = 1, FAT_DEV_F16_RANGE = 0x20000000,
+                         FAT_DEV_SMEM_ALIGN = 0x40000000 };
 
 FAT_API int fat_version(void);
 FAT_API const char* fat_error_string(int code);
@@ -214,7 +220,14 @@ FAT_API int fat_attn_fwd(const void* q, const void* k, const void* v, const floa
  *     dS_ij = 2 sigma^3 r^2 (dP_ij - Delta_i) / (L_i + eps),
  *     d_q = scale dS k,  d_k = scale dS^T q,  d_v = P^T d_out.
  * out_lo is the optional residual written by the forward (null: Delta uses the rounded out).
- * The workspace holds Delta (and, for the tensor-core path, a float32 d_q accumulator).
+ * The workspace holds Delta (and, for the tensor-core path, 1/(L+eps), max|d_out| per (batch, head)
+ * and a float32 d_q accumulator).
+ * Tensor-core path: dS enters the d_q and d_k contractions as float16 (bfloat16's 8 significand bits
+ * would leave a few elements in 10^4 outside rel 2e-2 / abs 1e-2), scaled by a power of two chosen
+ * from max|d_out| of the (batch, head), so gradients of any magnitude keep their precision.  For
+ * bfloat16 tensors q and k take part in those contractions as float16 copies made in shared memory:
+ * exact for magnitudes in [2^-14, 65504], absolute error <= 2^-25 below, clamped (and reported in the
+ * status word, bit 29) from 65536 on.
  * Replaces rational_attention_backward / rational_attention_bwd_dq_kernel /
  * rational_attention_bwd_dkv_kernel (backward.py:62-158, 165-266, 273-341).
  * ---------------------------------------------------------------------------------- */

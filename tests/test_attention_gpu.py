@@ -131,29 +131,97 @@ def test_strided_views_of_packed_projection():
     assert norm_max_err(out, ref) < FP32_TOL and norm_max_err(pd.grad, pr.grad) < FP32_TOL
 
 
+def assert_16bit_bar(got, want, what=""):
+    """Every element of out, dq, dk, dv within |a-b| <= 1e-2 + 2e-2 |b| of the float32 oracle."""
+    for g, w, name in zip(got, want, ("out", "dq", "dk", "dv")):
+        bad, nme = bf16_violations(g.float(), w)
+        assert not torch.isnan(g.float()).any(), f"{what}{name}: NaN"
+        assert bad == 0.0, f"{what}{name}: {bad:.2e} of elements outside the bar (norm max err {nme:.2e})"
+
+
+# the last two are the attention shapes of the small LM (12 heads: slopes that are no powers of one base, D=64, T=1024)
+# and of the XL LM (16 heads, D=128, T=2048)
+LOWP_SHAPES = [(1, 2, 64, 64), (2, 4, 200, 64), (1, 2, 333, 128), (1, 3, 100, 32), (1, 16, 512, 128),
+               (8, 12, 1024, 64), (1, 16, 2048, 128)]
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(1, 2, 64, 64), (2, 4, 200, 64), (1, 2, 333, 128), (1, 3, 100, 32), (1, 16, 512, 128)])
-@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("shape", LOWP_SHAPES)
+@pytest.mark.parametrize("path", [0, 1, 3])
 def test_low_precision_vs_oracle(shape, dtype, path):
-    """bf16 / fp16: inputs rounded, oracle in float32 on the rounded values, bar rel 2e-2 / abs 1e-2."""
+    """bf16 / fp16: inputs rounded, oracle in float32 on the rounded values, bar rel 2e-2 / abs 1e-2 on every element
+    of the output and of the three gradients, for the fused tensor-core kernels (0), the CUDA-core kernels (1) and the
+    deterministic tensor-core pair (3)."""
     B, H, T, D = shape
+    if path == 3 and D not in (64, 128):
+        pytest.skip("no tensor-core kernel for this head size")
+    if path == 1 and B * H * T >= 8 * 12 * 1024 and dtype == torch.float16:
+        pytest.skip("the CUDA-core kernels are covered on this shape in bf16")
     q, k, v, go = gen_qkv(26, B, H, T, D, dtype)
     slopes = oracle.compute_alibi_slopes(H)
     scale = 1.0 / math.sqrt(D)
-    out, dq, dk, dv = run_attention(q, k, v, go, slopes, scale, path=path)
+    got = run_attention(q, k, v, go, slopes, scale, path=path)
     want = oracle.rational_attention_grads(q.float(), k.float(), v.float(), go.float(), slopes, scale)
-    tensor_core = path == 0 and D in (64, 128)
-    for got, w, name in zip((out, dq, dk, dv), want, ("out", "dq", "dk", "dv")):
-        bad, nme = bf16_violations(got.float(), w)
-        if tensor_core and dtype == torch.bfloat16 and name in ("dq", "dk"):
-            # On the tensor cores dS enters the dQ / dK contractions rounded to bf16 (8 significand bits; the
-            # hardware takes both operands of one MMA in one format, so it cannot be kept in fp16 next to
-            # bf16 K / Q).  That rounding alone leaves a few elements in 10^4 just outside the element-wise
-            # bar; the normalised max error stays below 1.5e-2.  fp16 tensors and the CUDA-core path meet
-            # the bar on every element.
-            assert bad < 5e-3 and nme < 1.5e-2, f"{name}: {bad:.2e} outside the bar (norm max err {nme:.2e})"
-        else:
-            assert bad == 0.0, f"{name}: {bad:.2e} of elements outside the bar (norm max err {nme:.2e})"
+    assert_16bit_bar(got, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("path", [0, 3])
+@pytest.mark.parametrize("gscale", [1e-6, 1e-2, 1e2, 1e4, 1e6])
+def test_gradient_magnitude_does_not_matter(dtype, path, gscale):
+    """d_out as a loss scaler or a late-training step leaves it: the tensor-core backward stores dS as float16 scaled by
+    a power of two taken from max|d_out| of the (batch, head), so the gradients are d_out-homogeneous - finite, and
+    inside the bar after dividing the scale out again."""
+    B, H, T, D = 1, 4, 300, 128
+    q, k, v, go = gen_qkv(41, B, H, T, D, dtype)
+    if dtype == torch.float16 and not 1e-3 < gscale < 1e3:
+        pytest.skip("d_out or the gradients themselves would leave float16's range")
+    slopes = oracle.compute_alibi_slopes(H)
+    scale = 1.0 / math.sqrt(D)
+    go_scaled = (go.float() * gscale).to(dtype)
+    out, dq, dk, dv = run_attention(q, k, v, go_scaled, slopes, scale, path=path)
+    want = oracle.rational_attention_grads(q.float(), k.float(), v.float(), go_scaled.float() / gscale, slopes, scale)
+    for g in (dq, dk, dv):
+        assert torch.isfinite(g.float()).all()
+    assert_16bit_bar((out, dq.float() / gscale, dk.float() / gscale, dv.float() / gscale), want, f"x{gscale:g} ")
+
+
+def test_bf16_inputs_beyond_float16_are_reported():
+    """The tensor-core backward works on float16 copies of q and k.  A bfloat16 magnitude of 65536 or more does not fit:
+    the kernel clamps it and says so in the status word; the CUDA-core path takes such tensors."""
+    B, H, T, D = 1, 2, 256, 64
+    q, k, v, go = gen_qkv(42, B, H, T, D, torch.bfloat16)
+    k[0, 1, 200, 3] = 1.0e5
+    slopes = oracle.compute_alibi_slopes(H)
+    with pytest.raises(RuntimeError, match="65536"):
+        run_attention(q, k, v, go, slopes, 0.125, path=2)
+    got = run_attention(q, k, v, go, slopes, 0.125, path=1)
+    want = oracle.rational_attention_grads(q.float(), k.float(), v.float(), go.float(), slopes, 0.125)
+    assert_16bit_bar(got, want)
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 333, 64), (1, 16, 700, 128), (2, 12, 1024, 64)])
+def test_packed_projection_bf16_tensor_path(shape):
+    """The model's layout on the tensor cores: q, k, v read in place from one [B,T,3,H,D] projection through strided
+    tensor maps, the output written token-major, the three gradients landing in one packed buffer
+    (algebraic_model.py:89-107) - against the oracle on the permuted views."""
+    from fastalgebraictransformer_b200.backward import RationalAttentionPackedFunction
+    B, H, T, D = shape
+    g = torch.Generator().manual_seed(43)
+    packed = torch.randn(B, T, 3, H, D, generator=g).to(torch.bfloat16)
+    go = torch.randn(B, T, H * D, generator=g).to(torch.bfloat16)
+    slopes = oracle.compute_alibi_slopes(H)
+    scale = 1.0 / math.sqrt(D)
+    pd = packed.to(DEV).requires_grad_(True)
+    out = RationalAttentionPackedFunction.apply(pd, slopes.to(DEV), scale, 1e-6)
+    assert out.shape == (B, T, H * D) and out.is_contiguous()
+    out.backward(go.to(DEV))
+    fat().check_device_status()
+    q, k, v = packed.float().permute(2, 0, 3, 1, 4).unbind(0)
+    want = oracle.rational_attention_grads(q, k, v, go.float().view(B, T, H, D).permute(0, 2, 1, 3), slopes, scale)
+    got_out = out.detach().view(B, T, H, D).permute(0, 2, 1, 3)
+    gq, gk, gv = pd.grad.permute(2, 0, 3, 1, 4).unbind(0)
+    assert_16bit_bar((got_out, gq, gk, gv), want)
 
 
 def test_deterministic():
@@ -187,9 +255,8 @@ def test_deterministic_tensor_path(D):
         else:
             assert norm_max_err(x.float(), y.float().cpu()) < 1e-2, name
     want = oracle.rational_attention_grads(q.float(), k.float(), v.float(), go.float(), slopes, 0.09)
-    for got, w, name in zip(c, want, ("out", "dq", "dk", "dv")):
-        bad, nme = bf16_violations(got.float(), w)
-        assert bad < 5e-3 and nme < 1.5e-2, f"{name}: {bad:.2e} outside the bar (norm max err {nme:.2e})"
+    assert_16bit_bar(c, want, "fused ")
+    assert_16bit_bar(a, want, "deterministic ")
 
 
 @pytest.mark.parametrize("T", [640, 1280, 1408])
@@ -245,17 +312,15 @@ def test_config2_slice_bf16():
             assert (a[1:] != b).float().mean().item() < 1e-2 and norm_max_err(a[1:].float(), b.float().cpu()) < 1e-2
         else:
             assert torch.equal(a[1:], b), name
+    # all 16 heads of batch element 0 against the oracle, one head at a time (keeps the oracle's S x S temporaries small);
+    # heads 8-15 have slopes <= 2^-4.5: row sums in the hundreds to thousands, every key contributes
+    for h in range(H):
+        sl = slice(h, h + 1)
+        want = oracle.rational_attention_grads(q[:1, sl].float(), k[:1, sl].float(), v[:1, sl].float(), go[:1, sl].float(),
+                                               slopes[sl], scale)
+        assert_16bit_bar(tuple(t[:1, sl] for t in full), want, f"head {h} ")
+    # the CUDA-core kernels meet the bar on the two steepest heads of the same batch element
     want = oracle.rational_attention_grads(q[:1, :2].float(), k[:1, :2].float(), v[:1, :2].float(), go[:1, :2].float(),
                                            slopes[:2], scale)
-    got = run_attention(q[:1, :2], k[:1, :2], v[:1, :2], go[:1, :2], slopes[:2], scale)
-    for a, w, name in zip(got, want, ("out", "dq", "dk", "dv")):
-        bad, nme = bf16_violations(a.float(), w)
-        if name in ("dq", "dk"):       # bf16 dS operand on the tensor cores, see test_low_precision_vs_oracle
-            assert bad < 5e-3 and nme < 1.5e-2, f"{name}: {bad:.2e} outside the bar (norm max err {nme:.2e})"
-        else:
-            assert bad == 0.0, f"{name}: {bad:.2e} outside the bar (norm max err {nme:.2e})"
-    # the CUDA-core kernels meet the bar on every element of the same slice
     got = run_attention(q[:1, :2], k[:1, :2], v[:1, :2], go[:1, :2], slopes[:2], scale, path=1)
-    for a, w, name in zip(got, want, ("out", "dq", "dk", "dv")):
-        bad, nme = bf16_violations(a.float(), w)
-        assert bad == 0.0, f"simt {name}: {bad:.2e} outside the bar (norm max err {nme:.2e})"
+    assert_16bit_bar(got, want, "simt ")
