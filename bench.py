@@ -1,15 +1,19 @@
 #!/usr/bin/env python
 """Benchmark of the Algebraic-Transformer hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload attn|swiglu|norm|softmax|lm_small|lm_xl]
-                    [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload attn|swiglu|norm|softmax|add_norm|loss_head|lm_small|lm_xl]
+                    [--impl ours|reference] [--scaling strong|weak] [--no-extras]
 
-Default workload ``attn``: causal rational attention forward+backward, bf16, B=8, H=16, S=4096,
-D=128 with ALiBi — per GPU (weak scaling: every rank processes its own 128 (batch, head) units,
-no collective on the data path).  One JSON line is printed by rank 0.
+Default workload ``attn``: causal rational attention forward+backward, bf16, B=8, H=16, S=4096, D=128 with
+ALiBi.  With N ranks the 128 (batch, head) units are split into contiguous blocks of 128/N per rank (strong
+scaling, no collective on the data path: the units are independent); ``--scaling weak`` gives every rank the
+whole problem instead.  The line of the default workload also carries, under ``extra``, the second half of the
+headline metric and the bandwidth-sweep configuration measured in the same process at the same N: the small
+language model's training step (tokens/s, CUDA-graph replay and eager launches) and SwiGLU / mean-error norm /
+rational softmax forward+backward in GB/s.  One JSON line is printed by rank 0.
 
-``--impl reference`` times the CPU restatement of the reference's PyTorch path (the oracle) on the
-host cores on a bounded sample of the same workload.
+``--impl reference`` times the CPU restatement of the reference's PyTorch path (the oracle) on the host cores
+on a bounded sample of the same workload.
 """
 from __future__ import annotations
 
@@ -112,6 +116,12 @@ def max_over_ranks(ms: float, world: int, device) -> float:
     return float(t.item())
 
 
+def launch_count() -> int:
+    """Kernels launched so far by libfat_b200.so in this process (the library counts them itself)."""
+    from fastalgebraictransformer_b200 import _lib
+    return int(_lib.lib().fat_launch_count())
+
+
 def barrier(world: int):
     if world > 1:
         import torch.distributed as dist
@@ -199,14 +209,40 @@ def make_attn_inputs(cfg, seed, device=None, pin=False):
     return ts, slopes
 
 
+# DRAM bytes of the three backward launches of one step at B=2 (ncu, dram__bytes_read.sum + dram__bytes_write.sum):
+# profiles/attention_bf16_B2_H16_S4096_D128.md, table "DRAM traffic per launch"; traffic grows in proportion to
+# the (batch, head) units, so the full-size figure is this one scaled by units / 32.
+ATTN_BWD_TRAFFIC_B2 = 472.8e6
+
+
+def shard_batches(B: int, H: int, rank: int, world: int):
+    """The block of the B*H independent (batch, head) units that `rank` owns when they are dealt out in contiguous blocks
+    of B*H/world: returned as (first batch element, number of batch elements).  Blocks are whole batch elements (every rank
+    keeps all heads, hence all ALiBi slopes), which needs world to divide B."""
+    if B % world:
+        raise SystemExit(f"splitting {B * H} (batch, head) units over {world} ranks in whole batch elements needs the "
+                         f"batch ({B}) to be a multiple of the ranks")
+    nb = B // world
+    return rank * nb, nb
+
+
 def bench_attn(args, rank, world, device):
     import fastalgebraictransformer_b200 as fat
     from fastalgebraictransformer_b200 import _lib
-    cfg = dict(ATTN, B=args.batch) if args.batch else ATTN
-    (q, k, v, go), slopes = make_attn_inputs(cfg, 1234 + 1 + rank, device)
+    full = dict(ATTN, B=args.batch) if args.batch else dict(ATTN)
+    strong = args.scaling == "strong" and world > 1
+    lo, nb = shard_batches(full["B"], full["H"], rank, world) if strong else (0, full["B"])
+    cfg = dict(full, B=nb)
+    # every rank draws the whole problem from one seed and keeps its block, so the union over ranks is the 1-GPU input
+    (q, k, v, go), slopes = make_attn_inputs(full, 1234 + 1 + (0 if strong else rank))
+    if strong:
+        q, k, v, go = (t[lo:lo + nb].contiguous() for t in (q, k, v, go))
+    host_in = [t.pin_memory() for t in (q, k, v, go)]
+    q, k, v, go = (t.to(device) for t in host_in)
     slopes = slopes.to(device)
     scale = 1.0 / math.sqrt(cfg["D"])
-    fwd_flops, bwd_flops = attn_flops(**cfg)
+    fwd_flops, bwd_flops = attn_flops(**cfg)              # this rank's share
+    total_flops = (fwd_flops + bwd_flops) * world
     path = _lib.lib().fat_attn_select_path(cfg["S"], cfg["D"], _lib.BF16, 1, 1, 1)
 
     state = {}
@@ -221,16 +257,22 @@ def bench_attn(args, rank, world, device):
     def step():
         fwd(); bwd()
 
+    for _ in range(2):
+        step()
+    n0 = launch_count()
+    step()
+    launches_per_step = launch_count() - n0
     with ClockSampler(device.index) as clocks:
         ms = time_steps(step, args.steps, args.warmup, world, device)
     fat.check_device_status()
     ms_fwd = time_steps(fwd, max(3, args.steps // 2), 1, world, device)
     ms_bwd = time_steps(bwd, max(3, args.steps // 2), 1, world, device)
+    # the same step back to back for about a second: the regime the sustained peak is defined on
+    sus_steps = max(args.steps, int(1.2e3 / max(ms, 1e-3)))
+    with ClockSampler(device.index) as sus_clocks:
+        ms_sus = time_steps(step, sus_steps, 1, world, device)
 
     # end to end through the public autograd API with host buffers (pinned), copies inside the timed region
-    host_in, _ = make_attn_inputs(cfg, 1234 + 1 + rank, pin=True)
-    hq = host_in[0]
-
     def e2e_compute(d):
         dq, dk, dv = (t.detach().requires_grad_(True) for t in d[:3])
         out = fat.rational_attention(dq, dk, dv, slopes, scale)
@@ -240,89 +282,113 @@ def bench_attn(args, rank, world, device):
     e2e_step = make_pipelined_e2e(device, host_in, e2e_compute)
     e2e_steps = max(4, min(args.steps, 8))
     ms_e2e = time_steps(e2e_step, e2e_steps, 2, world, device)
-    nbytes = hq.numel() * hq.element_size()
+    nbytes = host_in[0].numel() * host_in[0].element_size()
 
     peaks = measured_peaks()
-    launches_per_step = {1: 3, 2: 4}.get(path, 3)       # tensor path: forward, prepare (+ accumulator clear), fused backward, d_q convert
-    tfl = (fwd_flops + bwd_flops) * world / (ms * 1e-3) / 1e12
+    tfl = total_flops / (ms * 1e-3) / 1e12
+    tfl_sus = total_flops / (ms_sus * 1e-3) / 1e12
     bwd_tfl = bwd_flops / (ms_bwd * 1e-3) / 1e12
-    return {
+    res = {
         "metric": "rational_attention_fwd_bwd_tflops", "value": tfl, "unit": "TFLOP/s",
-        "ms_per_step": ms, "dtype": "bf16",
-        "config": {"workload": f"rational_attention fwd+bwd causal ALiBi bf16 B={cfg['B']} H=16 S=4096 D=128 per GPU "
-                               + ("(headline configuration)" if cfg["B"] == 8 else "(REDUCED batch: profiling case, not a bench value)"),
-                   "units_per_gpu": cfg["B"] * cfg["H"], "shard": "batch x head",
-                   "kernel_path": "tcgen05" if path == 2 else "simt", "l2": "inputs (4 x 134 MB) exceed the 126 MB L2",
+        "ms_per_step": ms, "dtype": "bf16", "scaling": "strong" if strong or world == 1 else "weak",
+        "config": {"workload": f"rational_attention fwd+bwd causal ALiBi bf16 B={full['B']} H=16 S=4096 D=128 "
+                               + ("(headline configuration)" if full["B"] == 8 else "(REDUCED batch: profiling case, not a bench value)")
+                               + (f", split over the ranks in blocks of {cfg['B'] * cfg['H']} (batch, head) units" if strong
+                                  else (", the whole problem on every rank" if world > 1 else "")),
+                   "units_per_gpu": cfg["B"] * cfg["H"], "shard": "batch x head, contiguous blocks, no collective",
+                   "kernel_path": "tcgen05" if path == 2 else "simt", "l2": "inputs (4 x 134 MB at 128 units) exceed the 126 MB L2"
+                   if cfg["B"] * cfg["H"] >= 128 else f"inputs of this rank: 4 x {nbytes / 1e6:.0f} MB (the step also writes 5 tensors of that size)",
                    "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
-                   "pct_of_bf16_peak": 100.0 * tfl / world / peaks["bf16_tflops"]},
-        "e2e": {"value": (fwd_flops + bwd_flops) * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                   "pct_of_bf16_peak": 100.0 * tfl / world / peaks["bf16_tflops"],
+                   "sustained_ms": ms_sus, "sustained_steps": sus_steps, "sustained_tflops": tfl_sus,
+                   "sustained_frac_of_sustained_peak": tfl_sus / world / peaks["bf16_tflops_sustained"],
+                   "sustained_clocks": sus_clocks.summary()},
+        "e2e": {"value": total_flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes, "ms_per_step": ms_e2e,
                 "overlap": E2E_OVERLAP},
         "gpu_launches": launches_per_step * args.steps,
-        # traffic: dram bytes of the three backward launches, ncu capture at B=2 scaled by the units processed
-        # (the capture's summary is kept with the other profiler summaries of this repository)
+        "gpu_launches_how": "fat_launch_count() of libfat_b200.so around one step, times the steps of the timed region",
         "roofline": {"bound": "tensor", "kernel": "attention backward (prepare + fused d_k/d_v/d_q + d_q convert launches)", "achieved": bwd_tfl,
                      "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": bwd_tfl / peaks["bf16_tflops"],
-                     "traffic": 472.8e6 * cfg["B"] / 2, "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
-                     "fwd_achieved": fwd_flops / (ms_fwd * 1e-3) / 1e12},
+                     "traffic": ATTN_BWD_TRAFFIC_B2 * cfg["B"] * cfg["H"] / 32,
+                     "traffic_source": "profiles/attention_bf16_B2_H16_S4096_D128.md (B=2 capture, scaled by the units)",
+                     "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                     "fwd_achieved": fwd_flops / (ms_fwd * 1e-3) / 1e12,
+                     "step_frac": tfl / world / peaks["bf16_tflops"]},
         "clocks": clocks.summary(),
     }
+    del q, k, v, go, host_in, state, e2e_step
+    torch.cuda.empty_cache()
+    return res
 
 
-# `traffic`: dram bytes of one step's launches, from an ncu capture of these kernels at these shapes
+# `bytes`: algorithmic bytes of one forward+backward (2-byte elements; every tensor moved once):
+#   swiglu   fwd gate, value in, out out (3) + bwd d_out, gate, value in, d_gate, d_value out (5) = 8 passes
+#   norm     fwd x in, y out (2) + bwd d_out, x in, d_x out (3) = 5 passes (+ weight, means, d_weight: KBs)
+#   softmax  fwd x in, p out (2) + bwd d_out, x in, d_x out (3) = 5 passes: the backward recomputes p from x instead
+#            of reading the saved p (the variant that moves 3 tensors in the backward)
+# `traffic`: dram__bytes_read.sum + dram__bytes_write.sum of one step's launches at these shapes, from
+# profiles/fused_ops_bf16_config3.md (table "DRAM traffic per step")
 FUSED = {
-    "swiglu": dict(rows=16384, cols=8192, bytes=2147483648, traffic=2068e6),
-    "norm": dict(rows=16384, cols=4096, bytes=671088640, traffic=587e6),
-    "softmax": dict(rows=4096, cols=4096, bytes=150994944, traffic=106e6),   # backward reads d_out and x only (p is recomputed)
+    "swiglu": dict(rows=16384, cols=8192, bytes=8 * 16384 * 8192 * 2, traffic=2068e6),
+    "norm": dict(rows=16384, cols=4096, bytes=5 * 16384 * 4096 * 2, traffic=587e6),
+    "softmax": dict(rows=4096, cols=4096, bytes=5 * 4096 * 4096 * 2, traffic=106e6),
     # residual addition fused with the norm: forward x, residual in, sum, y out; backward d_y, d_sum_in, sum in, d_sum out
     "add_norm": dict(rows=16384, cols=4096, bytes=8 * 16384 * 4096 * 2, traffic=None),
     # loss head of the small LM: logits [8, 1024, 32000] read once, their gradient written once
     "loss_head": dict(rows=8 * 1024, cols=32000, bytes=2 * 8 * 1024 * 32000 * 2, traffic=None),
 }
+FUSED_TRAFFIC_SOURCE = "profiles/fused_ops_bf16_config3.md"
 
 
-def bench_fused(args, rank, world, device, name):
+def fused_inputs(name, gen, device=None, rows=None):
+    """One input set of a fused-op workload (bf16).  `gen` is a torch.Generator on `device` (or on the CPU)."""
+    cfg = FUSED[name]
+    shape = (rows or cfg["rows"], cfg["cols"])
+    dev = device if device is not None else "cpu"
+
+    def rnd(std=1.0):
+        return (torch.randn(*shape, generator=gen, device=dev) * std).to(torch.bfloat16)
+
+    def weight():
+        return (1 + 0.1 * torch.randn(cfg["cols"], generator=gen, device=dev)).to(torch.bfloat16)
+
+    if name == "swiglu":
+        return (rnd(), rnd(), rnd())                                          # gate, value, d_out
+    if name == "norm":
+        return (rnd(), weight(), rnd())                                       # x, weight, d_out
+    if name == "add_norm":
+        return (rnd(), weight(), rnd(), rnd(), rnd())                         # x, weight, residual, d_y, d_h
+    if name == "loss_head":
+        labels = torch.randint(0, cfg["cols"], (8, shape[0] // 8), generator=gen, device=dev)
+        return (rnd(2.0).view(8, shape[0] // 8, cfg["cols"]), labels)
+    return (rnd(math.sqrt(2.0)), rnd())                                       # softmax: scores ~ N(0, 2), d_out
+
+
+def run_fused(name, steps, warmup, rank, world, device, with_e2e=True):
     import fastalgebraictransformer_b200 as fat
     cfg = FUSED[name]
     g = torch.Generator(device=device).manual_seed(1234 + 2 + rank)
     shape = (cfg["rows"], cfg["cols"])
     nset = 1 if name != "softmax" else 6        # softmax tensors (33.5 MB) fit in L2: rotate 6 sets (> 126 MB each pass)
-
-    def rnd(std=1.0):
-        return (torch.randn(*shape, generator=g, device=device) * std).to(torch.bfloat16)
-
-    sets = []
-    for _ in range(nset):
-        if name == "swiglu":
-            sets.append((rnd().requires_grad_(True), rnd().requires_grad_(True), rnd()))
-        elif name == "norm":
-            w = (1 + 0.1 * torch.randn(cfg["cols"], generator=g, device=device)).to(torch.bfloat16)
-            sets.append((rnd().requires_grad_(True), w.requires_grad_(True), rnd()))
-        elif name == "add_norm":
-            w = (1 + 0.1 * torch.randn(cfg["cols"], generator=g, device=device)).to(torch.bfloat16)
-            sets.append((rnd(), w, rnd(), rnd(), rnd()))                       # x, weight, residual, d_y, d_h
-        elif name == "loss_head":
-            labels = torch.randint(0, cfg["cols"], (8, 1024), generator=g, device=device)
-            sets.append((rnd(2.0).view(8, 1024, cfg["cols"]), labels))
-        else:
-            sets.append((rnd(math.sqrt(2.0)).requires_grad_(True), rnd()))
+    sets = [fused_inputs(name, g, device) for _ in range(nset)]
     it = [0]
     alg = torch.ops.algebraic
 
     def step():
         s = sets[it[0] % nset]; it[0] += 1
         if name == "swiglu":
-            out = alg.swiglu_fwd(s[0].detach(), s[1].detach()); alg.swiglu_bwd(s[2], s[0].detach(), s[1].detach())
+            alg.swiglu_fwd(s[0], s[1]); alg.swiglu_bwd(s[2], s[0], s[1])
         elif name == "norm":
-            y, mean = alg.norm_fwd(s[0].detach(), s[1].detach(), 1e-6)
-            alg.norm_bwd(s[2], s[0].detach(), s[1].detach(), mean, 1e-6)
+            y, mean = alg.norm_fwd(s[0], s[1], 1e-6)
+            alg.norm_bwd(s[2], s[0], s[1], mean, 1e-6)
         elif name == "add_norm":
             h, y, mean = alg.add_norm_fwd(s[0], s[2], s[1], 1e-6)
             alg.add_norm_bwd(s[3], s[4], h, s[1], mean, 1e-6)
         elif name == "loss_head":
             alg.shifted_ce_fwd(s[0], s[1], -100)
         else:
-            alg.softmax_fwd(s[0].detach(), 1e-6); alg.softmax_bwd(s[1], s[0].detach(), 1e-6)
+            alg.softmax_fwd(s[0], 1e-6); alg.softmax_bwd(s[1], s[0], 1e-6)
 
     # These kernels last 10-100 us, less than the host needs to issue one, so each step is captured once in
     # a CUDA graph (one graph per rotating input set) and the timed region replays the graphs.
@@ -333,10 +399,13 @@ def bench_fused(args, rank, world, device, name):
             step()
     torch.cuda.current_stream(device).wait_stream(side)
     graphs = []
+    launches_per_step = 0
     for _ in range(nset):
         gr = torch.cuda.CUDAGraph()
+        n0 = launch_count()
         with torch.cuda.graph(gr):
             step()
+        launches_per_step = launch_count() - n0
         graphs.append(gr)
     gi = [0]
 
@@ -344,49 +413,55 @@ def bench_fused(args, rank, world, device, name):
         graphs[gi[0] % nset].replay(); gi[0] += 1
 
     with ClockSampler(device.index) as clocks:
-        ms = time_steps(replay, args.steps, args.warmup, world, device)
+        ms = time_steps(replay, steps, warmup, world, device)
     peaks = measured_peaks()
     gbs = cfg["bytes"] * world / (ms * 1e-3) / 1e9
-
-    # end to end: host (pinned) -> device -> forward+backward through the autograd API -> host
-    hs = [t.detach().cpu().pin_memory() for t in sets[0]]
-
-    def e2e_compute(dd):
-        d = [t.detach() for t in dd]
-        if name == "swiglu":
-            a, b = d[0].requires_grad_(True), d[1].requires_grad_(True)
-            o = fat.rational_swiglu(a, b); o.backward(d[2]); return (o.detach(), a.grad, b.grad)
-        if name == "norm":
-            a, w = d[0].requires_grad_(True), d[1].requires_grad_(True)
-            o = fat.mean_error_norm(a, w); o.backward(d[2]); return (o.detach(), a.grad)
-        if name == "loss_head":
-            a = d[0].requires_grad_(True)
-            loss = fat.shifted_cross_entropy(a, d[1]); loss.backward(); return (loss.detach().reshape(1), a.grad)
-        if name == "add_norm":
-            a, w, r = d[0].requires_grad_(True), d[1].requires_grad_(True), d[2].requires_grad_(True)
-            h, y = fat.add_mean_error_norm(a, r, w)
-            torch.autograd.backward([h, y], [d[4], d[3]]); return (h.detach(), y.detach(), a.grad)
-        a = d[0].requires_grad_(True)
-        o = fat.rational_softmax(a); o.backward(d[1]); return (o.detach(), a.grad)
-
-    e2e_step = make_pipelined_e2e(device, hs, e2e_compute)
-    ms_e2e = time_steps(e2e_step, 6, 2, world, device)
-    n_out = {"swiglu": 3, "norm": 2, "softmax": 2, "add_norm": 3, "loss_head": 1}[name]
-    return {
+    res = {
         "metric": f"rational_{name}_fwd_bwd_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "dtype": "bf16",
-        "config": {"workload": f"{name} fwd+bwd bf16 [{cfg['rows']},{cfg['cols']}] (bandwidth-sweep configuration)",
+        "scaling": "weak",
+        "config": {"workload": f"{name} fwd+bwd bf16 [{cfg['rows']},{cfg['cols']}] per GPU (bandwidth-sweep configuration)",
                    "algorithmic_bytes_per_step": cfg["bytes"],
                    "launch": "each step replayed from a CUDA graph",
                    "l2": "tensors exceed L2" if nset == 1 else f"{nset} rotating input sets (each pass touches > 126 MB before reuse)"},
-        "e2e": {"value": cfg["bytes"] * world / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
-                "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in hs),
-                "d2h_bytes_per_step": n_out * shape[0] * shape[1] * 2, "ms_per_step": ms_e2e, "overlap": E2E_OVERLAP},
-        "gpu_launches": {"norm": 3, "add_norm": 3, "loss_head": 1}.get(name, 2) * args.steps,
+        "gpu_launches": launches_per_step * steps,
+        "gpu_launches_how": "fat_launch_count() of libfat_b200.so around the capture of one step, times the replays of the timed region",
         "roofline": {"bound": "hbm", "kernel": f"{name} fwd+bwd", "achieved": gbs / world, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": gbs / world / peaks["hbm_gbs"], "traffic": cfg["traffic"],
-                     "peak_source": peaks["source"]},
+                     "traffic_source": FUSED_TRAFFIC_SOURCE if cfg["traffic"] else None,
+                     "peak_source": peaks["source"] + " (copy bandwidth)"},
         "clocks": clocks.summary(),
     }
+    if with_e2e:
+        # end to end: host (pinned) -> device -> forward+backward through the autograd API -> host
+        hs = [t.detach().cpu().pin_memory() for t in sets[0]]
+
+        def e2e_compute(dd):
+            d = [t.detach() for t in dd]
+            if name == "swiglu":
+                a, b = d[0].requires_grad_(True), d[1].requires_grad_(True)
+                o = fat.rational_swiglu(a, b); o.backward(d[2]); return (o.detach(), a.grad, b.grad)
+            if name == "norm":
+                a, w = d[0].requires_grad_(True), d[1].requires_grad_(True)
+                o = fat.mean_error_norm(a, w); o.backward(d[2]); return (o.detach(), a.grad)
+            if name == "loss_head":
+                a = d[0].requires_grad_(True)
+                loss = fat.shifted_cross_entropy(a, d[1]); loss.backward(); return (loss.detach().reshape(1), a.grad)
+            if name == "add_norm":
+                a, w, r = d[0].requires_grad_(True), d[1].requires_grad_(True), d[2].requires_grad_(True)
+                h, y = fat.add_mean_error_norm(a, r, w)
+                torch.autograd.backward([h, y], [d[4], d[3]]); return (h.detach(), y.detach(), a.grad)
+            a = d[0].requires_grad_(True)
+            o = fat.rational_softmax(a); o.backward(d[1]); return (o.detach(), a.grad)
+
+        e2e_step = make_pipelined_e2e(device, hs, e2e_compute)
+        ms_e2e = time_steps(e2e_step, 6, 2, world, device)
+        n_out = {"swiglu": 3, "norm": 2, "softmax": 2, "add_norm": 3, "loss_head": 1}[name]
+        res["e2e"] = {"value": cfg["bytes"] * world / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                      "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in hs),
+                      "d2h_bytes_per_step": n_out * shape[0] * shape[1] * 2, "ms_per_step": ms_e2e, "overlap": E2E_OVERLAP}
+    del sets, graphs
+    torch.cuda.empty_cache()
+    return res
 
 
 LM = {
@@ -395,7 +470,10 @@ LM = {
 }
 
 
-def bench_lm(args, rank, world, device, name):
+def run_lm(name, steps, warmup, rank, world, device, graph=True, eager_steps=0):
+    """One training step (forward, loss, backward with DDP's gradient all-reduce when world > 1, fused AdamW) of the
+    named model.  graph: capture the step in a CUDA graph and time its replays; eager_steps > 0: also time that many
+    steps issued launch by launch, as a user of the module would (reported as `eager_ms`)."""
     from fastalgebraictransformer_b200 import AlgebraicTransformerLM
     cfg = LM[name]
     torch.manual_seed(1234 + 3)
@@ -437,54 +515,95 @@ def bench_lm(args, rank, world, device, name):
     # side stream before a capture.
     launch = "eager"
     timed = step
-    if not args.no_graph:
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        for _ in range(3 if world == 1 else 11):
+            step()
+    torch.cuda.current_stream(device).wait_stream(side)
+    n0 = launch_count()
+    step()
+    launches_per_step = launch_count() - n0
+    eager_ms = None
+    if eager_steps > 0:
+        eager_ms = time_steps(step, eager_steps, 2, world, device)
+    if graph:
         try:
-            side = torch.cuda.Stream(device)
-            side.wait_stream(torch.cuda.current_stream(device))
-            with torch.cuda.stream(side):
-                for _ in range(3 if world == 1 else 11):
-                    step()
-            torch.cuda.current_stream(device).wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
+            graph_obj = torch.cuda.CUDAGraph()
             opt.zero_grad(set_to_none=True)
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph_obj):
                 _, gloss = net(ids, labels=lab)
                 gloss.backward()
                 opt.step()
             last["loss"] = gloss
 
             def timed():
-                graph.replay()
+                graph_obj.replay()
             launch = "cuda graph replay"
         except Exception as exc:      # noqa: BLE001 - fall back to eager launches, say so in the output
             print(f"graph capture failed ({exc!r}); timing eager launches", file=sys.stderr)
             torch.cuda.synchronize(device)
             timed, launch = step, "eager (graph capture failed)"
     with ClockSampler(device.index) as clocks:
-        ms = time_steps(timed, args.steps, args.warmup, world, device)
-    ms_e2e = time_steps(e2e_step, max(2, args.steps // 2), 1, world, device)
+        ms = time_steps(timed, steps, warmup, world, device)
+    ms_e2e = time_steps(e2e_step, max(2, steps // 2), 1, world, device)
     tokens = cfg["batch"] * cfg["seq"] * world
     peaks = measured_peaks()
     d_head = cfg["d_model"] // cfg["n_head"]
     attn = cfg["n_layers"] * 3.5 * 2 * cfg["batch"] * cfg["n_head"] * cfg["seq"] ** 2 * d_head
     flops = 6.0 * (n_params) * cfg["batch"] * cfg["seq"] + attn
-    return {
+    res = {
         "metric": "lm_train_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
-        "dtype": "bf16",
+        "dtype": "bf16", "scaling": "weak",
         "config": {"workload": f"AlgebraicTransformerLM {name} training step (fwd+loss+bwd+AdamW), bf16, "
                                f"batch {cfg['batch']} x seq {cfg['seq']} per GPU", "params": n_params,
-                   "parallelism": f"dp{world}", "launch": launch, "loss": float(last["loss"].item())},
+                   "parallelism": f"dp{world}", "launch": launch, "loss": float(last["loss"].item()),
+                   "eager_ms": eager_ms, "eager_tokens_per_s": tokens / (eager_ms * 1e-3) if eager_ms else None},
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * hids.numel() * 8,
-                "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e},
-        # this library's kernels per step: per layer 2 (add-)norm forward, attention forward, SwiGLU forward, 2 x 2 norm
-        # backward (+ d_weight reduce), 3 attention backward, SwiGLU backward = 12; final add-norm (1 + 2), loss head (1 + 1)
-        "gpu_launches": (cfg["n_layers"] * 12 + 5) * args.steps,
+                "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e, "launch": "eager"},
+        "gpu_launches": launches_per_step * steps,
+        "gpu_launches_how": "fat_launch_count() of libfat_b200.so around one eager step, times the steps of the timed region "
+                            "(the GEMMs, AdamW and NCCL launches of the step are library kernels and not counted)",
         "roofline": {"bound": "tensor", "kernel": "whole step (GEMMs in cuBLAS + this library's kernels)",
                      "achieved": flops / (ms * 1e-3) / 1e12, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], "traffic": None,
                      "peak_source": peaks["source"] + " (sustained cuBLAS bf16)"},
         "clocks": clocks.summary(),
     }
+    del net, model, opt
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_extras(args, rank, world, device):
+    """Compact records of the other configurations at the same N, for the default workload's line: the small LM's
+    training step and the three bandwidth-sweep operators.  A failure in one is recorded, not raised."""
+    extra = {}
+
+    def compact(r):
+        out = {"value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"], "scaling": r["scaling"],
+               "frac_of_peak": r["roofline"]["frac"], "peak": r["roofline"]["peak"], "workload": r["config"]["workload"],
+               "launch": r["config"].get("launch"), "gpu_launches_per_step": r["gpu_launches"] // max(1, r["_steps"]),
+               "clocks": r["clocks"]}
+        for k in ("eager_ms", "eager_tokens_per_s", "params", "parallelism"):
+            if r["config"].get(k) is not None:
+                out[k] = r["config"][k]
+        return out
+
+    for name in ("swiglu", "norm", "softmax"):
+        try:
+            r = run_fused(name, 50, 5, rank, world, device, with_e2e=False)
+            r["_steps"] = 50
+            extra[name] = compact(r)
+        except Exception as exc:      # noqa: BLE001
+            extra[name] = {"error": repr(exc)[:300]}
+    try:
+        r = run_lm("lm_small", 20, 3, rank, world, device, graph=True, eager_steps=10)
+        r["_steps"] = 20
+        extra["lm_small"] = compact(r)
+    except Exception as exc:      # noqa: BLE001
+        extra["lm_small"] = {"error": repr(exc)[:300]}
+    return extra
 
 
 # ------------------------------------------------------------------------------------------ CPU arm
@@ -498,65 +617,108 @@ def use_all_host_threads():
     return torch.get_num_threads()
 
 
-def cpu_attention_sample(heads: int, repeats: int = 1):
-    """The oracle (CPU restatement of the reference's PyTorch path) on `heads` heads of one batch element of the
-    attention workload, float32, all host threads.  Returns (seconds per pass, flops per pass)."""
+def cpu_sample(workload: str):
+    """A function that runs ONE bounded sample of `workload` through the oracle (the CPU restatement of the reference's
+    PyTorch path, float32, autograd for the gradients), the amount of the metric's unit it stands for, and a
+    description.  Returned as (run, amount, unit, what)."""
     from oracle import oracle
-    cfg = dict(ATTN, B=1, H=heads)
-    (q, k, v, go), slopes = make_attn_inputs(cfg, 1234 + 1)
-    q, k, v, go = (t.float() for t in (q, k, v, go))
-    slopes = slopes[:heads]
-    scale = 1.0 / math.sqrt(cfg["D"])
-    best = float("inf")
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        oracle.rational_attention_grads(q, k, v, go, slopes, scale)
-        best = min(best, time.perf_counter() - t0)
-    f, b = attn_flops(**cfg)
-    return best, f + b
+    if workload == "attn":
+        heads = 1
+        cfg = dict(ATTN, B=1, H=heads)
+        (q, k, v, go), slopes = make_attn_inputs(cfg, 1234 + 1)
+        q, k, v, go = (t.float() for t in (q, k, v, go))
+        scale = 1.0 / math.sqrt(cfg["D"])
+        f, b = attn_flops(**cfg)
+        return (lambda: oracle.rational_attention_grads(q, k, v, go, slopes[:heads], scale), (f + b) / 1e12, "TFLOP/s",
+                f"{heads} of the 128 (batch, head) units (S=4096, D=128), flops in the same causal convention")
+    if workload in ("swiglu", "norm", "softmax", "add_norm"):
+        cfg = FUSED[workload]
+        rows = {"swiglu": 2048, "norm": 4096, "softmax": 4096, "add_norm": 4096}[workload]
+        ins = [t.float() for t in fused_inputs(workload, torch.Generator().manual_seed(1234 + 2), rows=rows)]
+        amount = cfg["bytes"] * rows / cfg["rows"] / 1e9
+        what = f"rows 0..{rows - 1} of the [{cfg['rows']},{cfg['cols']}] tensors upcast to float32; bytes counted as for the bf16 kernels"
+        if workload == "swiglu":
+            return (lambda: oracle.autograd_grads(oracle.rational_swiglu, ins[:2], ins[2]), amount, "GB/s", what)
+        if workload == "norm":
+            return (lambda: oracle.autograd_grads(oracle.mean_error_norm, ins[:2], ins[2]), amount, "GB/s", what)
+        if workload == "add_norm":
+            def run():
+                leaves = [t.detach().clone().requires_grad_(True) for t in (ins[0], ins[2], ins[1])]
+                h, y = oracle.add_mean_error_norm(*leaves)
+                torch.autograd.backward([h, y], [ins[4], ins[3]])
+            return (run, amount, "GB/s", what)
+        return (lambda: oracle.autograd_grads(oracle.rational_softmax, ins[:1], ins[1]), amount, "GB/s", what)
+    if workload == "loss_head":
+        cfg = FUSED[workload]
+        logits, labels = fused_inputs(workload, torch.Generator().manual_seed(1234 + 2), rows=8 * 128)
+        logits = logits.float()
+
+        def run():
+            x = logits.detach().clone().requires_grad_(True)
+            oracle.shifted_cross_entropy(x, labels).backward()
+        return (run, cfg["bytes"] / 8 / 1e9, "GB/s", "8 sequences of 128 of the 1024 positions, float32")
+    if workload in LM:
+        from fastalgebraictransformer_b200 import AlgebraicTransformerLM
+        cfg = LM[workload]
+        seq = cfg["seq"] if workload == "lm_small" else 512
+        torch.manual_seed(1234 + 3)
+        model = AlgebraicTransformerLM(cfg["vocab_size"], cfg["d_model"], cfg["n_head"], cfg["n_layers"], d_ffn=cfg["d_ffn"],
+                                       block_size=cfg["seq"], dropout=0.0)
+        state = {k: v.detach().float() for k, v in model.state_dict().items()}
+        g = torch.Generator().manual_seed(1234 + 3)
+        ids = torch.randint(0, cfg["vocab_size"], (1, seq), generator=g)
+        lab = torch.randint(0, cfg["vocab_size"], (1, seq), generator=g)
+        what = (f"1 sequence of {seq} tokens (of the {cfg['batch']} x {cfg['seq']} per GPU): forward, loss and backward in float32, "
+                "no optimizer step" + ("" if seq == cfg["seq"] else "; REDUCED sequence length: the full one needs ~25 GB of S x S temporaries"))
+        return (lambda: oracle.lm_loss_and_grads(state, ids, lab, cfg["n_head"]), float(seq), "tokens/s", what)
+    raise SystemExit(f"no CPU sample for workload {workload}")
 
 
-def cpu_baseline_attn():
-    use_all_host_threads()
-    heads = 2
-    sec, flops = cpu_attention_sample(heads, repeats=1)           # warm-up / sizing pass
+REF_METRIC = {"attn": "rational_attention_fwd_bwd_tflops", "lm_small": "lm_train_tokens_per_s", "lm_xl": "lm_train_tokens_per_s"}
+
+
+def cpu_baseline(workload: str, budget_s: float = 10.0, max_passes: int = 8):
+    """The oracle on all host threads on a bounded sample of the workload: mean over passes worth ~budget_s."""
+    cores = use_all_host_threads()
+    run, amount, unit, what = cpu_sample(workload)
+    run()                                                            # warm-up / sizing pass
     total, n = 0.0, 0
-    while total < 10.0 and n < 8:
-        s, _ = cpu_attention_sample(heads)
-        total += s; n += 1
+    while total < budget_s and n < max_passes:
+        t0 = time.perf_counter()
+        run()
+        total += time.perf_counter() - t0; n += 1
     sec = total / n
-    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"oracle (PyTorch fp32, autograd) on {heads} of the 128 (batch, head) units, S=4096 D=128, "
-                      f"mean of {n} passes of {sec:.2f} s; flops counted with the same causal convention"}
+    return {"value": amount / sec, "unit": unit, "cores": cores, "kind": "port",
+            "sample": f"oracle (plain PyTorch on the CPU, float32) on {what}; mean of {n} passes of {sec:.2f} s"}
 
 
 def run_reference(args, rank, world):
+    """The reference arm: the CPU restatement of the reference's PyTorch path, timed step by step on rank 0."""
     if rank != 0:
         return None
-    if args.workload != "attn":
-        return {"impl": "reference", "unavailable": "the CPU arm is implemented for the attention workload only"}
-    use_all_host_threads()
-    heads = 1
-    cpu_attention_sample(heads)                                    # untimed
+    cores = use_all_host_threads()
+    run, amount, unit, what = cpu_sample(args.workload)
+    run()                                                            # untimed
     for _ in range(max(0, args.warmup - 1)):
-        cpu_attention_sample(heads)
+        run()
     times = []
-    flops = 0.0
     for _ in range(args.steps):
-        s, flops = cpu_attention_sample(heads)
-        times.append(s)
+        t0 = time.perf_counter()
+        run()
+        times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
-    val = flops / sec / 1e12
-    base = {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"each step = 1 of the 128 (batch, head) units (S=4096, D=128), oracle in float32 with autograd"}
+    val = amount / sec
+    base = {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": f"each step = {what}"}
+    metric = REF_METRIC.get(args.workload, f"rational_{args.workload}_fwd_bwd_gbs")
     return {
-        "impl": "reference", "metric": "rational_attention_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s",
+        "impl": "reference", "metric": metric, "value": val, "unit": unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "rational_attention fwd+bwd causal ALiBi B=8 H=16 S=4096 D=128 (headline configuration); "
-                               "CPU restatement of the reference's PyTorch path on a bounded sample"},
+        "higher_is_better": True, "scaling": "strong" if args.workload == "attn" else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: CPU restatement of the reference's PyTorch path on a bounded sample "
+                               f"of the configuration the GPU arm runs ({what})"},
         "cpu_baseline": base,
-        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
 
@@ -569,7 +731,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "add_norm", "loss_head", "lm_small", "lm_xl"])
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="attn workload on N > 1 ranks: split the 128 (batch, head) units over the ranks (strong, default) "
+                         "or give every rank all of them (weak)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="attn workload: leave out the LM / bandwidth-sweep records")
     ap.add_argument("--batch", type=int, default=0,
                     help="attn workload: override the batch size (profiling captures use a smaller case)")
     ap.add_argument("--no-graph", action="store_true", help="LM workloads: time eager launches instead of a CUDA graph")
@@ -587,9 +753,10 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU implementation of the product path)")
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    extras = args.workload == "attn" and not args.no_extras and not args.batch
     if world > 1:
         import torch.distributed as dist
-        if args.workload in LM and not args.no_graph:
+        if (args.workload in LM and not args.no_graph) or extras:
             # the DDP step is captured in a CUDA graph: the watchdog must not poll work objects captured there
             os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")
         dist.init_process_group("nccl", device_id=device)
@@ -598,19 +765,24 @@ def main():
 
     if args.workload == "attn":
         res = bench_attn(args, rank, world, device)
+        if extras:
+            res["extra"] = run_extras(args, rank, world, device)
     elif args.workload in FUSED:
-        res = bench_fused(args, rank, world, device, args.workload)
+        res = run_fused(args.workload, args.steps, args.warmup, rank, world, device)
     else:
-        res = bench_lm(args, rank, world, device, args.workload)
+        res = run_lm(args.workload, args.steps, args.warmup, rank, world, device, graph=not args.no_graph,
+                     eager_steps=0 if args.no_graph else max(3, args.steps // 2))
 
     if rank == 0:
         line = {"metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": res["dtype"],
+                "higher_is_better": True, "scaling": res["scaling"], "vs_baseline": None, "dtype": res["dtype"],
                 "data": "synthetic", "config": res["config"], "e2e": res["e2e"], "gpu_launches": res["gpu_launches"],
-                "roofline": res["roofline"], "clocks": res["clocks"]}
-        if world == 1 and not args.no_cpu_baseline and args.workload == "attn":
-            line["cpu_baseline"] = cpu_baseline_attn()
+                "gpu_launches_how": res["gpu_launches_how"], "roofline": res["roofline"], "clocks": res["clocks"]}
+        if "extra" in res:
+            line["extra"] = res["extra"]
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args.workload)
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist

@@ -29,6 +29,7 @@ PROTOTYPES = {
     "fat_version": (_int, []),
     "fat_error_string": (C.c_char_p, [_int]),
     "fat_last_error": (C.c_char_p, []),
+    "fat_launch_count": (C.c_ulonglong, []),
     "fat_swiglu_fwd": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "fat_swiglu_bwd": (_int, [_ptr] * 5 + [_i64] * 7 + [_int, _ptr]),
     "fat_norm_fwd": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _dbl, _int, _ptr]),

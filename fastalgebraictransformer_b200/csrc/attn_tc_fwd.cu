@@ -31,13 +31,20 @@ namespace {
 using namespace tc;
 using namespace tcattn;
 
-constexpr int kStages = 2;
+constexpr int kStages = 2;                            // K tiles in flight
+#ifndef FAT_FWD_VSTAGES
+#define FAT_FWD_VSTAGES 3
+#endif
+constexpr int kVStages = FAT_FWD_VSTAGES;             // V tiles in flight (a V tile is loaded, converted, then read by two MMAs)
+#ifndef FAT_FWD_CVT_WARPS
+#define FAT_FWD_CVT_WARPS 2
+#endif
 #ifndef FAT_FWD_SPLIT
 #define FAT_FWD_SPLIT 1
 #endif
 constexpr int kSplit = FAT_FWD_SPLIT;                 // softmax warpgroups per query tile (each takes 128/kSplit score columns)
 constexpr int kEwWarps = 8 * kSplit;                  // softmax warps; then one TMA warp, one MMA warp and two helper warps
-constexpr int kCvtWarps = 2;
+constexpr int kCvtWarps = FAT_FWD_CVT_WARPS;
 constexpr int kFwdThreads = 32 * kEwWarps + 64 + 32 * kCvtWarps;
 constexpr float kPUnit = 4096.0f;                     // P_stored = kPUnit sigma^4 = (4 (1 + s r))^4
 constexpr int kStatusF16Range = 0x20000000;
@@ -49,9 +56,9 @@ struct FwdSmem {
   static constexpr int kTileBytes = BLK * D * 2;          // one [128][D] 16-bit tile
   alignas(1024) unsigned char q[2][kTileBytes];           // reused as output staging in the epilogue
   alignas(1024) unsigned char k[kStages][kTileBytes];
-  alignas(1024) unsigned char v[kStages][kTileBytes];
-  uint64_t q_full[2], k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-  uint64_t v_ready[kStages];                              // helper warps: the V tile of this stage is float16 now
+  alignas(1024) unsigned char v[kVStages][kTileBytes];
+  uint64_t q_full[2], k_full[kStages], k_empty[kStages], v_full[kVStages], v_empty[kVStages];
+  uint64_t v_ready[kVStages];                              // helper warps: the V tile of this stage is float16 now
   uint64_t s_full[2], p_full[2], o_full[2];
   float l_part[2][kSplit][BLK];                           // row sums of each warpgroup's column share
   uint32_t tmem_base;
@@ -111,6 +118,28 @@ __device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int r, f32x2
   }
 }
 
+// bfloat16 -> float16 in place over `BYTES` bytes of a shared-memory tile, by the 32 lanes of one warp.  CHECK: returns
+// non-zero when a magnitude was 65536 or more (or not a number); such values are clamped to 65504.
+template <int BYTES, bool CHECK>
+__device__ __forceinline__ uint32_t convert_v(unsigned char* base, int lane) {
+  uint32_t flag = 0;
+#pragma unroll 4
+  for (int off = lane * 16; off < BYTES; off += 32 * 16) {
+    uint4 v = *reinterpret_cast<uint4*>(base + off);
+    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t x = w[i];
+      if (CHECK) flag |= ((x & 0x7fff7fffu) + 0x38803880u) & 0x80008000u;          // either half >= 0x4780 (65536.0)
+      uint32_t y;
+      asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(__uint_as_float(x & 0xffff0000u)), "f"(__uint_as_float(x << 16)));
+      w[i] = y;
+    }
+    *reinterpret_cast<uint4*>(base + off) = v;
+  }
+  return flag;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
@@ -137,9 +166,9 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.q_full[i], 1); mbar_init(&sm.s_full[i], 1); mbar_init(&sm.p_full[i], BLK * kSplit); mbar_init(&sm.o_full[i], 1);
     }
-    for (int i = 0; i < kStages; ++i) {
-      mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1);
-      mbar_init(&sm.v_ready[i], 32 * kCvtWarps);
+    for (int i = 0; i < kStages; ++i) { mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); }
+    for (int i = 0; i < kVStages; ++i) {
+      mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1); mbar_init(&sm.v_ready[i], 32 * kCvtWarps);
     }
     mbar_fence_init();
   }
@@ -156,12 +185,11 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       for (int t = 0; t < 2; ++t)
         if (n_tiles[t] > 0) load_tile_tma<D>(sm.q[t], &maps.q, &sm.q_full[t], (2 * qb + t) * BLK, h, b);
       for (int j = 0; j < n_max; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
-        if (!g.wait(&sm.k_empty[st], ph ^ 1, 10)) break;
+        const int st = j % kStages, vst = j % kVStages;
+        if (!g.wait(&sm.k_empty[st], ((j / kStages) & 1) ^ 1, 10)) break;
         load_tile_tma<D>(sm.k[st], &maps.k, &sm.k_full[st], j * BLK, h, b);
-        if (!g.wait(&sm.v_empty[st], ph ^ 1, 11)) break;
-        load_tile_tma<D>(sm.v[st], &maps.v, &sm.v_full[st], j * BLK, h, b);
+        if (!g.wait(&sm.v_empty[vst], ((j / kVStages) & 1) ^ 1, 11)) break;
+        load_tile_tma<D>(sm.v[vst], &maps.v, &sm.v_full[vst], j * BLK, h, b);
       }
     }
   } else if (warp == kEwWarps + 1) {
@@ -171,7 +199,9 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       constexpr uint32_t idesc_pv = idesc_f16(BLK, D, Pack16<__half>::kFmt, 0, 1);      // P and V are float16
       const uint64_t qd[2] = {desc_kmajor(sm.q[0]), desc_kmajor(sm.q[1])};
       const uint64_t kd[kStages] = {desc_kmajor(sm.k[0]), desc_kmajor(sm.k[1])};
-      const uint64_t vd[kStages] = {desc_mnmajor(sm.v[0]), desc_mnmajor(sm.v[1])};
+      uint64_t vd[kVStages];
+#pragma unroll
+      for (int i = 0; i < kVStages; ++i) vd[i] = desc_mnmajor(sm.v[i]);
       auto issue_qk = [&](int t, int st) { issue_gemm_nt<D>(tmem + t * BLK, qd[t], kd[st], idesc_qk); };          // S_t = Q_t K^T
       auto issue_pv = [&](int t, int st, bool first) {                                                           // O_t += P_t V
         issue_gemm_tn<kColsPerWg>(tmem + 2 * BLK + t * D, tmem + t * BLK, vd[st], idesc_pv, !first);
@@ -189,15 +219,15 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       }
       if (ok && n_max > 0) mma_commit(&sm.k_empty[0]);
       for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j % kStages, st1 = (j + 1) % kStages;
-        const uint32_t ph = (j / kStages) & 1, ph1 = ((j + 1) / kStages) & 1;
+        const int st1 = (j + 1) % kStages, vst = j % kVStages;
+        const uint32_t ph1 = ((j + 1) / kStages) & 1, vph = (j / kVStages) & 1;
         bool k_next_ready = false;
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_tiles[t]) continue;
           if (!(ok = g.wait(&sm.p_full[t], j & 1, 22))) break;
-          if (!(ok = g.wait(kConvertV ? &sm.v_ready[st] : &sm.v_full[st], ph, 23))) break;
+          if (!(ok = g.wait(kConvertV ? &sm.v_ready[vst] : &sm.v_full[vst], vph, 23))) break;
           tc_fence_after();
-          issue_pv(t, st, j == 0);
+          issue_pv(t, vst, j == 0);
           if (j + 1 < n_tiles[t]) {
             if (!k_next_ready) { if (!(ok = g.wait(&sm.k_full[st1], ph1, 24))) break; k_next_ready = true; tc_fence_after(); }
             issue_qk(t, st1);
@@ -207,7 +237,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
           }
         }
         if (!ok) break;
-        mma_commit(&sm.v_empty[st]);                       // V(j) and, if it was read, K(j+1) are free once these finish
+        mma_commit(&sm.v_empty[vst]);                      // V(j) and, if it was read, K(j+1) are free once these finish
         if (j + 1 < n_max) mma_commit(&sm.k_empty[st1]);
       }
     }
@@ -220,25 +250,11 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       constexpr int kPartBytes = S::kTileBytes / kCvtWarps;
       uint32_t out_of_range = 0;
       for (int j = 0; j < n_max; ++j) {
-        const int st = j % kStages;
-        if (!g.wait(&sm.v_full[st], (j / kStages) & 1, 40)) break;
+        const int st = j % kVStages;
+        if (!g.wait(&sm.v_full[st], (j / kVStages) & 1, 40)) break;
         unsigned char* base = sm.v[st] + part * kPartBytes;
-        uint32_t flag = 0;
-#pragma unroll 4
-        for (int off = lane * 16; off < kPartBytes; off += 32 * 16) {
-          uint4 v = *reinterpret_cast<uint4*>(base + off);
-          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint32_t x = w[i];
-            flag |= ((x & 0x7fff7fffu) + 0x38803880u) & 0x80008000u;          // either half >= 0x4780 (65536.0)
-            uint32_t y;
-            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(__uint_as_float(x & 0xffff0000u)), "f"(__uint_as_float(x << 16)));
-            w[i] = y;
-          }
-          *reinterpret_cast<uint4*>(base + off) = v;
-        }
-        if (j / 2 == qb) out_of_range |= flag;
+        if (j / 2 == qb) out_of_range |= convert_v<kPartBytes, true>(base, lane);
+        else             convert_v<kPartBytes, false>(base, lane);
         fence_async_smem();
         mbar_arrive(&sm.v_ready[st]);
       }

@@ -1,4 +1,5 @@
 // The C ABI: argument validation, path selection and error reporting around the kernels.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -16,9 +17,12 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+
+// Called exactly once after every kernel launch of this library.
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
-  if (e == cudaSuccess) return FAT_OK;
+  if (e == cudaSuccess) { g_launches.fetch_add(1, std::memory_order_relaxed); return FAT_OK; }
   set_error("%s: %s", what, cudaGetErrorString(e));
   return FAT_ERR_LAUNCH;
 }
@@ -68,6 +72,8 @@ extern "C" {
 int fat_version(void) { return 100; }
 
 const char* fat_last_error(void) { return g_err; }
+
+unsigned long long fat_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* fat_error_string(int code) {
   switch (code) {

@@ -69,6 +69,10 @@ enum fat_device_status { FAT_DEV_OK = 0, FAT_DEV_WAIT_TIMEOUT = 1, FAT_DEV_F16_R
 FAT_API int fat_version(void);
 FAT_API const char* fat_error_string(int code);
 FAT_API const char* fat_last_error(void);   /* thread-local detail of the last non-zero return */
+/* Number of kernels this library has launched in this process so far (every entry point counts each of its
+ * launches; launches recorded into a CUDA graph count once, at capture).  A diagnostic with no counterpart
+ * in the reference: benchmarks use it to state how many of this library's kernels ran in a timed region. */
+FAT_API unsigned long long fat_launch_count(void);
 
 /* ------------------------------------------------------------------------------------
  * Rational SwiGLU.  out = gate * sigma(gate) * value, sigma(x) = (x/(|x|+1)+1)/2.
