@@ -21,7 +21,8 @@ from torch.utils.checkpoint import checkpoint
 
 from .backward import RationalAttentionPackedFunction
 from .forward import compute_alibi_slopes
-from .fused_ops import EPS, RationalSwiGLUPacked, add_mean_error_norm, mean_error_norm, shifted_cross_entropy
+from .fused_ops import (EPS, RationalSwiGLUPacked, add_mean_error_norm, head_shifted_cross_entropy, mean_error_norm,
+                        shifted_cross_entropy)
 
 
 class RationalMR(nn.Module):
@@ -137,7 +138,11 @@ class AlgebraicTransformerLM(nn.Module):
             nn.init.normal_(module.weight, mean=0.0, std=0.02)
 
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
-                attention_mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                attention_mask: Optional[torch.Tensor] = None,
+                return_logits: bool = True) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        """(logits, loss) as the reference returns them (algebraic_model.py:209-237).  ``return_logits=False`` (an
+        extension; needs ``labels``) is for training loops that only use the loss: the head GEMM and the loss then run one
+        sequence at a time and neither the [B, T, V] logits nor their gradient are ever materialised; ``logits`` is None."""
         x = self.embed(input_ids)
         if self.gradient_checkpointing and self.training:
             for block in self.blocks:
@@ -152,6 +157,11 @@ class AlgebraicTransformerLM(nn.Module):
                 y = self.norm(x)
             else:
                 _, y = add_mean_error_norm(x, pending, self.norm.weight, self.norm.eps)
+        if not return_logits:
+            if labels is None:
+                raise ValueError("return_logits=False needs labels (there would be nothing to return)")
+            if y.dim() == 3 and y.dtype in (torch.float32, torch.bfloat16, torch.float16):
+                return None, head_shifted_cross_entropy(y, self.head.weight, labels, -100)
         logits = self.head(y)
         loss = None
         if labels is not None:
@@ -163,7 +173,7 @@ class AlgebraicTransformerLM(nn.Module):
                 shift_labels = labels[..., 1:].contiguous()
                 loss = F.cross_entropy(shift_logits.view(-1, shift_logits.size(-1)), shift_labels.view(-1),
                                        ignore_index=-100)
-        return logits, loss
+        return (logits if return_logits else None), loss
 
     @torch.no_grad()
     def generate(self, idx: torch.Tensor, max_new_tokens: int, temperature: float = 1.0,

@@ -27,6 +27,26 @@ int check_launch(const char* what) {
   return FAT_ERR_LAUNCH;
 }
 
+int num_sms() {
+  constexpr int kMaxDev = 64;
+  static std::atomic<int> cached[kMaxDev];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n <= 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+// The tensor-core attention kernels cover 16-bit tensors, head sizes 64 and 128, causal masking, and pointers /
+// strides that TMA can address (16-byte aligned, strides multiples of 8 elements).
+bool attn_tc_eligible(int T, int D, int dtype, bool aligned, bool causal, bool backward) {
+  (void)backward;
+  return T >= 1 && (D == 64 || D == 128) && (dtype == FAT_BF16 || dtype == FAT_F16) && aligned && causal;
+}
+
 namespace {
 
 bool strides_aligned(const int64_t* s, int w) { return s[0] % w == 0 && s[1] % w == 0 && s[2] % w == 0; }

@@ -11,7 +11,9 @@
 
 namespace fat {
 
-constexpr int kNumSM = 148;   // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+// Streaming multiprocessors of the current device (cudaDevAttrMultiProcessorCount, cached per device; 148 on a
+// B200: 2 dies x 74).  Grids of the grid-stride kernels are sized in multiples of it.
+int num_sms();
 
 // ---------------------------------------------------------------- host-side errors
 void set_error(const char* fmt, ...);          // defined in cabi.cu (thread-local buffer)

@@ -30,7 +30,8 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxVPT = 8;
-constexpr int kNormBwdMaxBlocks = 4 * kNumSM;   // rows of the d_weight partial-sum scratch
+// rows of the d_weight partial-sum scratch: one per block of the norm backward, whose grid never exceeds this
+inline int norm_bwd_max_blocks() { return FAT_NORM_BWD_BPS * num_sms(); }
 
 // Scratch of fat_norm_bwd_static: a fixed array inside the library image.  Every GPU that loads
 // the library holds these 16 MiB until the process exits; all calls on a device share them.
@@ -532,9 +533,9 @@ RowPlan plan_rows(int64_t n_rows, int64_t n_cols, std::initializer_list<const vo
     p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
     const int rpc = threads / G;
     const int64_t blocks = (n_rows + rpc - 1) / rpc;
-    p.grid = int(blocks < int64_t(blocks_per_sm) * kNumSM ? blocks : int64_t(blocks_per_sm) * kNumSM);
+    p.grid = int(blocks < int64_t(blocks_per_sm) * num_sms() ? blocks : int64_t(blocks_per_sm) * num_sms());
   } else {
-    p.grid = int(n_rows < int64_t(blocks_per_sm) * kNumSM ? n_rows : int64_t(blocks_per_sm) * kNumSM);
+    p.grid = int(n_rows < int64_t(blocks_per_sm) * num_sms() ? n_rows : int64_t(blocks_per_sm) * num_sms());
   }
   if (p.grid < 1) p.grid = 1;
   return p;
@@ -557,7 +558,7 @@ int swiglu_fwd_t(const void* gate, const void* value, void* out, int64_t n_rows,
                    gs % W == 0 && vs % W == 0 && os % W == 0;
   const int64_t ppr = vec ? n_cols / W : n_cols;
   int64_t gx = (ppr + kThreads - 1) / kThreads;
-  const int64_t cap = FAT_SWIGLU_BPS * kNumSM;
+  const int64_t cap = int64_t(FAT_SWIGLU_BPS) * num_sms();
   if (gx > cap) gx = cap;
   int64_t gy = n_rows < (cap + gx - 1) / gx ? n_rows : (cap + gx - 1) / gx;
   dim3 grid((unsigned)gx, (unsigned)gy);
@@ -578,7 +579,7 @@ int swiglu_bwd_t(const void* d_out, const void* gate, const void* value, void* d
                    n_cols % W == 0 && dos % W == 0 && gs % W == 0 && vs % W == 0 && dgs % W == 0 && dvs % W == 0;
   const int64_t ppr = vec ? n_cols / W : n_cols;
   int64_t gx = (ppr + kThreads - 1) / kThreads;
-  const int64_t cap = FAT_SWIGLU_BPS * kNumSM;
+  const int64_t cap = int64_t(FAT_SWIGLU_BPS) * num_sms();
   if (gx > cap) gx = cap;
   int64_t gy = n_rows < (cap + gx - 1) / gx ? n_rows : (cap + gx - 1) / gx;
   dim3 grid((unsigned)gx, (unsigned)gy);
@@ -601,7 +602,7 @@ add_rows_kernel(const T* a, const T* b, T* out, int64_t n_rows, int64_t n_cols, 
 template <typename T>
 int add_rows_t(const void* a, const void* b, void* out, int64_t n_rows, int64_t n_cols, int64_t as, int64_t bs, int64_t os,
                cudaStream_t st) {
-  const int64_t cap = 32 * kNumSM;
+  const int64_t cap = 32 * int64_t(num_sms());
   add_rows_kernel<T><<<unsigned(n_rows < cap ? n_rows : cap), kThreads, 0, st>>>((const T*)a, (const T*)b, (T*)out, n_rows,
                                                                                 n_cols, as, bs, os);
   return check_launch("add_rows");
@@ -647,7 +648,7 @@ int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mea
   const bool wide = n_cols / W > kThreads;
   const int threads = wide ? kWide : kThreads;
   RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, w, d_x, d_add}, {dos, xs, dxs, das}, FAT_NORM_BWD_BPS, FAT_NORM_BWD_PPT, threads);
-  if (p.grid > kNormBwdMaxBlocks) p.grid = kNormBwdMaxBlocks;
+  if (p.grid > norm_bwd_max_blocks()) p.grid = norm_bwd_max_blocks();
   if (size_t(p.grid) * size_t(n_cols) * sizeof(C) > ws_bytes) {
     set_error("norm_bwd: workspace of %zu bytes is smaller than the %zu needed", ws_bytes,
               size_t(p.grid) * size_t(n_cols) * sizeof(C));
@@ -818,7 +819,7 @@ int fat_add_norm_bwd(const void* d_y, const void* d_h, const void* h, const void
 size_t fat_norm_bwd_workspace_bytes(int64_t n_rows, int64_t n_cols, int dtype) {
   (void)n_rows;
   if (n_cols <= 0) return 0;
-  return size_t(kNormBwdMaxBlocks) * size_t(n_cols) * (dtype == FAT_F64 ? 8 : 4);
+  return size_t(norm_bwd_max_blocks()) * size_t(n_cols) * (dtype == FAT_F64 ? 8 : 4);
 }
 
 int fat_norm_bwd(const void* d_out, const void* x, const void* weight, const float* mean, void* d_x, void* d_weight,

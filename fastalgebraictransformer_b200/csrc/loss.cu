@@ -59,11 +59,12 @@ shifted_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labe
   for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
     const int b = row / Tn, t = row - b * Tn;
     const T* x = logits + b * ls_b + t * ls_t;
-    T* dx = d_logits + int64_t(row) * V;
+    T* dx = d_logits ? d_logits + int64_t(row) * V : nullptr;     // null: the caller wants the loss only
     const int64_t target = t + 1 < Tn ? labels[b * lab_b + (t + 1) * lab_t] : ignore_index;
     const bool valid = target != ignore_index && target >= 0 && target < V;
     if (!valid) {                                  // uniform over the block
-      if (CACHED) {
+      if (!dx) {
+      } else if (CACHED) {
         for (int pk = tid; pk < npk; pk += kCeThreads) reinterpret_cast<uint4*>(dx)[pk] = make_uint4(0u, 0u, 0u, 0u);
       } else {
         for (int c = tid; c < V; c += kCeThreads) dx[c] = Elem<T>::from_c(0.f);
@@ -71,6 +72,9 @@ shifted_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labe
       if (tid == 0) row_loss[row] = 0.f;
       continue;
     }
+    // d_logits may be the logits buffer itself (every element is read before the same thread overwrites it), so the
+    // target's logit is fetched before anything is written
+    const float x_target = tid == 0 ? Elem<T>::to_c(x[int(target)]) : 0.f;
     uint4 raw[kCePacks];
     float m = -INFINITY;
     if (CACHED) {
@@ -105,7 +109,8 @@ shifted_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labe
     s = block_reduce<kCeThreads>(s, buf, false);
     const float inv = scale / s;                   // softmax normaliser and 1/n_valid in one factor
     const int tgt = int(target);
-    if (CACHED) {
+    if (!dx) {
+    } else if (CACHED) {
 #pragma unroll
       for (int i = 0; i < kCePacks; ++i) {
         const int pk = tid + i * kCeThreads;
@@ -127,7 +132,7 @@ shifted_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labe
         dx[c] = Elem<T>::from_c(o);
       }
     }
-    if (tid == 0) row_loss[row] = m + logf(s) - Elem<T>::to_c(x[tgt]);
+    if (tid == 0) row_loss[row] = m + logf(s) - x_target;
   }
 }
 
@@ -147,9 +152,9 @@ int shifted_ce_t(const void* logits, const int64_t* labels, const float* n_valid
                  cudaStream_t st) {
   constexpr int W = 16 / sizeof(T);
   const bool aligned = V % W == 0 && ls_b % W == 0 && ls_t % W == 0 && reinterpret_cast<uintptr_t>(logits) % 16 == 0 &&
-                       reinterpret_cast<uintptr_t>(d_logits) % 16 == 0;
+                       reinterpret_cast<uintptr_t>(d_logits) % 16 == 0;      // (a null d_logits counts as aligned)
   const int64_t rows = int64_t(B) * Tn;
-  const unsigned grid = unsigned(rows < 64 * kNumSM ? rows : 64 * kNumSM);
+  const unsigned grid = unsigned(rows < 64 * int64_t(num_sms()) ? rows : 64 * int64_t(num_sms()));
   auto go = [&](auto kern, int threads) {
     kern<<<grid, threads, 0, st>>>((const T*)logits, labels, n_valid, row_loss, (T*)d_logits, B, Tn, V, ls_b, ls_t, lab_b, lab_t,
                                    ignore_index);
@@ -163,7 +168,7 @@ int shifted_ce_t(const void* logits, const int64_t* labels, const float* n_valid
 template <typename T>
 int scale_t(void* x, int64_t n, const float* s, cudaStream_t st) {
   const int64_t blocks = (n + 255) / 256;
-  scale_unless_one_kernel<T><<<unsigned(blocks < 16 * kNumSM ? blocks : 16 * kNumSM), 256, 0, st>>>((T*)x, n, s);
+  scale_unless_one_kernel<T><<<unsigned(blocks < 16 * int64_t(num_sms()) ? blocks : 16 * int64_t(num_sms())), 256, 0, st>>>((T*)x, n, s);
   return check_launch("scale_unless_one");
 }
 
@@ -183,7 +188,7 @@ int fat_shifted_ce_fwd(const void* logits, const int64_t* labels, const float* n
     return FAT_ERR_SHAPE;
   }
   if (B == 0 || T == 0) return FAT_OK;
-  if (!logits || !labels || !n_valid || !row_loss || !d_logits) { set_error("shifted_ce_fwd: null pointer"); return FAT_ERR_NULL; }
+  if (!logits || !labels || !n_valid || !row_loss) { set_error("shifted_ce_fwd: null pointer"); return FAT_ERR_NULL; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case FAT_F32: return shifted_ce_t<float>(logits, labels, n_valid, row_loss, d_logits, B, T, V, logits_batch_stride,

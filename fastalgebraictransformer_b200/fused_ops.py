@@ -126,8 +126,49 @@ class ShiftedCrossEntropy(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_loss):
         (d_logits,) = ctx.saved_tensors
+        if getattr(ctx, "consumed", False):
+            # the gradient is scaled in place to avoid a second [B, T, V] tensor; a second pass over the same graph
+            # (retain_graph=True) would scale it twice
+            raise RuntimeError("ShiftedCrossEntropy: backward through the same forward twice is not supported "
+                               "(its saved gradient is scaled in place); run the forward again")
+        ctx.consumed = True
         _alg.scale_unless_one(d_logits, grad_loss.to(torch.float32).reshape(1))
         return d_logits, None, None
+
+
+class HeadShiftedCrossEntropy(torch.autograd.Function):
+    """Loss of the language-model head, ``cross_entropy((y @ weight^T)[:, :-1], labels[:, 1:])`` (reference
+    algebraic_model.py:225-235), for callers that do not keep the logits: the [B, T, V] tensor and its gradient never
+    exist, only one sequence's [T, V] slice at a time.  The gradients with respect to ``y`` and ``weight`` are formed in
+    the forward (they need the same slices) and scaled by the incoming scalar in the backward."""
+
+    @staticmethod
+    def forward(ctx, y: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+        assert y.is_cuda, "Input must be on CUDA"
+        want = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        loss, d_y, d_w = ops.head_shifted_ce(y, weight, labels, ignore_index, want_grads=want)
+        if want:
+            ctx.save_for_backward(d_y, d_w)
+        return loss.to(y.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_loss):
+        d_y, d_w = ctx.saved_tensors
+        if getattr(ctx, "consumed", False):
+            raise RuntimeError("HeadShiftedCrossEntropy: backward through the same forward twice is not supported "
+                               "(its saved gradients are scaled in place); run the forward again")
+        ctx.consumed = True
+        scale = grad_loss.to(torch.float32).reshape(1)
+        _alg.scale_unless_one(d_y, scale)
+        _alg.scale_unless_one(d_w, scale)
+        return d_y, d_w, None, None
+
+
+def head_shifted_cross_entropy(y: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                               ignore_index: int = -100) -> torch.Tensor:
+    """Next-token loss of ``y @ weight^T`` against ``labels`` without materialising the logits."""
+    _require_cuda(y, "head_shifted_cross_entropy")
+    return HeadShiftedCrossEntropy.apply(y, weight, labels, ignore_index)
 
 
 def shifted_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:

@@ -208,6 +208,47 @@ def _shifted_ce_fwd(logits: Tensor, labels: Tensor, ignore_index: int) -> Tuple[
     return loss, d_logits
 
 
+def head_shifted_ce(y: Tensor, weight: Tensor, labels: Tensor, ignore_index: int,
+                    want_grads: bool = True) -> Tuple[Tensor, Optional[Tensor], Optional[Tensor]]:
+    """Loss head without the [B, T, V] logits: (loss, d_y, d_weight) of the mean cross-entropy between
+    (y @ weight^T)[:, :-1] and labels[:, 1:] (reference algebraic_model.py:225-235).
+
+    The logits exist one sequence at a time: a [T, V] buffer is filled by the head GEMM, the loss kernel turns it in
+    place into its own gradient, and two more GEMMs fold that gradient into d_y [B, T, C] and d_weight [V, C] before the
+    buffer is reused for the next sequence.  With ``want_grads=False`` only the loss is computed."""
+    _cuda_check(y, weight, labels)
+    assert y.dim() == 3 and weight.dim() == 2 and y.shape[2] == weight.shape[1] and labels.shape == y.shape[:2]
+    assert labels.dtype == torch.int64 and y.dtype == weight.dtype
+    B, T, C = y.shape
+    V = weight.shape[0]
+    y = y.contiguous()
+    counted = labels[:, 1:]
+    n_valid = ((counted != ignore_index) & (counted >= 0) & (counted < V)).sum().to(torch.float32).reshape(1)
+    row_loss = torch.zeros(B * T, dtype=torch.float32, device=y.device)
+    d_y = torch.empty_like(y) if want_grads else None
+    d_w = torch.empty_like(weight) if want_grads else None
+    if y.numel() and V:
+        buf = torch.empty((T, V), dtype=y.dtype, device=y.device)
+        lib, tag, wt = _lib.lib(), _lib.dtype_tag(y), weight.t()
+        with _lib.device_guard(y.device):
+            for b in range(B):
+                torch.mm(y[b], wt, out=buf)
+                _lib.check(lib.fat_shifted_ce_fwd(_p(buf), _p(labels[b]), _p(n_valid), _p(row_loss[b * T:]),
+                                                  _p(buf) if want_grads else None, 1, T, V, T * V, V,
+                                                  labels.stride(0), labels.stride(1), ignore_index, tag,
+                                                  _lib.stream_ptr(y.device)))
+                if want_grads:
+                    torch.mm(buf, weight, out=d_y[b])
+                    if b == 0:
+                        torch.mm(buf.t(), y[b], out=d_w)
+                    else:
+                        d_w.addmm_(buf.t(), y[b])
+    elif want_grads:
+        d_w.zero_()
+    loss = row_loss.sum() / n_valid.clamp_min(1.0).squeeze(0)
+    return loss, d_y, d_w
+
+
 def _scale_unless_one(x: Tensor, scale: Tensor) -> None:
     _cuda_check(x, scale)
     assert x.is_contiguous() and scale.dtype == torch.float32 and scale.numel() == 1

@@ -101,7 +101,8 @@ FAT_API int fat_swiglu_bwd(const void* d_out, const void* gate, const void* valu
  * logits [B, T, V] (unit stride along V), labels [B, T] int64.  Row (b, t) is scored against labels[b, t+1]; the
  * last position of every sequence and targets equal to ignore_index (or outside [0, V)) contribute nothing.
  *   row_loss [B*T] float32: the row's -log softmax(logits)[target], 0 for rows that do not count;
- *   d_logits [B*T, V] (dtype of logits, dense): (softmax - onehot) / n_valid[0], 0 for rows that do not count;
+ *   d_logits [B*T, V] (dtype of logits, dense): (softmax - onehot) / n_valid[0], 0 for rows that do not count; may be
+ *            null (loss only) and may be the logits buffer itself when that is dense (the gradient replaces the logits);
  *   n_valid: device pointer to the number of rows that count, as float32 (the caller counts the labels).
  * loss = sum(row_loss) / n_valid.  fat_scale_unless_one multiplies d_logits by the scalar gradient that reaches the
  * loss and returns without touching memory when that scalar is exactly 1.  dtypes: F32, BF16, F16.
@@ -162,11 +163,15 @@ FAT_API int fat_add_norm_bwd(const void* d_y, const void* d_h, const void* h, co
  * calls no allocator of any kind.
  *
  *  - Limit: fat_norm_bwd_workspace_bytes(n_rows, n_cols, dtype) must not exceed
- *    fat_norm_bwd_static_capacity() (16 MiB: up to 7084 columns for F32/BF16/F16, 3542 for
- *    F64); larger requests return FAT_ERR_WORKSPACE and launch nothing.
+ *    fat_norm_bwd_static_capacity() (16 MiB; the workspace is one row of partial sums per
+ *    block of the kernel's grid, two blocks per SM: on a 148-SM B200 up to 14168 columns for
+ *    F32/BF16/F16, 7084 for F64); larger requests return FAT_ERR_WORKSPACE and launch nothing.
  *  - Every GPU on which the library is loaded holds the 16 MiB until the process exits.
  *  - The first call on each device looks up the array's device address (one host-side
  *    query, with that device current).  Make that first call before starting a stream capture.
+ *    The address is remembered per device ordinal and belongs to the device's primary context
+ *    (the one the CUDA runtime uses): a process that destroys and re-creates that context
+ *    (cudaDeviceReset) or calls in under a context of its own must not use this entry point.
  *  - All calls on one device share the array.  It is fully rewritten by each call before it
  *    is read, so nothing has to be cleared, but two calls that overlap on the GPU (different
  *    streams) race on it: serialise them.

@@ -309,3 +309,89 @@ def test_full_size_properties():
     o1 = f.rational_swiglu(gate, val)
     assert torch.equal(f.rational_swiglu(gate, 2 * val), 2 * o1)                 # linear in value
     assert torch.equal(f.rational_swiglu(gate, val), o1)                         # deterministic
+
+
+def _bar16(got, want, what):
+    """Every element within |a-b| <= 1e-2 + 2e-2 |b| of the float32 oracle (the 16-bit bar)."""
+    bad, nme = bf16_violations(got.float(), want)
+    assert bad == 0.0, f"{what}: {bad:.2e} of elements outside the bar (norm max err {nme:.2e})"
+
+
+def test_config3_swiglu_full_size_vs_oracle():
+    """Bandwidth-sweep configuration, SwiGLU [16384, 8192] bf16 forward + backward, every element against the float32
+    oracle on the rounded inputs (evaluated 2048 rows at a time to keep the host's working set small)."""
+    g = torch.Generator().manual_seed(1234 + 2)
+    gate, val, go = (torch.randn(16384, 8192, generator=g).to(torch.bfloat16) for _ in range(3))
+    a, b = gate.to(DEV).requires_grad_(True), val.to(DEV).requires_grad_(True)
+    out = fat().rational_swiglu(a, b)
+    out.backward(go.to(DEV))
+    got = [t.cpu() for t in (out.detach(), a.grad, b.grad)]
+    for r0 in range(0, 16384, 2048):
+        sl = slice(r0, r0 + 2048)
+        want_out, (wg, wv) = oracle.autograd_grads(oracle.rational_swiglu, [gate[sl].float(), val[sl].float()], go[sl].float())
+        for t, w, name in zip(got, (want_out, wg, wv), ("out", "d_gate", "d_value")):
+            _bar16(t[sl], w, f"swiglu {name} rows {r0}..")
+
+
+def test_config3_norm_full_size_vs_oracle():
+    """Mean-error norm [16384, 4096] bf16 with weight 1 + 0.1 N(0,1): y, d_x and d_weight against the float32 oracle."""
+    g = torch.Generator().manual_seed(1234 + 2)
+    x = torch.randn(16384, 4096, generator=g).to(torch.bfloat16)
+    go = torch.randn(16384, 4096, generator=g).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(4096, generator=g)).to(torch.bfloat16)
+    a, wd = x.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
+    y = fat().mean_error_norm(a, wd)
+    y.backward(go.to(DEV))
+    want_y, (wx, ww) = oracle.autograd_grads(oracle.mean_error_norm, [x.float(), w.float()], go.float())
+    _bar16(y.detach().cpu(), want_y, "norm y")
+    _bar16(a.grad.cpu(), wx, "norm d_x")
+    # d_weight sums 16384 rows: its magnitude is ~sqrt(16384), so the bar is applied relative to that scale
+    assert norm_max_err(wd.grad, ww) < 2e-2
+
+
+@pytest.mark.parametrize("std", [1.4142135, 2.0])
+def test_config3_softmax_full_size_vs_oracle(std):
+    """Rational softmax [4096, 4096] bf16, scores ~ N(0, 2) read both ways (variance 2 and standard deviation 2)."""
+    g = torch.Generator().manual_seed(1234 + 2)
+    x = (torch.randn(4096, 4096, generator=g) * std).to(torch.bfloat16)
+    go = torch.randn(4096, 4096, generator=g).to(torch.bfloat16)
+    a = x.to(DEV).requires_grad_(True)
+    p = fat().rational_softmax(a)
+    p.backward(go.to(DEV))
+    want_p, (wx,) = oracle.autograd_grads(oracle.rational_softmax, [x.float()], go.float())
+    _bar16(p.detach().cpu(), want_p, "softmax p")
+    _bar16(a.grad.cpu(), wx, "softmax d_x")
+    assert norm_max_err(p.detach().float().cpu(), want_p) < 2e-2 and norm_max_err(a.grad.float().cpu(), wx) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(2, 32, 64, 128), (3, 17, 32, 1000), (2, 64, 128, 32000)])
+def test_head_loss_without_logits_vs_oracle(shape, dtype):
+    """The loss head for callers that do not keep the logits: loss, d_y and d_weight of cross_entropy((y W^T)[:, :-1],
+    labels[:, 1:]) with the logits existing one sequence at a time, against the reference's formulation in float32, and
+    against this library's own two-step path (head GEMM, then the loss over the full logits)."""
+    B, T, C, V = shape
+    g = torch.Generator().manual_seed(53)
+    y = torch.randn(B, T, C, generator=g).to(dtype)
+    w = (torch.randn(V, C, generator=g) * 0.3).to(dtype)
+    labels = torch.randint(0, V, (B, T), generator=g)
+    labels[torch.rand(B, T, generator=g) < 0.2] = -100
+    yd, wd = y.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
+    loss = fat().head_shifted_cross_entropy(yd, wd, labels.to(DEV), -100)
+    (loss.float() * 2.0).backward()
+    yr, wr = y.float().requires_grad_(True), w.float().requires_grad_(True)
+    want = oracle.shifted_cross_entropy(yr @ wr.t(), labels, -100)
+    (want * 2.0).backward()
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert abs(float(loss.detach()) - float(want.detach())) <= tol * max(1.0, abs(float(want.detach())))
+    assert norm_max_err(yd.grad, yr.grad) < (2e-5 if dtype == torch.float32 else 2e-2)
+    assert norm_max_err(wd.grad, wr.grad) < (2e-5 if dtype == torch.float32 else 2e-2)
+    # the two-step path of the same library
+    y2, w2 = y.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
+    loss2 = fat().shifted_cross_entropy(y2 @ w2.t(), labels.to(DEV), -100)
+    (loss2.float() * 2.0).backward()
+    assert abs(float(loss.detach()) - float(loss2.detach())) <= tol * max(1.0, abs(float(want.detach())))
+    assert norm_max_err(yd.grad, y2.grad.cpu()) < (2e-5 if dtype == torch.float32 else 2e-2)
+    with torch.no_grad():                              # loss only: no gradient buffers, same number
+        loss3 = fat().head_shifted_cross_entropy(y.to(DEV), w.to(DEV), labels.to(DEV), -100)
+    assert float(loss3) == float(loss.detach())

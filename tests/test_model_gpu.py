@@ -66,3 +66,29 @@ def test_generate_runs():
     model.eval()
     out = model.generate(g["input_ids"][:1, :8].to(DEV), max_new_tokens=4, top_k=5)
     assert out.shape == (1, 12)
+
+
+def test_lm_without_logits_gives_the_same_loss_and_gradients():
+    """return_logits=False: the head GEMM and the loss run one sequence at a time, the [B, T, V] logits never exist.
+    Same loss and parameter gradients as the reference's golden vectors."""
+    model, g = build_from_golden()
+    logits, loss = model(g["input_ids"].to(DEV), labels=g["labels"].to(DEV), return_logits=False)
+    assert logits is None
+    assert abs(loss.item() - g["loss"]) < 1e-5
+    loss.backward()
+    for name, p in model.named_parameters():
+        assert norm_max_err(p.grad, g["g__" + name.replace(".", "__")]) < 5e-5, name
+    with pytest.raises(ValueError):
+        model(g["input_ids"].to(DEV), return_logits=False)
+
+
+def test_loss_backward_twice_is_refused_not_wrong():
+    """The loss gradients are scaled in place in the backward; a second backward over the same graph would scale them
+    twice, so it raises instead."""
+    model, g = build_from_golden()
+    for keep in (True, False):
+        _, loss = model(g["input_ids"].to(DEV), labels=g["labels"].to(DEV), return_logits=keep)
+        loss.backward(retain_graph=True)
+        with pytest.raises(RuntimeError, match="twice"):
+            loss.backward()
+        model.zero_grad(set_to_none=True)
