@@ -131,12 +131,14 @@ attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out, uint32_
         for (int i = 0; i < 8; ++i) o[i] += lo[i];
       }
     }
-    if (q16 && live) {                            // float16 copies of this row of q and k (dense [B,H,T,D])
+    if (q16 && live) {                            // float16 copies of this row of q (and k) (dense [B,H,T,D])
       const uint4 qv = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1] + int64_t(t) * p.qs[2] + l * 8));
-      const uint4 kv = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.k) + b * p.ks[0] + h * p.ks[1] + int64_t(t) * p.ks[2] + l * 8));
       const int64_t at = (int64_t(bh) * p.T + t) * D + l * 8;
       *reinterpret_cast<uint4*>(q16 + at) = bf16x8_to_f16x8(qv, out_of_range);
-      *reinterpret_cast<uint4*>(k16 + at) = bf16x8_to_f16x8(kv, out_of_range);
+      if (k16) {                                  // (the fused kernel converts its K tile itself)
+        const uint4 kv = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.k) + b * p.ks[0] + h * p.ks[1] + int64_t(t) * p.ks[2] + l * 8));
+        *reinterpret_cast<uint4*>(k16 + at) = bf16x8_to_f16x8(kv, out_of_range);
+      }
     }
     float dot = 0.f;
 #pragma unroll
@@ -703,26 +705,51 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   float dscale, dscale_inv;                                  // c and 1/c of this (batch, head), see the top of the file
   dout_scale(dmax_of(p)[bh], dscale, dscale_inv);
 
+  // K and V of this CTA, and the first loads of the streamed tiles (both Q stages, dO), all issued before anything
+  // else.  bfloat16 tensors: the whole CTA then turns the K tile into float16 in place before any role starts (four
+  // 16-byte packs per thread, while the other loads are in flight; every K tile belongs to exactly one CTA, which
+  // also checks its range).  Q tiles arrive as float16 from the copy the prepare pass made.
+  const float* delta_bh = p.delta + (int64_t(b) * p.H + h) * pad_rows(p.T);
+  const float* inv_bh = delta_bh + int64_t(p.B) * p.H * pad_rows(p.T);
+  auto load_q = [&](int i) {                                  // Q tile, Delta and kOpScale/(L+eps) of query tile kt + i
+    const int st = i & 1, qi = kt + i;
+    mbar_expect_tx(&sm.q_full[st], S::kTileBytes + 2 * BLK * 4);
+    load_tile_tma_noexpect<D>(sm.q[st], &maps.q, &sm.q_full[st], qi * BLK, h, b);
+    bulk_load(sm.delta[st], delta_bh + qi * BLK, BLK * 4, &sm.q_full[st]);
+    bulk_load(sm.inv[st], inv_bh + qi * BLK, BLK * 4, &sm.q_full[st]);
+  };
+  if (warp == kFusedTmaWarp && elect_one()) {
+    mbar_expect_tx(&sm.kv_full, 2 * S::kTileBytes);
+    load_tile_tma_noexpect<D>(sm.k, &maps.k, &sm.kv_full, kt * BLK, h, b);
+    load_tile_tma_noexpect<D>(sm.v, &maps.v, &sm.kv_full, kt * BLK, h, b);
+    load_q(0);
+    load_tile_tma<D>(sm.dout, &maps.dout, &sm.do_full, kt * BLK, h, b);
+    if (n > 1) load_q(1);
+  }
+  if constexpr (!std::is_same<T, __half>::value) {
+    if (g.wait(&sm.kv_full, 0, 139)) {
+      uint32_t out_of_range = 0;
+#pragma unroll
+      for (int off = tid * 16; off < S::kTileBytes; off += kFusedThreads * 16)
+        *reinterpret_cast<uint4*>(sm.k + off) = bf16x8_to_f16x8(*reinterpret_cast<const uint4*>(sm.k + off), out_of_range);
+      if (out_of_range && p.status) atomicOr(p.status, kStatusF16Range);
+      fence_async_smem();
+    }
+    __syncthreads();
+  }
+
   if (warp >= kFusedTmaWarp) {
     reg_share_dec<kFusedRegsAux>();                             // warps 12..15 (15 only takes part in this)
     if (warp == kFusedTmaWarp) {
       // ---------------------------------------------------------------- TMA producer
       if (elect_one()) {
-        mbar_expect_tx(&sm.kv_full, 2 * S::kTileBytes);
-        load_tile_tma_noexpect<D>(sm.k, &maps.k, &sm.kv_full, kt * BLK, h, b);
-        load_tile_tma_noexpect<D>(sm.v, &maps.v, &sm.kv_full, kt * BLK, h, b);
-        const float* delta_bh = p.delta + (int64_t(b) * p.H + h) * pad_rows(p.T);
-        const float* inv_bh = delta_bh + int64_t(p.B) * p.H * pad_rows(p.T);
-        for (int i = 0; i < n; ++i) {
-          const int st = i & 1, qi = kt + i;
-          const uint32_t ph = (i >> 1) & 1;
-          if (!g.wait(&sm.q_empty[st], ph ^ 1, 140)) break;
-          mbar_expect_tx(&sm.q_full[st], S::kTileBytes + 2 * BLK * 4);
-          load_tile_tma_noexpect<D>(sm.q[st], &maps.q, &sm.q_full[st], qi * BLK, h, b);
-          bulk_load(sm.delta[st], delta_bh + qi * BLK, BLK * 4, &sm.q_full[st]);
-          bulk_load(sm.inv[st], inv_bh + qi * BLK, BLK * 4, &sm.q_full[st]);
+        for (int i = 1; i < n; ++i) {                                          // (Q(0), Q(1) and dO(0) are on their way)
+          if (i >= 2) {
+            if (!g.wait(&sm.q_empty[i & 1], ((i >> 1) & 1) ^ 1, 140)) break;
+            load_q(i);
+          }
           if (!g.wait(&sm.do_empty, (i & 1) ^ 1, 141)) break;                  // dV(i-1) and dP^T(i-1) have read dO(i-1)
-          load_tile_tma<D>(sm.dout, &maps.dout, &sm.do_full, qi * BLK, h, b);
+          load_tile_tma<D>(sm.dout, &maps.dout, &sm.do_full, (kt + i) * BLK, h, b);
         }
       }
     } else if (warp == kFusedMmaWarpX || warp == kFusedMmaWarpY) {
@@ -1030,25 +1057,29 @@ __half* ws_k16(const AttnParams& p) {
 }
 
 // dq_zero: the fused backward's float32 d_q accumulator, cleared by the same pass (nullptr: nothing to clear)
+// copy_k: also write the float16 copy of k (the fused kernel converts its K tile itself and does not need it)
 template <typename T, int D>
-int launch_prepare(const AttnParams& p, cudaStream_t st, float* dq_zero = nullptr) {
+int launch_prepare(const AttnParams& p, cudaStream_t st, float* dq_zero, bool copy_k) {
   float* inv_rows = p.delta + int64_t(p.B) * p.H * pad_rows(p.T);
   const unsigned blocks = unsigned(p.B) * p.H * unsigned(pad_rows(p.T) / kPrepRows);
   if (cudaMemsetAsync(dmax_of(p), 0, size_t(p.B) * p.H * sizeof(uint32_t), st) != cudaSuccess) return check_launch("attn_bwd_prepare (clear)");
   constexpr bool kCopies = !std::is_same<T, __half>::value;
   attn_bwd_prepare_kernel<T, D><<<blocks, 256, 0, st>>>(p, inv_rows, dmax_of(p), dq_zero, kCopies ? ws_q16(p) : nullptr,
-                                                        kCopies ? ws_k16(p) : nullptr);
+                                                        kCopies && copy_k ? ws_k16(p) : nullptr);
   return check_launch("attn_bwd_prepare");
 }
 
-// Tensor maps of the q and k operands of the main kernels: the float16 copies (dense) for bfloat16 tensors, the
-// tensors themselves for float16.
+// Tensor maps of the q and k operands of the main kernels: for bfloat16 tensors the float16 copies (dense), except
+// that a kernel which converts its K tile itself (k_copy = false) reads k in place; for float16 the tensors themselves.
 template <typename T, int D>
-bool make_qk_maps(const AttnParams& p, CUtensorMap* mq, CUtensorMap* mk) {
-  if (std::is_same<T, __half>::value)
-    return make_tmap_bhtd(mq, p.q, p.B, p.H, p.T, D, p.qs, 64, BLK) && make_tmap_bhtd(mk, p.k, p.B, p.H, p.T, D, p.ks, 64, BLK);
+bool make_qk_maps(const AttnParams& p, CUtensorMap* mq, CUtensorMap* mk, bool k_copy) {
+  const bool copies = !std::is_same<T, __half>::value;
   const int64_t dense[3] = {int64_t(p.H) * p.T * D, int64_t(p.T) * D, D};
-  return make_tmap_bhtd(mq, ws_q16(p), p.B, p.H, p.T, D, dense, 64, BLK) && make_tmap_bhtd(mk, ws_k16(p), p.B, p.H, p.T, D, dense, 64, BLK);
+  const bool ok_q = copies ? make_tmap_bhtd(mq, ws_q16(p), p.B, p.H, p.T, D, dense, 64, BLK)
+                           : make_tmap_bhtd(mq, p.q, p.B, p.H, p.T, D, p.qs, 64, BLK);
+  const bool ok_k = copies && k_copy ? make_tmap_bhtd(mk, ws_k16(p), p.B, p.H, p.T, D, dense, 64, BLK)
+                                     : make_tmap_bhtd(mk, p.k, p.B, p.H, p.T, D, p.ks, 64, BLK);
+  return ok_q && ok_k;
 }
 
 template <typename Kern, typename Maps>
@@ -1067,7 +1098,7 @@ template <typename T, int D>
 int launch_bwd_split(const AttnParams& p, cudaStream_t st) {
   DqMaps mq;
   DkvMaps mk;
-  if (!make_qk_maps<T, D>(p, &mq.q, &mq.k) ||
+  if (!make_qk_maps<T, D>(p, &mq.q, &mq.k, true) ||
       !make_tmap_bhtd(&mq.dout, p.d_out, p.B, p.H, p.T, D, p.dos, 64, BLK) ||
       !make_tmap_bhtd(&mq.v, p.v, p.B, p.H, p.T, D, p.vs, 64, BLK) ||
       !make_tmap_bhtd(&mq.dq, p.d_q, p.B, p.H, p.T, D, p.dqs, 64, BLK) ||
@@ -1075,7 +1106,7 @@ int launch_bwd_split(const AttnParams& p, cudaStream_t st) {
       !make_tmap_bhtd(&mk.dv, p.d_v, p.B, p.H, p.T, D, p.dvs, 64, BLK))
     return FAT_ERR_LAUNCH;
   mk.q = mq.q; mk.dout = mq.dout; mk.k = mq.k; mk.v = mq.v;
-  if (int rc = launch_prepare<T, D>(p, st)) return rc;
+  if (int rc = launch_prepare<T, D>(p, st, nullptr, true)) return rc;
   if (int rc = launch_main(attn_bwd_dq_tc_kernel<T, D>, mq, p, sizeof(DqSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dq_tc")) return rc;
   return launch_main(attn_bwd_dkv_tc_kernel<T, D>, mk, p, sizeof(DkvSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dkv_tc");
 }
@@ -1093,14 +1124,14 @@ int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
     return FAT_ERR_LAUNCH;
   }
   FusedMaps m;
-  if (!make_qk_maps<T, D>(p, &m.q, &m.k) ||
+  if (!make_qk_maps<T, D>(p, &m.q, &m.k, false) ||
       !make_tmap_bhtd(&m.dout, p.d_out, p.B, p.H, p.T, D, p.dos, 64, BLK) ||
       !make_tmap_bhtd(&m.v, p.v, p.B, p.H, p.T, D, p.vs, 64, BLK) ||
       !make_tmap_bhtd(&m.dk, p.d_k, p.B, p.H, p.T, D, p.dks, 64, BLK) ||
       !make_tmap_bhtd(&m.dv, p.d_v, p.B, p.H, p.T, D, p.dvs, 64, BLK) ||
       !make_tmap_bhtd_f32(&m.dq_acc, dq_acc, p.B, p.H, p.T, D, D, 32))
     return FAT_ERR_LAUNCH;
-  if (int rc = launch_prepare<T, D>(p, st, dq_acc)) return rc;
+  if (int rc = launch_prepare<T, D>(p, st, dq_acc, false)) return rc;
   if (int rc = launch_main(kern, m, p, sizeof(FusedSmem<D>), kFusedThreads, st, "attn_bwd_fused_tc")) return rc;
   const unsigned blocks = unsigned(p.B) * p.H * unsigned((p.T + kConvRows - 1) / kConvRows);
   attn_bwd_dq_convert_kernel<T, D><<<blocks, 256, 0, st>>>(p, dq_acc);
