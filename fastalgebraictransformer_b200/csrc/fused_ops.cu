@@ -313,6 +313,162 @@ norm_bwd_kernel(const T* __restrict__ d_out, const T* __restrict__ x, const T* _
   }
 }
 
+// ---------------------------------------------------------------- 16-bit rows, packed float32 arithmetic
+// The same backward for bfloat16 / float16 rows of up to two 16-byte packs per thread, written for instruction count:
+// the generic kernel above spends ~30 instructions per element (scalar conversions, a shared-memory read-modify-write
+// per element for the column sums, the weight converted twice per row) and is bound by instruction issue, not by
+// memory.  Here two neighbouring elements travel as one float32 pair (fma.rn.f32x2 and friends), the weight is
+// unpacked once per block, and the running column sums stay in registers until the block is done.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void upk2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { f32x2 d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+
+// one 32-bit word holding two 16-bit elements -> the pair as float32 (element 0 first)
+template <typename T> __device__ __forceinline__ void unpack16(uint32_t w, float& lo, float& hi);
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(uint32_t w, float& lo, float& hi) {
+  lo = __uint_as_float(w << 16); hi = __uint_as_float(w & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void unpack16<__half>(uint32_t w, float& lo, float& hi) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w)); lo = f.x; hi = f.y;
+}
+template <typename T> __device__ __forceinline__ uint32_t pack16(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack16<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack16<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&v);
+}
+// -sign(x) * c with sign(0) = 0 (c given as the bits of -c)
+__device__ __forceinline__ float neg_signed(float x, uint32_t neg_c_bits) {
+  const float v = __uint_as_float((__float_as_uint(x) & 0x80000000u) ^ neg_c_bits);
+  return x == 0.f ? 0.f : v;
+}
+
+#ifndef FAT_NORM_BWD16_MINB
+#define FAT_NORM_BWD16_MINB 2
+#endif
+template <typename T, int VPT, int NT, bool ADD = false>
+__global__ void __launch_bounds__(NT, NT == 256 ? FAT_NORM_BWD16_MINB : 1)
+norm_bwd16_kernel(const T* __restrict__ d_out, const T* __restrict__ x, const T* __restrict__ weight,
+                  const float* __restrict__ mean, T* __restrict__ d_x, float* __restrict__ partial,
+                  int64_t n_rows, int n_cols, int64_t dos, int64_t xs, int64_t dxs,
+                  double eps_d, int G, const T* __restrict__ d_add = nullptr, int64_t das = 0) {
+  constexpr int W = 8;
+  __shared__ float red[2 * (NT / 32)];
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  float* acc_sm = reinterpret_cast<float*>(dyn_smem);     // used once, at the end: slot (i, j) of thread tid at [(i * W + j) * NT + tid]
+  int phase = 0;
+  const int npk = n_cols / W, rpc = NT / G, g = threadIdx.x / G, t = threadIdx.x % G;
+  const float eps = float(eps_d);
+  f32x2 w2[VPT][4], acc[VPT][4];
+  {
+    RawRow<T, VPT> wraw;
+    wraw.fetch(weight, t, G, npk, true);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t* ww = reinterpret_cast<const uint32_t*>(&wraw.v[i]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { float a, b; unpack16<T>(ww[k], a, b); w2[i][k] = pk2(a, b); acc[i][k] = pk2(0.f, 0.f); }
+    }
+  }
+  const int64_t row_step = int64_t(gridDim.x) * rpc, first_row = int64_t(blockIdx.x) * rpc + g;
+  RawRow<T, VPT> next_x, next_g, next_a;
+  next_x.fetch(x + first_row * xs, t, G, npk, first_row < n_rows);
+  next_g.fetch(d_out + first_row * dos, t, G, npk, first_row < n_rows);
+  if (ADD) next_a.fetch(d_add + first_row * das, t, G, npk, first_row < n_rows);
+  float next_mean = first_row < n_rows ? __ldg(mean + first_row) : 0.f;       // fetched a row ahead like the packs
+  for (int64_t row0 = int64_t(blockIdx.x) * rpc; row0 < n_rows; row0 += row_step) {
+    const int64_t row = row0 + g;
+    const bool ok = row < n_rows;
+    const RawRow<T, VPT> xr = next_x, gr = next_g;
+    RawRow<T, VPT> ar;
+    if (ADD) ar = next_a;
+    const bool more = row + row_step < n_rows;
+    next_x.fetch(x + (row + row_step) * xs, t, G, npk, more);
+    next_g.fetch(d_out + (row + row_step) * dos, t, G, npk, more);
+    if (ADD) next_a.fetch(d_add + (row + row_step) * das, t, G, npk, more);
+    const float inv = ok ? 1.0f / (next_mean + eps) : 0.f;
+    next_mean = more ? __ldg(mean + row + row_step) : 0.f;
+    const f32x2 inv2 = pk2(inv, inv);
+    f32x2 s2 = pk2(0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xr.v[i]);
+      const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gr.v[i]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float x0, x1, g0, g1;
+        unpack16<T>(xw[k], x0, x1);
+        unpack16<T>(gw[k], g0, g1);
+        const f32x2 gxn = mul2(pk2(g0, g1), mul2(pk2(x0, x1), inv2));     // d_out * x / mu  (0 beyond the row: zero packs)
+        acc[i][k] = add2(acc[i][k], gxn);
+        s2 = fma2(gxn, w2[i][k], s2);
+      }
+    }
+    float s[1];
+    {
+      float a, b;
+      upk2(s2, a, b);
+      s[0] = a + b;
+    }
+    group_sum<float, 1, NT>(s, G, red, phase);
+    const float corr = s[0] / float(n_cols) * inv;
+    const uint32_t neg_corr = __float_as_uint(-corr);
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int pk = t + i * G;
+        if (pk < npk) {
+          const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xr.v[i]);
+          const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gr.v[i]);
+          const uint32_t* aw = reinterpret_cast<const uint32_t*>(&ar.v[i]);
+          uint4 out_raw;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&out_raw);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float x0, x1, g0, g1, o0, o1;
+            unpack16<T>(xw[k], x0, x1);
+            unpack16<T>(gw[k], g0, g1);
+            // d_out * w / mu - sign(x) * corr
+            upk2(fma2(mul2(pk2(g0, g1), w2[i][k]), inv2, pk2(neg_signed(x0, neg_corr), neg_signed(x1, neg_corr))), o0, o1);
+            uint32_t packed = pack16<T>(o0, o1);
+            if (ADD) {                                       // rounded like the separate norm backward, then added
+              float r0, r1, a0, a1;
+              unpack16<T>(packed, r0, r1);
+              unpack16<T>(aw[k], a0, a1);
+              packed = pack16<T>(r0 + a0, r1 + a1);
+            }
+            ow[k] = packed;
+          }
+          __stcs(reinterpret_cast<uint4*>(d_x + row * dxs + int64_t(pk) * W), out_raw);
+        }
+      }
+    }
+  }
+  // fold the row groups of this block and publish the block's partial sums
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float a, b;
+      upk2(acc[i][k], a, b);
+      acc_sm[(i * W + 2 * k) * NT + threadIdx.x] = a;
+      acc_sm[(i * W + 2 * k + 1) * NT + threadIdx.x] = b;
+    }
+  }
+  float* prow = partial + int64_t(blockIdx.x) * n_cols;
+  __syncthreads();
+  for (int c = threadIdx.x; c < n_cols; c += NT) {
+    const int pk = c / W, j = c % W, i = pk / G, tt = pk % G;
+    float sum = 0.f;
+    for (int r = 0; r < rpc; ++r) sum += acc_sm[(i * W + j) * NT + r * G + tt];
+    prow[c] = sum;
+  }
+}
+
 // d_weight[c] = sum over the n_part partial rows.  Block = 32 columns x kReduceSlices slices of the partial rows,
 // so that a thread has only a handful of (independent) loads to wait for.
 constexpr int kReduceSlices = 32;
@@ -513,6 +669,15 @@ row_slow_kernel(const T* __restrict__ a,      // x
 // =====================================================================================
 struct RowPlan { bool fast; int G; int vpt; int grid; };
 
+// Grid of a grid-stride kernel over `items` equal work items with at most `max_blocks` blocks: every block gets the
+// same number of items (give or take one), so that no block is still working while the others have run out.  With
+// the plain min(items, max_blocks), 2048 items on 888 blocks would leave 272 blocks with a third item while 616 idle.
+inline int balanced_grid(int64_t items, int64_t max_blocks) {
+  if (items <= max_blocks) return int(items);
+  const int64_t per_block = (items + max_blocks - 1) / max_blocks;
+  return int((items + per_block - 1) / per_block);
+}
+
 // Fast path: all pointers 16-byte aligned, n_cols and the row strides multiples of the pack
 // width, and the row fits in registers (<= 256 * 8 packs).
 template <typename T>
@@ -532,10 +697,9 @@ RowPlan plan_rows(int64_t n_rows, int64_t n_cols, std::initializer_list<const vo
     const int need = (npk + G - 1) / G;
     p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
     const int rpc = threads / G;
-    const int64_t blocks = (n_rows + rpc - 1) / rpc;
-    p.grid = int(blocks < int64_t(blocks_per_sm) * num_sms() ? blocks : int64_t(blocks_per_sm) * num_sms());
+    p.grid = balanced_grid((n_rows + rpc - 1) / rpc, int64_t(blocks_per_sm) * num_sms());
   } else {
-    p.grid = int(n_rows < int64_t(blocks_per_sm) * num_sms() ? n_rows : int64_t(blocks_per_sm) * num_sms());
+    p.grid = balanced_grid(n_rows, int64_t(blocks_per_sm) * num_sms());
   }
   if (p.grid < 1) p.grid = 1;
   return p;
@@ -645,7 +809,12 @@ int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mea
   // wide rows run with 512-thread blocks so that a thread owns one or two packs of a row: the per-thread
   // state (weight, d_weight partials, the row and the prefetched next row) then fits in 64 registers
   constexpr int kWide = 512;
-  const bool wide = n_cols / W > kThreads;
+#ifndef FAT_NORM_BWD16_WIDE
+#define FAT_NORM_BWD16_WIDE 0
+#endif
+  // (16-bit rows of up to 2 x 256 packs go to the packed-arithmetic kernel, which keeps 256-thread blocks: two of them
+  //  share an SM and fill each other's reduction barriers)
+  const bool wide = n_cols / W > kThreads && !(sizeof(T) == 2 && n_cols / W <= 2 * kThreads && !FAT_NORM_BWD16_WIDE);
   const int threads = wide ? kWide : kThreads;
   RowPlan p = plan_rows<T>(n_rows, n_cols, {d_out, x, w, d_x, d_add}, {dos, xs, dxs, das}, FAT_NORM_BWD_BPS, FAT_NORM_BWD_PPT, threads);
   if (p.grid > norm_bwd_max_blocks()) p.grid = norm_bwd_max_blocks();
@@ -661,7 +830,27 @@ int norm_bwd_t(const void* d_out, const void* x, const void* w, const float* mea
       kern<<<p.grid, threads, smem, st>>>((const T*)d_out, (const T*)x, (const T*)w, mean, (T*)d_x, partial,
                                          n_rows, int(n_cols), dos, xs, dxs, eps, p.G, (const T*)d_add, das);
     };
-    if (d_add) {
+    bool launched16 = false;
+    if constexpr (sizeof(T) == 2) {
+      if (p.vpt <= 2) {                                     // 16-bit rows of up to two packs per thread: the packed-arithmetic kernel
+        auto go16 = [&](auto kern, size_t smem) {
+          if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+          kern<<<p.grid, threads, smem, st>>>((const T*)d_out, (const T*)x, (const T*)w, mean, (T*)d_x, partial,
+                                             n_rows, int(n_cols), dos, xs, dxs, eps, p.G, (const T*)d_add, das);
+        };
+        const size_t smem1 = size_t(threads) * 1 * W * sizeof(float), smem2 = size_t(threads) * 2 * W * sizeof(float);
+        if (d_add) {
+          if (wide) { if (p.vpt == 1) go16(norm_bwd16_kernel<T, 1, kWide, true>, smem1); else go16(norm_bwd16_kernel<T, 2, kWide, true>, smem2); }
+          else      { if (p.vpt == 1) go16(norm_bwd16_kernel<T, 1, kThreads, true>, smem1); else go16(norm_bwd16_kernel<T, 2, kThreads, true>, smem2); }
+        } else {
+          if (wide) { if (p.vpt == 1) go16(norm_bwd16_kernel<T, 1, kWide>, smem1); else go16(norm_bwd16_kernel<T, 2, kWide>, smem2); }
+          else      { if (p.vpt == 1) go16(norm_bwd16_kernel<T, 1, kThreads>, smem1); else go16(norm_bwd16_kernel<T, 2, kThreads>, smem2); }
+        }
+        launched16 = true;
+      }
+    }
+    if (launched16) {
+    } else if (d_add) {
       if (wide) { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kWide, true>, size_t(kWide) * VPT * W * sizeof(C))); }
       else      { FAT_VPT_SWITCH(p.vpt, go(norm_bwd_kernel<T, W, VPT, kThreads, true>, size_t(kThreads) * VPT * W * sizeof(C))); }
     } else {

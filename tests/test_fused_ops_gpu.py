@@ -379,7 +379,7 @@ def test_head_loss_without_logits_vs_oracle(shape, dtype):
     yd, wd = y.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
     loss = fat().head_shifted_cross_entropy(yd, wd, labels.to(DEV), -100)
     (loss.float() * 2.0).backward()
-    yr, wr = y.float().requires_grad_(True), w.float().requires_grad_(True)
+    yr, wr = y.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
     want = oracle.shifted_cross_entropy(yr @ wr.t(), labels, -100)
     (want * 2.0).backward()
     tol = 1e-5 if dtype == torch.float32 else 2e-2
