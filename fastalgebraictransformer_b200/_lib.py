@@ -90,36 +90,32 @@ def strides3(t: torch.Tensor):
     return (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
 
 
-_status = {}
-
-
 def device_status(device: torch.device) -> torch.Tensor:
-    """The int32 status word kernels of this device write when a bounded wait runs out."""
+    """The int32 status word the attention kernels of this device write (a bounded wait that ran out, an operand outside
+    float16's range); owned by the operator library."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    if idx not in _status:
-        _status[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
-    return _status[idx]
+    return torch.ops.algebraic.device_status(idx)
 
 
 def check_device_status(device=None) -> None:
-    """Synchronise and raise if any kernel reported a timed-out wait since the last check."""
-    for idx, word in list(_status.items()):
-        if device is not None and torch.device(device).index not in (None, idx):
-            continue
-        v = int(word.item())
-        if v:
-            word.zero_()
-            if v & 0x40000000:
-                raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x}: the fused attention backward found its "
-                                   "dynamic shared memory not 1024-byte aligned and did nothing; request path 3 "
-                                   "(PATH_TENSOR_DETERMINISTIC) on this platform")
-            if v & 0x20000000:
-                raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x}: the tensor-core attention backward met "
-                                   "|q| or |k| >= 65536 in a bfloat16 tensor; it forms d_q and d_k from float16 copies of q and k, "
-                                   "which were clamped to 65504, so those gradients are wrong for this call; request path 1 "
-                                   "(PATH_SIMT) for tensors of that magnitude")
-            raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x} "
-                               f"(code {(v >> 24) & 0x1f}: a bounded wait inside a kernel ran out, detail {v & 0xffffff})")
+    """Synchronise and raise if a kernel reported something on `device` (default: the current device) since the last check."""
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    word = device_status(torch.device("cuda", idx))
+    v = int(word.item())
+    if v:
+        word.zero_()
+        if v & 0x40000000:
+            raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x}: the fused attention backward found its "
+                               "dynamic shared memory not 1024-byte aligned and did nothing; request path 3 "
+                               "(PATH_TENSOR_DETERMINISTIC) on this platform")
+        if v & 0x20000000:
+            raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x}: the tensor-core attention kernels met a magnitude "
+                               "of 65536 or more in a bfloat16 tensor (v in the forward, q or k in the backward); they work on float16 "
+                               "copies of those operands, which were clamped to 65504, so the results of this call are wrong; request "
+                               "path 1 (PATH_SIMT) for tensors of that magnitude")
+        raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x} "
+                           f"(code {(v >> 24) & 0x1f}: a bounded wait inside a kernel ran out, detail {v & 0xffffff})")
 
 
 class device_guard:

@@ -65,7 +65,7 @@ class RationalAttentionPackedFunction(torch.autograd.Function):
         assert qkv.is_cuda and qkv.dim() == 5 and qkv.shape[2] == 3
         B, T, _, H, D = qkv.shape
         q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
-        out, L, out_lo = ops._attn_fwd(q, k, v, alibi_slopes, float(scale), True, float(eps), _lib.PATH_AUTO, True)
+        out, L, out_lo = ops.attn_fwd(q, k, v, alibi_slopes, float(scale), True, float(eps), _lib.PATH_AUTO, True)
         ctx.save_for_backward(qkv, out, L, out_lo, alibi_slopes)
         ctx.scale, ctx.eps = float(scale), float(eps)
         return out.permute(0, 2, 1, 3).reshape(B, T, H * D)        # a view: the memory order already is [B,T,H,D]

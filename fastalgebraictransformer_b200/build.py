@@ -1,4 +1,4 @@
-"""Build libfat_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
+"""Build libfat_b200.so (the C-ABI library, nvcc for sm_100a) and libfat_torch_ops.so (the torch.library operators, g++) in-tree.
 
     python -m fastalgebraictransformer_b200.build [--force] [--verbose]
 
@@ -19,6 +19,8 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(PKG, "libfat_b200.so")
+OPS_SRC = os.path.join(CSRC, "torch_ops.cpp")
+OPS_LIB = os.path.join(PKG, "libfat_torch_ops.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
@@ -73,7 +75,31 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link of libfat_b200.so failed")
+    build_ops(force or bool(jobs), verbose)
     return LIB
+
+
+def build_ops(force: bool = False, verbose: bool = False) -> str:
+    """Compile csrc/torch_ops.cpp (the C++ registration of the torch.library operators) against the installed torch
+    and link it to libfat_b200.so.  Host code only: g++, no nvcc."""
+    header = os.path.join(PKG, "..", "include", "fat_b200.h")
+    if not (force or _stale(OPS_LIB, [OPS_SRC, header, LIB])):
+        return OPS_LIB
+    import torch
+    from torch.utils import cpp_extension as ce
+    cuda_home = os.environ.get("CUDA_HOME") or os.path.dirname(os.path.dirname(_nvcc()))
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", OPS_SRC, "-o", OPS_LIB,
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", "-I" + os.path.join(cuda_home, "include")]
+    cmd += ["-I" + p for p in ce.include_paths()]
+    cmd += ["-L" + p for p in ce.library_paths()]
+    cmd += ["-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", "-L" + PKG, "-lfat_b200", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode:
+        sys.stderr.write(r.stdout + r.stderr)
+    if r.returncode:
+        raise RuntimeError("build of libfat_torch_ops.so failed")
+    return OPS_LIB
 
 
 if __name__ == "__main__":

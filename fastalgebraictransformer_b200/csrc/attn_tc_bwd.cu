@@ -834,8 +834,9 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
     float* stage0 = sm.dq_stage;                              // two staging tiles of [32 query rows][D] float32
     float* stage1 = sm.dq_stage + 32 * D;
     bool ok = true;
-    // One quarter (32 query rows) of dQ^T: registers -> staging tile -> reduce-add.  `pending` bulk groups may still be
-    // reading the other staging tile; the one that read this tile must be done before it is overwritten.
+    // One quarter (32 query rows) of dQ^T: registers -> staging tile -> reduce-add.  One bulk group may still be reading
+    // the other staging tile; the one that read this tile (the group before the newest) must be done before it is
+    // overwritten, so every quarter commits exactly one group, issued or not.
     auto flush = [&](const uint32_t (&v)[32], float* stage, int row, bool wait_first) {
       if (wait_first) {
         if (dl == 0) tma_store_wait_read1();
@@ -847,9 +848,9 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
       }
       fence_async_smem();
       named_barrier(3, 128);
-      if (dl == 0 && row < p.T) {
-        tma_reduce_add_4d(&maps.dq_acc, stage, 0, row, h, b);
-        tma_store_commit();
+      if (dl == 0) {
+        if (row < p.T) tma_reduce_add_4d(&maps.dq_acc, stage, 0, row, h, b);
+        tma_store_commit();                                   // also when nothing was issued (rows beyond T): the waits above count groups
       }
     };
     for (int i = 0; i < n; ++i) {

@@ -1,6 +1,7 @@
 // Host-side construction of TMA tensor maps.  cuTensorMapEncodeTiled is fetched from the
 // driver at run time (cudaGetDriverEntryPoint), so the library does not link against libcuda.
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -25,10 +26,49 @@ EncodeFn encode_fn() {
   return fn;
 }
 
+// A tensor map is a pure function of (address, extents, strides, box, element kind), and a training loop presents the
+// same few of them step after step, so encoded maps are kept: a launch then costs a hash lookup per operand instead of
+// a driver call.  The table is dropped wholesale when it grows past a bound (addresses from a caching allocator recur,
+// so in practice it stays small).
+struct MapKey {
+  const void* base; int B, H, T, D, box_d, box_t, kind; int64_t s0, s1, s2;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && B == o.B && H == o.H && T == o.T && D == o.D && box_d == o.box_d && box_t == o.box_t &&
+           kind == o.kind && s0 == o.s0 && s1 == o.s1 && s2 == o.s2;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    auto mix = [&](uint64_t v) { h = (h ^ v) * 1099511628211ull; };
+    mix(reinterpret_cast<uintptr_t>(k.base)); mix(uint64_t(k.B) << 32 | uint32_t(k.H)); mix(uint64_t(k.T) << 32 | uint32_t(k.D));
+    mix(uint64_t(k.box_d) << 40 | uint64_t(k.box_t) << 8 | uint32_t(k.kind)); mix(uint64_t(k.s0)); mix(uint64_t(k.s1)); mix(uint64_t(k.s2));
+    return size_t(h);
+  }
+};
+std::mutex g_map_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+constexpr size_t kMaxCachedMaps = 4096;
+
+bool cached_map(const MapKey& key, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) return false;
+  *out = it->second;
+  return true;
+}
+void remember_map(const MapKey& key, const CUtensorMap& m) {
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  if (g_maps.size() >= kMaxCachedMaps) g_maps.clear();
+  g_maps.emplace(key, m);
+}
+
 }  // namespace
 
 bool make_tmap_bhtd(CUtensorMap* out, const void* base, int B, int H, int T, int D,
                     const int64_t* s, int box_d, int box_t) {
+  const MapKey key{base, B, H, T, D, box_d, box_t, 16, s[0], s[1], s[2]};
+  if (cached_map(key, out)) return true;
   // The encoder is a driver-API call: it needs the primary context bound to the calling thread,
   // which a thread that has only been handed pointers (e.g. an autograd worker) may not have yet.
   static thread_local bool bound = false;
@@ -51,10 +91,13 @@ bool make_tmap_bhtd(CUtensorMap* out, const void* base, int B, int H, int T, int
               D, T, H, B, (long long)strides[0], (long long)strides[1], (long long)strides[2], box_d, box_t);
     return false;
   }
+  remember_map(key, *out);
   return true;
 }
 
 bool make_tmap_bhtd_f32(CUtensorMap* out, const void* base, int B, int H, int T, int D, int box_d, int box_t) {
+  const MapKey key{base, B, H, T, D, box_d, box_t, 32, 0, 0, 0};
+  if (cached_map(key, out)) return true;
   static thread_local bool bound = false;
   if (!bound) { cudaFree(nullptr); bound = true; }
   EncodeFn fn = encode_fn();
@@ -70,6 +113,7 @@ bool make_tmap_bhtd_f32(CUtensorMap* out, const void* base, int B, int H, int T,
     set_error("cuTensorMapEncodeTiled (float32) failed with code %d (dims %d,%d,%d,%d box %d,%d)", int(r), D, T, H, B, box_d, box_t);
     return false;
   }
+  remember_map(key, *out);
   return true;
 }
 

@@ -62,7 +62,7 @@ class RationalSwiGLUPacked(torch.autograd.Function):
         assert gv.is_cuda, "Inputs must be on CUDA"
         gate, value = gv.chunk(2, dim=-1)
         ctx.save_for_backward(gv)
-        return ops._swiglu_fwd(gate, value)
+        return _alg.swiglu_fwd(gate, value)
 
     @staticmethod
     def backward(ctx, grad_output: torch.Tensor):
