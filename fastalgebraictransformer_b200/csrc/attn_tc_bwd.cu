@@ -236,7 +236,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
   if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kBwdBands, rank, bh)) return;   // padding block of the banded order
   const int b = bh / p.H, h = bh % p.H;
   const int qt = (p.T + BLK - 1) / BLK - 1 - rank;           // long rows first
-  const int n = qt + 1;                                      // key tiles 0..qt (causal)
+  const int n = p.causal ? qt + 1 : (p.T + BLK - 1) / BLK;   // key tiles 0..qt (causal) or all of them
   Guard g{&sm.abort_flag, p.status};
 
   if (tid == 0) {
@@ -317,7 +317,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
     const int64_t srow = (int64_t(b) * p.H + h) * pad_rows(p.T) + row;
     const float dlt = p.delta[srow];                                               // Delta of this query
     const float ginv = p.delta[int64_t(p.B) * p.H * pad_rows(p.T) + srow] ;              // kOpScale/(L+eps)
-    const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(2.f * slope, 2.f * slope);
+    const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f);
     const float cs = kDsScaleQ * dscale;                     // dS_stored = g8 cs (dP - Delta)
     const f32x2 cs2 = pk2(cs, cs), ndlt2 = pk2(-dlt * cs, -dlt * cs);
     bool ok = true;
@@ -326,30 +326,43 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       // ---- phase A: g = sigma^3 r^2 / (L+eps) from the scores
       if (!(ok = g.wait(&sm.s_full, j & 1, 60))) break;
       tc_fence_after();
-      const float base = slope * float(j * BLK - row);       // bias of key column 0 of this tile
+      // bias of key column c of this tile: -slope |row - (j BLK + c)| = sl * c + base with sl = slope for keys up to the
+      // query, -slope for keys after it (non-causal only); the diagonal tile of a non-causal problem takes the absolute
+      // value element by element (ABS)
+      const float sl = (!p.causal && j > qt) ? -slope : slope;
+      const float base = sl * float(j * BLK - row);
+      const f32x2 step2 = pk2(2.f * sl, 2.f * sl);
+      auto phase_a = [&](auto ABS) {
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t sreg[32];
-        tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
-        tmem_wait_ld_regs(sreg);
-        const int col0 = kColsPerGroup * w + 32 * c;
-        f32x2 bias2 = pk2(fmaf(slope, float(col0), base), fmaf(slope, float(col0 + 1), base));
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t sreg[32];
+          tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
+          tmem_wait_ld_regs(sreg);
+          const int col0 = kColsPerGroup * w + 32 * c;
+          f32x2 bias2 = pk2(fmaf(sl, float(col0), base), fmaf(sl, float(col0 + 1), base));
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          f32x2 F2, g2;
-          const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-          if (rcp_shared(i, FAT_RCP_SHARE_BWD)) score_fg2<false, true>(acc2, scale2, bias2, half2, F2, g2);
-          else            score_fg2<false, false>(acc2, scale2, bias2, half2, F2, g2);
-          bias2 = add2(bias2, step2);
-          gq[16 * c + i] = g2;
+          for (int i = 0; i < 16; ++i) {
+            f32x2 F2, g2, b2 = bias2;
+            if constexpr (decltype(ABS)::value) {
+              float b0, b1;
+              upk2(bias2, b0, b1);
+              b2 = pk2(-fabsf(b0), -fabsf(b1));
+            }
+            const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+            if (rcp_shared(i, FAT_RCP_SHARE_BWD)) score_fg2<false, true>(acc2, scale2, b2, half2, F2, g2);
+            else            score_fg2<false, false>(acc2, scale2, b2, half2, F2, g2);
+            bias2 = add2(bias2, step2);
+            gq[16 * c + i] = g2;
+          }
         }
-      }
+      };
+      if (!p.causal && j == qt) phase_a(std::true_type{}); else phase_a(std::false_type{});
       tc_fence_before();
       mbar_arrive(&sm.s_free);
       // ---- phase B: dS = g (dP - Delta), packed over dP
       if (!(ok = g.wait(&sm.dp_full[j & 1], (j >> 1) & 1, 61))) break;
       tc_fence_after();
-      const bool diag = (j == qt);
+      const bool diag = p.causal && (j == qt);               // (non-causal: nothing is masked)
       const uint32_t tP = tP0 + (j & 1) * BLK;
       // (the diagonal tile gets its own copy of the loop: a run-time test inside the unrolled body would split it
       //  into basic blocks and keep the compiler from interleaving the independent pairs)
@@ -434,7 +447,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
   if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kBwdBands, kt, bh)) return;     // padding block of the banded order
   const int b = bh / p.H, h = bh % p.H;
   const int n_q_total = (p.T + BLK - 1) / BLK;
-  const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
+  const int q0 = p.causal ? kt : 0;                          // first query tile that sees this key tile
+  const int n = n_q_total - q0;                              // query tiles q0..n_q_total-1
   Guard g{&sm.abort_flag, p.status};
 
   if (tid == 0) {
@@ -463,7 +477,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       const float* delta_bh = p.delta + (int64_t(b) * p.H + h) * pad_rows(p.T);
       const float* inv_bh = delta_bh + int64_t(p.B) * p.H * pad_rows(p.T);
       for (int it = 0; it < n; ++it) {
-        const int st = it % kBwdStages, qi = kt + it;
+        const int st = it % kBwdStages, qi = q0 + it;
         const uint32_t ph = (it / kBwdStages) & 1;
         if (!g.wait(&sm.q_empty[st], ph ^ 1, 70)) break;
         mbar_expect_tx(&sm.q_full[st], S::kTileBytes + 2 * BLK * 4);
@@ -522,42 +536,53 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
     const int key = kt * BLK + r;
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
     const float slope = p.slopes[h], scale = p.scale;
-    const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f), step2 = pk2(-2.f * slope, -2.f * slope);
+    const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f);
     const float cs = kDsScale * dscale / kOpScale;           // dS_stored = g8 (kOpScale/(L+eps)) cs (dP - Delta)
     const f32x2 cs2 = pk2(cs, cs);
     bool ok = true;
     for (int it = 0; it < n; ++it) {
-      const int st = it % kBwdStages, qi = kt + it;
-      const bool diag = (it == 0);
+      const int st = it % kBwdStages, qi = q0 + it;
+      const bool diag = (qi == kt);
       f32x2 gq[kColsPerGroup / 2];
       // ---- phase A: p = sigma^4 / (L+eps) -> packed P^T over S^T; g / (L+eps) kept in registers
       if (!(ok = g.wait(&sm.q_full[st], (it / kBwdStages) & 1, 93))) break;       // Delta / inv arrived with the Q tile
       if (!(ok = g.wait(&sm.s_full, it & 1, 90))) break;
       tc_fence_after();
-      const float base = slope * float(key - qi * BLK);      // bias of query column 0: -slope*(q-key)
+      // bias of query column c: -slope |key - (qi BLK + c)| = -sl * c + base with sl = slope for queries from the key on,
+      // -slope for queries before it (non-causal only); MODE 1: causal diagonal tile (queries before the key are masked),
+      // MODE 2: non-causal diagonal tile (absolute value element by element, nothing masked)
+      const float sl = (!p.causal && qi < kt) ? -slope : slope;
+      const float base = sl * float(key - qi * BLK);
+      const f32x2 step2 = pk2(-2.f * sl, -2.f * sl);
       const float* iv = sm.inv[st];
-      auto phase_a = [&](auto DIAG) {          // the diagonal tile gets its own copy (no run-time test in the unrolled body)
+      auto phase_a = [&](auto MODE) {          // the diagonal tile gets its own copy (no run-time test in the unrolled body)
+        constexpr int kMode = decltype(MODE)::value;
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
           uint32_t sreg[32], preg[16];
           tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
           tmem_wait_ld_regs(sreg);
           const int col0 = kColsPerGroup * w + 32 * c;
-          f32x2 bias2 = pk2(fmaf(-slope, float(col0), base), fmaf(-slope, float(col0 + 1), base));
+          f32x2 bias2 = pk2(fmaf(-sl, float(col0), base), fmaf(-sl, float(col0 + 1), base));
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float2 iv2f = *reinterpret_cast<const float2*>(iv + col0 + 2 * i);
             const f32x2 iv2 = pk2(iv2f.x, iv2f.y);
-            f32x2 F2, g2;
+            f32x2 F2, g2, b2 = bias2;
+            if constexpr (kMode == 2) {
+              float b0, b1;
+              upk2(bias2, b0, b1);
+              b2 = pk2(-fabsf(b0), -fabsf(b1));
+            }
             const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-            if (rcp_shared(i, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, bias2, half2, F2, g2);
-            else                                  score_fg2<true, false>(acc2, scale2, bias2, half2, F2, g2);
+            if (rcp_shared(i, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, b2, half2, F2, g2);
+            else                                  score_fg2<true, false>(acc2, scale2, b2, half2, F2, g2);
             bias2 = add2(bias2, step2);
             F2 = mul2(F2, iv2);
             g2 = mul2(g2, iv2);
             float p0, p1;
             upk2(F2, p0, p1);
-            if constexpr (decltype(DIAG)::value) {            // queries before the key see nothing of it
+            if constexpr (kMode == 1) {                       // queries before the key see nothing of it
               float g0, g1;
               upk2(g2, g0, g1);
               if (col0 + 2 * i < r) { p0 = 0.f; g0 = 0.f; }
@@ -570,7 +595,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
           tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
         }
       };
-      if (diag) phase_a(std::true_type{}); else phase_a(std::false_type{});
+      if (!diag)         phase_a(std::integral_constant<int, 0>{});
+      else if (p.causal) phase_a(std::integral_constant<int, 1>{});
+      else               phase_a(std::integral_constant<int, 2>{});
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full);
@@ -681,7 +708,8 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   if (!banded_tile((p.T + BLK - 1) / BLK, p.B * p.H, kBwdBands, kt, bh)) return;     // padding block of the banded order
   const int b = bh / p.H, h = bh % p.H;
   const int n_q_total = (p.T + BLK - 1) / BLK;
-  const int n = n_q_total - kt;                              // query tiles kt..n_q_total-1 (causal)
+  const int q0 = p.causal ? kt : 0;                          // first query tile that sees this key tile
+  const int n = n_q_total - q0;                              // query tiles q0..n_q_total-1
   Guard g{&sm.abort_flag, p.status};
   if ((smem_u32(smem_raw) & 1023u) != 0) {                   // the swizzled tiles need a 1024-byte aligned base
     if (tid == 0 && p.status) atomicOr(p.status, 0x40000000);
@@ -711,8 +739,8 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
   // also checks its range).  Q tiles arrive as float16 from the copy the prepare pass made.
   const float* delta_bh = p.delta + (int64_t(b) * p.H + h) * pad_rows(p.T);
   const float* inv_bh = delta_bh + int64_t(p.B) * p.H * pad_rows(p.T);
-  auto load_q = [&](int i) {                                  // Q tile, Delta and kOpScale/(L+eps) of query tile kt + i
-    const int st = i & 1, qi = kt + i;
+  auto load_q = [&](int i) {                                  // Q tile, Delta and kOpScale/(L+eps) of query tile q0 + i
+    const int st = i & 1, qi = q0 + i;
     mbar_expect_tx(&sm.q_full[st], S::kTileBytes + 2 * BLK * 4);
     load_tile_tma_noexpect<D>(sm.q[st], &maps.q, &sm.q_full[st], qi * BLK, h, b);
     bulk_load(sm.delta[st], delta_bh + qi * BLK, BLK * 4, &sm.q_full[st]);
@@ -723,7 +751,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
     load_tile_tma_noexpect<D>(sm.k, &maps.k, &sm.kv_full, kt * BLK, h, b);
     load_tile_tma_noexpect<D>(sm.v, &maps.v, &sm.kv_full, kt * BLK, h, b);
     load_q(0);
-    load_tile_tma<D>(sm.dout, &maps.dout, &sm.do_full, kt * BLK, h, b);
+    load_tile_tma<D>(sm.dout, &maps.dout, &sm.do_full, q0 * BLK, h, b);
     if (n > 1) load_q(1);
   }
   if constexpr (!std::is_same<T, __half>::value) {
@@ -749,7 +777,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
             load_q(i);
           }
           if (!g.wait(&sm.do_empty, (i & 1) ^ 1, 141)) break;                  // dV(i-1) and dP^T(i-1) have read dO(i-1)
-          load_tile_tma<D>(sm.dout, &maps.dout, &sm.do_full, (kt + i) * BLK, h, b);
+          load_tile_tma<D>(sm.dout, &maps.dout, &sm.do_full, (q0 + i) * BLK, h, b);
         }
       }
     } else if (warp == kFusedMmaWarpX || warp == kFusedMmaWarpY) {
@@ -854,7 +882,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
       }
     };
     for (int i = 0; i < n; ++i) {
-      const int row0 = (kt + i) * BLK;
+      const int row0 = (q0 + i) * BLK;
       if (!(ok = g.wait(&sm.dq_full, i & 1, 160))) break;
       tc_fence_after();
       uint32_t a[32], c[32];
@@ -897,43 +925,54 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
     const int key = kt * BLK + r;
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
     const float slope = p.slopes[h], scale = p.scale;
-    const f32x2 scale2 = pk2(scale, scale), one2 = pk2(1.0f, 1.0f), step2 = pk2(-2.f * slope, -2.f * slope);
+    const f32x2 scale2 = pk2(scale, scale), one2 = pk2(1.0f, 1.0f);
     const float cs = kDsScale * dscale / kOpScale;           // dS_stored = g8 (kOpScale/(L+eps)) cs (dP - Delta)
     const f32x2 cs2 = pk2(cs, cs);
     bool ok = true;
     for (int i = 0; i < n; ++i) {
-      const int st = i & 1, qi = kt + i;
-      const bool diag = (i == 0);
+      const int st = i & 1, qi = q0 + i;
+      const bool diag = (qi == kt);
       f32x2 gq[kColsPerGroup / 2];
       // ---- phase A: p = sigma^4 / (L+eps) -> packed P^T over S^T; g / (L+eps) kept in registers
       if (!(ok = g.wait(&sm.q_full[st], (i >> 1) & 1, 170))) break;        // Delta / inv arrived with the Q tile
       if (!(ok = g.wait(&sm.s_full, i & 1, 171))) break;
       tc_fence_after();
-      const float base = slope * float(key - qi * BLK);      // bias of query column 0: -slope*(q-key)
+      // bias of query column c: -slope |key - (qi BLK + c)| = -sl * c + base with sl = slope for queries from the key on,
+      // -slope for queries before it (non-causal only); MODE 1: causal diagonal tile (queries before the key are masked),
+      // MODE 2: non-causal diagonal tile (absolute value element by element, nothing masked)
+      const float sl = (!p.causal && qi < kt) ? -slope : slope;
+      const float base = sl * float(key - qi * BLK);
+      const f32x2 step2 = pk2(-2.f * sl, -2.f * sl);
       const float* iv = sm.inv[st];
-      auto phase_a = [&](auto DIAG) {          // the diagonal tile gets its own copy (no run-time test in the unrolled body)
+      auto phase_a = [&](auto MODE) {          // the diagonal tile gets its own copy (no run-time test in the unrolled body)
+        constexpr int kMode = decltype(MODE)::value;
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
           uint32_t sreg[32], preg[16];
           tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
           tmem_wait_ld_regs(sreg);
           const int col0 = kColsPerGroup * w + 32 * c;
-          f32x2 bias2 = pk2(fmaf(-slope, float(col0), base), fmaf(-slope, float(col0 + 1), base));
+          f32x2 bias2 = pk2(fmaf(-sl, float(col0), base), fmaf(-sl, float(col0 + 1), base));
           float4 ivq = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             if (e % 2 == 0) ivq = *reinterpret_cast<const float4*>(iv + col0 + 2 * e);
             const f32x2 iv2 = e % 2 == 0 ? pk2(ivq.x, ivq.y) : pk2(ivq.z, ivq.w);
-            f32x2 F2, g2;
+            f32x2 F2, g2, b2 = bias2;
+            if constexpr (kMode == 2) {
+              float b0, b1;
+              upk2(bias2, b0, b1);
+              b2 = pk2(-fabsf(b0), -fabsf(b1));
+            }
             const f32x2 acc2 = pk2(__uint_as_float(sreg[2 * e]), __uint_as_float(sreg[2 * e + 1]));
-            if (rcp_shared(e, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, bias2, one2, F2, g2);
-            else                                  score_fg2<true, false>(acc2, scale2, bias2, one2, F2, g2);
+            if (rcp_shared(e, FAT_RCP_SHARE_BWD)) score_fg2<true, true>(acc2, scale2, b2, one2, F2, g2);
+            else                                  score_fg2<true, false>(acc2, scale2, b2, one2, F2, g2);
             bias2 = add2(bias2, step2);
             F2 = mul2(F2, iv2);
             g2 = mul2(g2, iv2);
             float p0, p1;
             upk2(F2, p0, p1);
-            if constexpr (decltype(DIAG)::value) {            // queries before the key see nothing of it
+            if constexpr (kMode == 1) {                       // queries before the key see nothing of it
               float g0, g1;
               upk2(g2, g0, g1);
               if (col0 + 2 * e < r) { p0 = 0.f; g0 = 0.f; }
@@ -946,7 +985,9 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
           tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
         }
       };
-      if (diag) phase_a(std::true_type{}); else phase_a(std::false_type{});
+      if (!diag)         phase_a(std::integral_constant<int, 0>{});
+      else if (p.causal) phase_a(std::integral_constant<int, 1>{});
+      else               phase_a(std::integral_constant<int, 2>{});
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full);

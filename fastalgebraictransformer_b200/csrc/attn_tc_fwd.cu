@@ -71,14 +71,23 @@ struct FwdMaps { CUtensorMap q, k, v, out, out_lo; };
 // as packed float16 pairs in preg (the factor cancels in O = P V / sum P); adds the chunk's row sum to l2.
 // With r' = 1/((|s|+1)/4) = 4 r (one fused multiply-add feeds the reciprocal, as the plain |s|+1 would) and
 // w' = 4 + s r' = 4 (1 + s r) = 8 sigma, the scaling costs no instruction.  `four2` holds the packed constant 4.
-// MASK: diagonal tile, keys with column index > r get no weight.
-template <bool MASK>
-__device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32_t (&preg)[16], int c, int r, f32x2 scale2,
+// The ALiBi bias of column c is slope * c + base (the caller gives slope and base the sign that makes it -slope_h |i - j|
+// on its side of the diagonal).  MASK: keys with column index > lim get no weight (causal: the diagonal tile, lim = the
+// thread's row; non-causal: the last key tile of a ragged sequence, lim = its last valid column).  ABS: the tile
+// straddles the diagonal of a non-causal problem, the bias is -|slope * c + base|.
+template <bool MASK, bool ABS>
+__device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32_t (&preg)[16], int c, int lim, f32x2 scale2,
                                               f32x2 four2, f32x2 step2, float slope, float base, f32x2& l2) {
   f32x2 bias2 = pk2(fmaf(slope, float(c * 32), base), fmaf(slope, float(c * 32 + 1), base));
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    const f32x2 s2 = fma2(pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), scale2, bias2);
+    f32x2 b2 = bias2;
+    if (ABS) {
+      float b0, b1;
+      upk2(bias2, b0, b1);
+      b2 = pk2(-fabsf(b0), -fabsf(b1));
+    }
+    const f32x2 s2 = fma2(pk2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), scale2, b2);
     bias2 = add2(bias2, step2);
     float s0, s1;
     upk2(s2, s0, s1);
@@ -90,8 +99,8 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32
     float f0, f1;
     upk2(f2, f0, f1);
     if (MASK) {
-      if (c * 32 + 2 * i > r) f0 = 0.f;
-      if (c * 32 + 2 * i + 1 > r) f1 = 0.f;
+      if (c * 32 + 2 * i > lim) f0 = 0.f;
+      if (c * 32 + 2 * i + 1 > lim) f1 = 0.f;
       f2 = pk2(f0, f1);
     }
     l2 = add2(l2, f2);
@@ -103,8 +112,8 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32
 // index c0).  The packed P of chunk c lands on columns [16 c, 16 c + 16) counted from `trow`, i.e. over scores
 // this thread has already taken into registers.  The chunk loop is kept rolled (the body is ~400 instructions;
 // unrolled four times it no longer fits the instruction cache).
-template <bool MASK>
-__device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int r, f32x2 scale2, f32x2 four2, f32x2 step2,
+template <bool MASK, bool ABS>
+__device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int lim, f32x2 scale2, f32x2 four2, f32x2 step2,
                                              float slope, float base, f32x2& l2) {
   uint32_t sreg[32];
   tmem_ld32(trow, sreg);
@@ -112,7 +121,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int r, f32x2
   for (int c = 0; c < kChunks; ++c) {
     tmem_wait_ld_regs(sreg);
     uint32_t preg[16];
-    softmax_chunk<MASK>(sreg, preg, c0 + c, r, scale2, four2, step2, slope, base, l2);
+    softmax_chunk<MASK, ABS>(sreg, preg, c0 + c, lim, scale2, four2, step2, slope, base, l2);
     if (c + 1 < kChunks) tmem_ld32(trow + (c + 1) * 32, sreg);      // next chunk in flight while this one is stored
     tmem_st16(trow + c * 16, preg);
   }
@@ -156,7 +165,7 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
   // query tile t covers rows [(2qb+t)*128, +128); it needs key tiles 0..(2qb+t) (causal)
   int n_tiles[2];
 #pragma unroll
-  for (int t = 0; t < 2; ++t) n_tiles[t] = (2 * qb + t) * BLK < p.T ? min(2 * qb + t + 1, n_kv_total) : 0;
+  for (int t = 0; t < 2; ++t) n_tiles[t] = (2 * qb + t) * BLK < p.T ? (p.causal ? min(2 * qb + t + 1, n_kv_total) : n_kv_total) : 0;
   const int n_max = max(n_tiles[0], n_tiles[1]);
   Guard g{&sm.abort_flag, p.status};
   constexpr bool kConvertV = !std::is_same<T, __half>::value;
@@ -271,16 +280,31 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
     const float scale = p.scale;
     const int n = n_tiles[t];
     f32x2 l2 = pk2(0.f, 0.f);
-    const f32x2 scale2 = pk2(scale, scale), four2 = pk2(4.0f, 4.0f), step2 = pk2(2.f * slope, 2.f * slope);
+    const f32x2 scale2 = pk2(scale, scale), four2 = pk2(4.0f, 4.0f);
     bool ok = true;
     for (int j = 0; j < n; ++j) {
       if (!(ok = g.wait(&sm.s_full[t], j & 1, 30))) break;
       tc_fence_after();
-      const float base = slope * float(j * BLK - row);       // bias of column 0 of this tile: -slope*(row-k0)
       const bool diag = (j == 2 * qb + t);
+      // bias of column c of this tile: -slope |row - (j BLK + c)|.  Keys up to the query: slope * c + slope (j BLK - row);
+      // keys after it (non-causal only): the same with the sign flipped; the diagonal tile of a non-causal problem
+      // takes the absolute value element by element.
+      const float sl = (!p.causal && j > 2 * qb + t) ? -slope : slope;
+      const float base = sl * float(j * BLK - row);
+      const f32x2 step2 = pk2(2.f * sl, 2.f * sl);
       const uint32_t trow = tmem_addr(tmem, lane_base, t * BLK + part * kColsPerWg);
-      if (diag) softmax_tile<true>(trow, part * kChunks, r, scale2, four2, step2, slope, base, l2);
-      else      softmax_tile<false>(trow, part * kChunks, r, scale2, four2, step2, slope, base, l2);
+      if (p.causal) {
+        if (diag) softmax_tile<true, false>(trow, part * kChunks, r, scale2, four2, step2, sl, base, l2);
+        else      softmax_tile<false, false>(trow, part * kChunks, r, scale2, four2, step2, sl, base, l2);
+      } else {
+        // zero-filled keys beyond T are not neutral (sigma(bias)^4 > 0): the last tile of a ragged sequence masks them
+        const int last_col = p.T - 1 - j * BLK;
+        const bool tail = last_col < BLK - 1;
+        if (diag && tail)  softmax_tile<true, true>(trow, part * kChunks, last_col, scale2, four2, step2, sl, base, l2);
+        else if (diag)     softmax_tile<false, true>(trow, part * kChunks, 0, scale2, four2, step2, sl, base, l2);
+        else if (tail)     softmax_tile<true, false>(trow, part * kChunks, last_col, scale2, four2, step2, sl, base, l2);
+        else               softmax_tile<false, false>(trow, part * kChunks, 0, scale2, four2, step2, sl, base, l2);
+      }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full[t]);

@@ -40,11 +40,11 @@ int num_sms() {
   return n;
 }
 
-// The tensor-core attention kernels cover 16-bit tensors, head sizes 64 and 128, causal masking, and pointers /
+// The tensor-core attention kernels cover 16-bit tensors, head sizes 64 and 128 (causal or not), and pointers /
 // strides that TMA can address (16-byte aligned, strides multiples of 8 elements).
 bool attn_tc_eligible(int T, int D, int dtype, bool aligned, bool causal, bool backward) {
-  (void)backward;
-  return T >= 1 && (D == 64 || D == 128) && (dtype == FAT_BF16 || dtype == FAT_F16) && aligned && causal;
+  (void)backward; (void)causal;
+  return T >= 1 && (D == 64 || D == 128) && (dtype == FAT_BF16 || dtype == FAT_F16) && aligned;
 }
 
 namespace {
@@ -71,8 +71,8 @@ int resolve_path(const char* what, int path, int T, int D, int dtype, bool align
   if (path == FAT_PATH_SIMT) return FAT_PATH_SIMT;
   if (path == FAT_PATH_TENSOR || path == FAT_PATH_TENSOR_DETERMINISTIC) {
     if (!ok) {
-      set_error("%s: the tensor-core path needs bf16/f16, D in {64,128}, causal masking, 16-byte aligned pointers and "
-                "strides (got dtype %d, D=%d, causal=%d, aligned=%d)", what, dtype, D, int(causal), int(aligned));
+      set_error("%s: the tensor-core path needs bf16/f16, D in {64,128}, 16-byte aligned pointers and "
+                "strides (got dtype %d, D=%d, aligned=%d)", what, dtype, D, int(aligned));
       return aligned ? -FAT_ERR_UNSUPPORTED : -FAT_ERR_ALIGNMENT;
     }
     return FAT_PATH_TENSOR;

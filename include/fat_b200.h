@@ -48,7 +48,7 @@ enum fat_status {
 enum fat_attn_path {
   FAT_PATH_AUTO = 0,        /* tensor-core kernels when eligible, else the SIMT kernels */
   FAT_PATH_SIMT = 1,        /* fp32-accumulating CUDA-core kernels (any dtype, D<=128)  */
-  FAT_PATH_TENSOR = 2,      /* tcgen05/TMEM kernels (bf16/f16, D in {64,128}, causal); error if not eligible */
+  FAT_PATH_TENSOR = 2,      /* tcgen05/TMEM kernels (bf16/f16, D in {64,128}); error if not eligible */
   FAT_PATH_TENSOR_DETERMINISTIC = 3   /* same, but the backward never uses the fused kernel, whose d_q is
                                accumulated across key tiles with float32 reduce-adds in an unordered sequence:
                                bit-reproducible gradients at the price of recomputing the scores twice */

@@ -294,9 +294,25 @@ def test_forced_tensor_path_rejects_ineligible_requests():
     slopes = oracle.compute_alibi_slopes(2).to(DEV)
     with pytest.raises(RuntimeError):
         torch.ops.algebraic.attn_fwd(q, q, q, slopes, 0.2, True, 1e-6, 2, False)      # D=32 has no tcgen05 kernel
-    q = torch.randn(1, 2, 64, 64, device=DEV, dtype=torch.bfloat16)
+    q = torch.randn(1, 2, 64, 64, device=DEV, dtype=torch.float32)
     with pytest.raises(RuntimeError):
-        torch.ops.algebraic.attn_fwd(q, q, q, slopes, 0.2, False, 1e-6, 2, False)     # non-causal runs on the CUDA cores
+        torch.ops.algebraic.attn_fwd(q, q, q, slopes, 0.2, True, 1e-6, 2, False)      # float32 runs on the CUDA cores
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 2, 64, 64), (2, 3, 200, 64), (1, 2, 333, 128), (1, 4, 512, 128), (1, 2, 192, 64), (1, 2, 1024, 128)])
+@pytest.mark.parametrize("path", [2, 3])
+def test_non_causal_on_the_tensor_cores(shape, dtype, path):
+    """causal=False on the tcgen05 kernels (every query sees every key, bias -slope |i-j| on both sides of the diagonal,
+    zero-filled keys of a ragged last tile masked): against the oracle with its mask line removed.  Parity unpinned by the
+    reference for this flag: its kernels never read it."""
+    B, H, T, D = shape
+    q, k, v, go = gen_qkv(61, B, H, T, D, dtype)
+    slopes = oracle.compute_alibi_slopes(H)
+    scale = 1.0 / math.sqrt(D)
+    got = run_attention(q, k, v, go, slopes, scale, causal=False, path=path)
+    want = oracle.rational_attention_grads(q.float(), k.float(), v.float(), go.float(), slopes, scale, causal=False)
+    assert_16bit_bar(got, want)
 
 
 def test_config2_slice_bf16():
