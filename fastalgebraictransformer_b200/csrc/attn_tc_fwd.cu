@@ -198,6 +198,11 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
         if (!g.wait(&sm.k_empty[st], ((j / kStages) & 1) ^ 1, 10)) break;
         load_tile_tma<D>(sm.k[st], &maps.k, &sm.k_full[st], j * BLK, h, b);
         if (!g.wait(&sm.v_empty[vst], ((j / kVStages) & 1) ^ 1, 11)) break;
+#ifdef FAT_TEST_WITHHOLD_V_TILE
+        // test builds only (never the shipped library): this V tile is not loaded, so every wait that depends on it
+        // runs out, which is how the give-up path (status word, teardown, TMEM release) gets exercised
+        if (j == FAT_TEST_WITHHOLD_V_TILE) continue;
+#endif
         load_tile_tma<D>(sm.v[vst], &maps.v, &sm.v_full[vst], j * BLK, h, b);
       }
     }

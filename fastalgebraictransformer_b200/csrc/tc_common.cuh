@@ -56,7 +56,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Every wait in these kernels is bounded.  When the bound is hit the kernel records a status
 // word, raises a CTA-wide abort flag that makes all later waits fall through, and runs to
 // its normal teardown (TMEM is released, the launch ends, the context stays usable).
-#if FAT_WAIT_HINT_NS >= 100000
+#if defined(FAT_WAIT_SPINS)
+constexpr uint32_t kWaitSpins = FAT_WAIT_SPINS;   // test builds: a wait gives up after FAT_WAIT_SPINS x kWaitHintNs
+#elif FAT_WAIT_HINT_NS >= 100000
 constexpr uint32_t kWaitSpins = 1u << 15;      // x kWaitHintNs: a few seconds at most
 #elif FAT_WAIT_HINT_NS > 0
 constexpr uint32_t kWaitSpins = (1u << 15) * (100000u / FAT_WAIT_HINT_NS);
