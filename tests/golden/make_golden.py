@@ -41,7 +41,7 @@ def grads(fn, inputs, d_out):
 
 def main():
     ap = argparse.ArgumentParser()
-XX
+    ap.add_argument("--reference", required=True, help="directory that contains the 'reference' package")
     ap.add_argument("--only", default=None, help="write only the fixtures whose name starts with this prefix")
     args = ap.parse_args()
     global ONLY
