@@ -268,7 +268,7 @@ def bench_attn(args, rank, world, device):
     ms_fwd = time_steps(fwd, max(3, args.steps // 2), 1, world, device)
     ms_bwd = time_steps(bwd, max(3, args.steps // 2), 1, world, device)
     # the same step back to back for about a second: the regime the sustained peak is defined on
-    sus_steps = max(args.steps, int(1.2e3 / max(ms, 1e-3)))
+    sus_steps = max(args.steps, int(1.2e3 / max(ms, 1e-3))) if not args.batch else args.steps    # (profiling case: kept short)
     with ClockSampler(device.index) as sus_clocks:
         ms_sus = time_steps(step, sus_steps, 1, world, device)
 

@@ -89,7 +89,11 @@ __host__ __device__ inline uint32_t* dmax_of(const AttnParams& p) {
 // ------------------------------------------------------------------------------------- 1. prepare
 // One block = kPrepRows consecutive (padded) rows of one (batch, head): the only divisions are one 32-bit pair per
 // block (the kernel is bound by instruction issue as much as by memory; per-row 64-bit divisions doubled its time).
-constexpr int kPrepRows = 64;
+#ifndef FAT_PREP_ROWS
+#define FAT_PREP_ROWS 64
+#define FAT_PREP_UNROLL 2
+#endif
+constexpr int kPrepRows = FAT_PREP_ROWS, kPrepUnroll = FAT_PREP_UNROLL;
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
 attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out, uint32_t* __restrict__ dmax,
@@ -117,7 +121,7 @@ attn_bwd_prepare_kernel(const AttnParams p, float* __restrict__ inv_out, uint32_
     float4* z = reinterpret_cast<float4*>(dq_zero + (int64_t(bh) * p.T + t0) * D);
     for (int i = threadIdx.x; i < rows * (D / 4); i += 256) __stcs(z + i, make_float4(0.f, 0.f, 0.f, 0.f));
   }
-#pragma unroll 2
+#pragma unroll (kPrepUnroll)
   for (int t = t0 + warp * RPW + sub; t < t0 + kPrepRows; t += 8 * RPW) {
     const bool live = t < p.T;
     float g[8] = {}, o[8] = {};
