@@ -210,9 +210,9 @@ def make_attn_inputs(cfg, seed, device=None, pin=False):
 
 
 # DRAM bytes of the three backward launches of one step at B=2 (ncu, dram__bytes_read.sum + dram__bytes_write.sum):
-# profiles/attention_bf16_B2_H16_S4096_D128.md, table "DRAM traffic per launch"; traffic grows in proportion to
+# profiles/attention_bf16_B2_H16_S4096_D128.md, section "DRAM traffic per launch"; traffic grows in proportion to
 # the (batch, head) units, so the full-size figure is this one scaled by units / 32.
-ATTN_BWD_TRAFFIC_B2 = 472.8e6
+ATTN_BWD_TRAFFIC_B2 = 570.6e6
 
 
 def shard_batches(B: int, H: int, rank: int, world: int):
@@ -328,10 +328,10 @@ def bench_attn(args, rank, world, device):
 #   softmax  fwd x in, p out (2) + bwd d_out, x in, d_x out (3) = 5 passes: the backward recomputes p from x instead
 #            of reading the saved p (the variant that moves 3 tensors in the backward)
 # `traffic`: dram__bytes_read.sum + dram__bytes_write.sum of one step's launches at these shapes, from
-# profiles/fused_ops_bf16_config3.md (table "DRAM traffic per step")
+# profiles/fused_ops_bf16_config3.md (section "DRAM traffic per step")
 FUSED = {
     "swiglu": dict(rows=16384, cols=8192, bytes=8 * 16384 * 8192 * 2, traffic=2068e6),
-    "norm": dict(rows=16384, cols=4096, bytes=5 * 16384 * 4096 * 2, traffic=587e6),
+    "norm": dict(rows=16384, cols=4096, bytes=5 * 16384 * 4096 * 2, traffic=595e6),
     "softmax": dict(rows=4096, cols=4096, bytes=5 * 4096 * 4096 * 2, traffic=106e6),
     # residual addition fused with the norm: forward x, residual in, sum, y out; backward d_y, d_sum_in, sum in, d_sum out
     "add_norm": dict(rows=16384, cols=4096, bytes=8 * 16384 * 4096 * 2, traffic=None),
