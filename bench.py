@@ -470,10 +470,12 @@ LM = {
 }
 
 
-def run_lm(name, steps, warmup, rank, world, device, graph=True, eager_steps=0):
+def run_lm(name, steps, warmup, rank, world, device, graph=True, eager_steps=0, keep_logits=True):
     """One training step (forward, loss, backward with DDP's gradient all-reduce when world > 1, fused AdamW) of the
     named model.  graph: capture the step in a CUDA graph and time its replays; eager_steps > 0: also time that many
-    steps issued launch by launch, as a user of the module would (reported as `eager_ms`)."""
+    steps issued launch by launch, as a user of the module would (reported as `eager_ms`).  keep_logits: the step is the
+    reference-shaped call `model(ids, labels=labels)`, which returns the [B,T,V] logits; otherwise it asks for the loss only
+    (`return_logits=False`: the head GEMM and the loss run one sequence at a time, the logits never exist)."""
     from fastalgebraictransformer_b200 import AlgebraicTransformerLM
     cfg = LM[name]
     torch.manual_seed(1234 + 3)
@@ -497,7 +499,7 @@ def run_lm(name, steps, warmup, rank, world, device, graph=True, eager_steps=0):
 
     def step():
         opt.zero_grad(set_to_none=True)
-        _, loss = net(ids, labels=lab)
+        _, loss = net(ids, labels=lab, return_logits=keep_logits)
         loss.backward()
         opt.step()
         last["loss"] = loss
@@ -505,7 +507,7 @@ def run_lm(name, steps, warmup, rank, world, device, graph=True, eager_steps=0):
     def e2e_step():
         i, l = hids.to(device, non_blocking=True), hlab.to(device, non_blocking=True)
         opt.zero_grad(set_to_none=True)
-        _, loss = net(i, labels=l)
+        _, loss = net(i, labels=l, return_logits=keep_logits)
         loss.backward()
         opt.step()
         last["loss_host"] = loss.item()
@@ -532,7 +534,7 @@ def run_lm(name, steps, warmup, rank, world, device, graph=True, eager_steps=0):
             graph_obj = torch.cuda.CUDAGraph()
             opt.zero_grad(set_to_none=True)
             with torch.cuda.graph(graph_obj):
-                _, gloss = net(ids, labels=lab)
+                _, gloss = net(ids, labels=lab, return_logits=keep_logits)
                 gloss.backward()
                 opt.step()
             last["loss"] = gloss
@@ -558,6 +560,8 @@ def run_lm(name, steps, warmup, rank, world, device, graph=True, eager_steps=0):
         "config": {"workload": f"AlgebraicTransformerLM {name} training step (fwd+loss+bwd+AdamW), bf16, "
                                f"batch {cfg['batch']} x seq {cfg['seq']} per GPU", "params": n_params,
                    "parallelism": f"dp{world}", "launch": launch, "loss": float(last["loss"].item()),
+                   "loss_head": "full logits kept" if keep_logits else "one sequence at a time, logits never materialised",
+                   "peak_memory_gb": torch.cuda.max_memory_allocated(device) / 1e9,
                    "eager_ms": eager_ms, "eager_tokens_per_s": tokens / (eager_ms * 1e-3) if eager_ms else None},
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * hids.numel() * 8,
                 "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e, "launch": "eager"},
@@ -739,6 +743,8 @@ def main():
     ap.add_argument("--batch", type=int, default=0,
                     help="attn workload: override the batch size (profiling captures use a smaller case)")
     ap.add_argument("--no-graph", action="store_true", help="LM workloads: time eager launches instead of a CUDA graph")
+    ap.add_argument("--no-logits", action="store_true",
+                    help="LM workloads: the step asks for the loss only (return_logits=False) instead of the reference-shaped call")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world, local = dist_env()
@@ -771,7 +777,7 @@ def main():
         res = run_fused(args.workload, args.steps, args.warmup, rank, world, device)
     else:
         res = run_lm(args.workload, args.steps, args.warmup, rank, world, device, graph=not args.no_graph,
-                     eager_steps=0 if args.no_graph else max(3, args.steps // 2))
+                     eager_steps=0 if args.no_graph else max(3, args.steps // 2), keep_logits=not args.no_logits)
 
     if rank == 0:
         line = {"metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": world,
