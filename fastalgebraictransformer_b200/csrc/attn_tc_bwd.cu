@@ -806,14 +806,15 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
           }
           for (int i = 0; i < n && ok; ++i) {
             const int st = i & 1, st1 = st ^ 1;
-            if (!(ok = g.wait(&sm.p_full, i & 1, 152))) break;
-            if (!(ok = g.wait(&sm.do_full, i & 1, 153))) break;
+            // dO(i) and Q(i+1) were requested long ago: their barriers are settled before P^T, so that nothing but the issue
+            // of the MMAs stands between the end of phase A and the next S^T (a satisfied wait still costs 150-250 cycles)
+            if (!(ok = g.wait_polling(&sm.do_full, i & 1, 153))) break;
+            if (i + 1 < n && !(ok = g.wait_polling(&sm.q_full[st1], ((i + 1) >> 1) & 1, 154))) break;
+            if (!(ok = g.wait_polling(&sm.p_full, i & 1, 152))) break;
             tc_fence_after();
             issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn, idesc_dv, i > 0);               // dV += P^T dO
             mma_commit(&sm.do_empty);                                                // X's share of releasing dO(i)
             if (i + 1 < n) {
-              if (!(ok = g.wait(&sm.q_full[st1], ((i + 1) >> 1) & 1, 154))) break;
-              tc_fence_after();
               issue_gemm_nt<D>(tS, kd, qd[st1], idesc_s);                                // S^T of the next query tile
               mma_commit(&sm.s_full);
             }
@@ -832,7 +833,7 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
           }
           for (int i = 0; i < n && ok; ++i) {
             const int st = i & 1;
-            if (!(ok = g.wait(&sm.ds_full, i & 1, 156))) break;                          // phase B done: dS^T in smem, dP^T read
+            if (!(ok = g.wait_polling(&sm.ds_full, i & 1, 156))) break;                  // phase B done: dS^T in smem, dP^T read
             tc_fence_after();
             // dQ^T = K^T dS^T over the keys.  The MMA is always 128 rows tall: with D = 64 the second 64-row chunk of the
             // MN-major A operand is the tile that follows K in shared memory (V), so TMEM lanes 64..127 receive numbers
@@ -846,8 +847,8 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
               mma_ss(tK, dsd_k + ((((s / 4) * (BLK * 128) + (s % 4) * 32)) >> 4), qd_mn[st] + ((s * 2048) >> 4), idesc_dk, i > 0 || s > 0);
             mma_commit(&sm.q_empty[st]);
             if (i + 1 < n) {
-              if (!(ok = g.wait(&sm.dq_free, i & 1, 157))) break;                        // dQ^T(i) has left TMEM
-              if (!(ok = g.wait(&sm.do_full, (i + 1) & 1, 158))) break;
+              if (!(ok = g.wait_polling(&sm.do_full, (i + 1) & 1, 158))) break;         // (settled long before dQ^T is out)
+              if (!(ok = g.wait_polling(&sm.dq_free, i & 1, 157))) break;                // dQ^T(i) has left TMEM
               tc_fence_after();
               issue_gemm_nt<D>(tP, vd, dod, idesc_dp);                                   // dP^T of the next query tile
               mma_commit(&sm.dp_full);

@@ -236,20 +236,23 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
         const int st1 = (j + 1) % kStages, vst = j % kVStages;
         const uint32_t ph1 = ((j + 1) / kStages) & 1, vph = (j / kVStages) & 1;
         bool k_next_ready = false;
+        // V(j) and K(j+1) were requested an iteration or more ago: their barriers are settled first, so that nothing but the
+        // issue of the MMAs stands between a tile's P and its next S (a satisfied wait still costs 150-250 cycles)
+        if (!(ok = g.wait_polling(kConvertV ? &sm.v_ready[vst] : &sm.v_full[vst], vph, 23))) break;
+        if (j + 1 < n_max) { if (!(ok = g.wait_polling(&sm.k_full[st1], ph1, 24))) break; k_next_ready = true; }
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_tiles[t]) continue;
-          if (!(ok = g.wait(&sm.p_full[t], j & 1, 22))) break;
-          if (!(ok = g.wait(kConvertV ? &sm.v_ready[vst] : &sm.v_full[vst], vph, 23))) break;
+          if (!(ok = g.wait_polling(&sm.p_full[t], j & 1, 22))) break;
           tc_fence_after();
           issue_pv(t, vst, j == 0);
           if (j + 1 < n_tiles[t]) {
-            if (!k_next_ready) { if (!(ok = g.wait(&sm.k_full[st1], ph1, 24))) break; k_next_ready = true; tc_fence_after(); }
             issue_qk(t, st1);
             mma_commit(&sm.s_full[t]);
           } else {
             mma_commit(&sm.o_full[t]);
           }
         }
+        (void)k_next_ready;
         if (!ok) break;
         mma_commit(&sm.v_empty[vst]);                      // V(j) and, if it was read, K(j+1) are free once these finish
         if (j + 1 < n_max) mma_commit(&sm.k_empty[st1]);

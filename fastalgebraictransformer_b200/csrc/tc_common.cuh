@@ -53,6 +53,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// non-blocking test of a phase
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+
 // Every wait in these kernels is bounded.  When the bound is hit the kernel records a status
 // word, raises a CTA-wide abort flag that makes all later waits fall through, and runs to
 // its normal teardown (TMEM is released, the launch ends, the context stays usable).
@@ -82,6 +93,22 @@ struct Guard {
     }
     fail(where);
     return false;
+  }
+  // The same for the single threads that sit on the critical path between two roles (the MMA issuers): they poll without
+  // parking, which costs one warp's issue slots and wakes them some hundred cycles sooner.  Bounded like wait(): after
+  // kPollSpins polls (about a second) it gives up.
+  __device__ __forceinline__ bool wait_polling(uint64_t* bar, uint32_t parity, int where) const {
+#ifdef FAT_WAIT_SPINS
+    return wait(bar, parity, where);                      // test builds with short limits: one code path for the limit
+#else
+    constexpr uint32_t kPollSpins = 1u << 25;
+    for (uint32_t i = 0; i < kPollSpins; ++i) {
+      if (mbar_test_wait(bar, parity)) return true;
+      if ((i & 63u) == 63u && aborted()) return false;
+    }
+    fail(where);
+    return false;
+#endif
   }
 };
 
