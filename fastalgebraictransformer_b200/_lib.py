@@ -93,6 +93,7 @@ def strides3(t: torch.Tensor):
 def device_status(device: torch.device) -> torch.Tensor:
     """The int32 status word the attention kernels of this device write (a bounded wait that ran out, an operand outside
     float16's range); owned by the operator library."""
+    from . import ops  # noqa: F401  (loads the operator library on first use)
     idx = device.index if device.index is not None else torch.cuda.current_device()
     return torch.ops.algebraic.device_status(idx)
 

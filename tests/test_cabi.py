@@ -91,3 +91,15 @@ def test_alibi_slopes_match_golden():
     g = load_golden("alibi_slopes")
     for h in (1, 2, 4, 6, 8, 12, 16, 24, 40):
         assert torch.allclose(fat.compute_alibi_slopes(h), g[f"h{h}"], rtol=1e-6, atol=0)
+
+
+def test_build_module_imports_without_the_libraries():
+    """`python -m fastalgebraictransformer_b200.build` has to work in a fresh checkout: importing the package and its build
+    module must not touch the operator library (the public names load it on first use)."""
+    import subprocess
+    import sys
+    code = ("import sys; import fastalgebraictransformer_b200 as f; from fastalgebraictransformer_b200 import build; "
+            "assert 'fastalgebraictransformer_b200.ops' not in sys.modules; "
+            "assert 'rational_attention' in dir(f) and callable(build.build); print('ok')")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-500:]
