@@ -228,7 +228,7 @@ def shard_batches(B: int, H: int, rank: int, world: int):
 
 def bench_attn(args, rank, world, device):
     import fastalgebraictransformer_b200 as fat
-    from fastalgebraictransformer_b200 import _lib
+    from fastalgebraictransformer_b200 import _lib, ops  # noqa: F401  (ops: loads the operator library)
     full = dict(ATTN, B=args.batch) if args.batch else dict(ATTN)
     strong = args.scaling == "strong" and world > 1
     lo, nb = shard_batches(full["B"], full["H"], rank, world) if strong else (0, full["B"])
@@ -367,6 +367,7 @@ def fused_inputs(name, gen, device=None, rows=None):
 
 def run_fused(name, steps, warmup, rank, world, device, with_e2e=True):
     import fastalgebraictransformer_b200 as fat
+    from fastalgebraictransformer_b200 import ops  # noqa: F401  (loads the operator library)
     cfg = FUSED[name]
     g = torch.Generator(device=device).manual_seed(1234 + 2 + rank)
     shape = (cfg["rows"], cfg["cols"])
