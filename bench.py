@@ -337,6 +337,9 @@ FUSED = {
     "add_norm": dict(rows=16384, cols=4096, bytes=8 * 16384 * 4096 * 2, traffic=None),
     # loss head of the small LM: logits [8, 1024, 32000] read once, their gradient written once
     "loss_head": dict(rows=8 * 1024, cols=32000, bytes=2 * 8 * 1024 * 32000 * 2, traffic=None),
+    # one decode step of a key/value-cached generate(): every (batch, head) pair reads its 4096 cached key rows and value
+    # rows once (the query, the appended rows and the output are KBs); shape of the headline attention configuration
+    "decode": dict(rows=8 * 16 * 4096, cols=128, bytes=2 * 8 * 16 * 4096 * 128 * 2, traffic=None, B=8, H=16, cap=4096),
 }
 FUSED_TRAFFIC_SOURCE = "profiles/fused_ops_bf16_config3.md"
 
@@ -359,6 +362,11 @@ def fused_inputs(name, gen, device=None, rows=None):
         return (rnd(), weight(), rnd())                                       # x, weight, d_out
     if name == "add_norm":
         return (rnd(), weight(), rnd(), rnd(), rnd())                         # x, weight, residual, d_y, d_h
+    if name == "decode":
+        B, H, cap, D = cfg["B"], cfg["H"], (rows or cfg["rows"]) // (cfg["B"] * cfg["H"]), cfg["cols"]
+        new = [torch.randn(B, H, D, generator=gen, device=dev).to(torch.bfloat16) for _ in range(3)]    # q, k_new, v_new
+        caches = [torch.randn(B, H, cap, D, generator=gen, device=dev).to(torch.bfloat16) for _ in range(2)]
+        return (*new, *caches, torch.full((B,), cap - 1, dtype=torch.int32, device=dev))
     if name == "loss_head":
         labels = torch.randint(0, cfg["cols"], (8, shape[0] // 8), generator=gen, device=dev)
         return (rnd(2.0).view(8, shape[0] // 8, cfg["cols"]), labels)
@@ -375,6 +383,7 @@ def run_fused(name, steps, warmup, rank, world, device, with_e2e=True):
     sets = [fused_inputs(name, g, device) for _ in range(nset)]
     it = [0]
     alg = torch.ops.algebraic
+    slopes = fat.compute_alibi_slopes(cfg["H"]).to(device) if name == "decode" else None
 
     def step():
         s = sets[it[0] % nset]; it[0] += 1
@@ -388,6 +397,8 @@ def run_fused(name, steps, warmup, rank, world, device, with_e2e=True):
             alg.add_norm_bwd(s[3], s[4], h, s[1], mean, 1e-6)
         elif name == "loss_head":
             alg.shifted_ce_fwd(s[0], s[1], -100)
+        elif name == "decode":
+            alg.attn_decode(s[0], s[1], s[2], s[3], s[4], s[5], slopes, ATTN["D"] ** -0.5, 1e-6)
         else:
             alg.softmax_fwd(s[0], 1e-6); alg.softmax_bwd(s[1], s[0], 1e-6)
 
@@ -418,15 +429,17 @@ def run_fused(name, steps, warmup, rank, world, device, with_e2e=True):
     peaks = measured_peaks()
     gbs = cfg["bytes"] * world / (ms * 1e-3) / 1e9
     res = {
-        "metric": f"rational_{name}_fwd_bwd_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "dtype": "bf16",
+        "metric": f"rational_{name}_fwd_bwd_gbs" if name != "decode" else "rational_attention_decode_gbs",
+        "value": gbs, "unit": "GB/s", "ms_per_step": ms, "dtype": "bf16",
         "scaling": "weak",
-        "config": {"workload": f"{name} fwd+bwd bf16 [{cfg['rows']},{cfg['cols']}] per GPU (bandwidth-sweep configuration)",
+        "config": {"workload": f"{name} fwd+bwd bf16 [{cfg['rows']},{cfg['cols']}] per GPU (bandwidth-sweep configuration)" if name != "decode" else
+                   f"attention decode step bf16: {cfg['B']} x {cfg['H']} (batch, head) pairs, {cfg['cap']} cached tokens of {cfg['cols']} per GPU",
                    "algorithmic_bytes_per_step": cfg["bytes"],
                    "launch": "each step replayed from a CUDA graph",
                    "l2": "tensors exceed L2" if nset == 1 else f"{nset} rotating input sets (each pass touches > 126 MB before reuse)"},
         "gpu_launches": launches_per_step * steps,
         "gpu_launches_how": "fat_launch_count() of libfat_b200.so around the capture of one step, times the replays of the timed region",
-        "roofline": {"bound": "hbm", "kernel": f"{name} fwd+bwd", "achieved": gbs / world, "peak": peaks["hbm_gbs"],
+        "roofline": {"bound": "hbm", "kernel": f"{name} fwd+bwd" if name != "decode" else "attn_decode_kernel", "achieved": gbs / world, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": gbs / world / peaks["hbm_gbs"], "traffic": cfg["traffic"],
                      "traffic_source": FUSED_TRAFFIC_SOURCE if cfg["traffic"] else None,
                      "peak_source": peaks["source"] + " (copy bandwidth)"},
@@ -434,7 +447,8 @@ def run_fused(name, steps, warmup, rank, world, device, with_e2e=True):
     }
     if with_e2e:
         # end to end: host (pinned) -> device -> forward+backward through the autograd API -> host
-        hs = [t.detach().cpu().pin_memory() for t in sets[0]]
+        # (decode: the caches stay on the device, which is what a cache is for; the new token's rows go up, its output comes back)
+        hs = [t.detach().cpu().pin_memory() for t in (sets[0][:3] if name == "decode" else sets[0])]
 
         def e2e_compute(dd):
             d = [t.detach() for t in dd]
@@ -444,6 +458,8 @@ def run_fused(name, steps, warmup, rank, world, device, with_e2e=True):
             if name == "norm":
                 a, w = d[0].requires_grad_(True), d[1].requires_grad_(True)
                 o = fat.mean_error_norm(a, w); o.backward(d[2]); return (o.detach(), a.grad)
+            if name == "decode":
+                return (alg.attn_decode(d[0], d[1], d[2], sets[0][3], sets[0][4], sets[0][5], slopes, ATTN["D"] ** -0.5, 1e-6),)
             if name == "loss_head":
                 a = d[0].requires_grad_(True)
                 loss = fat.shifted_cross_entropy(a, d[1]); loss.backward(); return (loss.detach().reshape(1), a.grad)
@@ -456,10 +472,11 @@ def run_fused(name, steps, warmup, rank, world, device, with_e2e=True):
 
         e2e_step = make_pipelined_e2e(device, hs, e2e_compute)
         ms_e2e = time_steps(e2e_step, 6, 2, world, device)
-        n_out = {"swiglu": 3, "norm": 2, "softmax": 2, "add_norm": 3, "loss_head": 1}[name]
+        n_out = {"swiglu": 3, "norm": 2, "softmax": 2, "add_norm": 3, "loss_head": 1, "decode": 1}[name]
+        out_bytes = n_out * shape[0] * shape[1] * 2 if name != "decode" else cfg["B"] * cfg["H"] * cfg["cols"] * 2
         res["e2e"] = {"value": cfg["bytes"] * world / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                       "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in hs),
-                      "d2h_bytes_per_step": n_out * shape[0] * shape[1] * 2, "ms_per_step": ms_e2e, "overlap": E2E_OVERLAP}
+                      "d2h_bytes_per_step": out_bytes, "ms_per_step": ms_e2e, "overlap": E2E_OVERLAP}
     del sets, graphs
     torch.cuda.empty_cache()
     return res
@@ -582,7 +599,7 @@ def run_lm(name, steps, warmup, rank, world, device, graph=True, eager_steps=0, 
 
 def run_extras(args, rank, world, device):
     """Compact records of the other configurations at the same N, for the default workload's line: the small LM's
-    training step and the three bandwidth-sweep operators.  A failure in one is recorded, not raised."""
+    training step, the three bandwidth-sweep operators and the decode step over a key/value cache.  A failure in one is recorded, not raised."""
     extra = {}
 
     def compact(r):
@@ -595,7 +612,7 @@ def run_extras(args, rank, world, device):
                 out[k] = r["config"][k]
         return out
 
-    for name in ("swiglu", "norm", "softmax"):
+    for name in ("swiglu", "norm", "softmax", "decode"):
         try:
             r = run_fused(name, 50, 5, rank, world, device, with_e2e=False)
             r["_steps"] = 50
@@ -653,6 +670,13 @@ def cpu_sample(workload: str):
                 torch.autograd.backward([h, y], [ins[4], ins[3]])
             return (run, amount, "GB/s", what)
         return (lambda: oracle.autograd_grads(oracle.rational_softmax, ins[:1], ins[1]), amount, "GB/s", what)
+    if workload == "decode":
+        cfg = FUSED[workload]
+        q, _, _, kc, vc, _ = fused_inputs(workload, torch.Generator().manual_seed(1234 + 2))
+        q, kc, vc = q.float(), kc.float(), vc.float()
+        slopes = oracle.compute_alibi_slopes(cfg["H"])
+        return (lambda: oracle.rational_attention_last_row(q, kc, vc, slopes, cfg["cols"] ** -0.5), cfg["bytes"] / 1e9, "GB/s",
+                "the whole step (128 (batch, head) pairs x 4096 cached tokens) upcast to float32; bytes counted as for the bf16 kernel")
     if workload == "loss_head":
         cfg = FUSED[workload]
         logits, labels = fused_inputs(workload, torch.Generator().manual_seed(1234 + 2), rows=8 * 128)
@@ -682,7 +706,7 @@ def cpu_sample(workload: str):
 REF_METRIC = {"attn": "rational_attention_fwd_bwd_tflops", "lm_small": "lm_train_tokens_per_s", "lm_xl": "lm_train_tokens_per_s"}
 
 
-def cpu_baseline(workload: str, budget_s: float = 10.0, max_passes: int = 8):
+def cpu_baseline(workload: str, budget_s: float = 10.0, max_passes: int = 64):
     """The oracle on all host threads on a bounded sample of the workload: mean over passes worth ~budget_s."""
     cores = use_all_host_threads()
     run, amount, unit, what = cpu_sample(workload)
@@ -735,7 +759,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "add_norm", "loss_head", "lm_small", "lm_xl"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "add_norm", "loss_head", "decode", "lm_small", "lm_xl"])
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="attn workload on N > 1 ranks: split the 128 (batch, head) units over the ranks (strong, default) "
                          "or give every rank all of them (weak)")

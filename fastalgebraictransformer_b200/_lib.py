@@ -47,6 +47,7 @@ PROTOTYPES = {
     "fat_attn_bwd_workspace_bytes": (_sz, [_int] * 6),
     "fat_attn_bwd": (_int, [_ptr] * 12 + [_sz] + [_int] * 4 + [_p64] * 8 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
     "fat_attn_select_path": (_int, [_int] * 6),
+    "fat_attn_decode": (_int, [_ptr] * 8 + [_int] * 4 + [_p64] * 6 + [_dbl, _dbl, _int, _ptr, _ptr]),
 }
 
 
@@ -115,8 +116,11 @@ def check_device_status(device=None) -> None:
                                "of 65536 or more in a bfloat16 tensor (v in the forward, q or k in the backward); they work on float16 "
                                "copies of those operands, which were clamped to 65504, so the results of this call are wrong; request "
                                "path 1 (PATH_SIMT) for tensors of that magnitude")
+        if v & 0x10000000:
+            raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x}: a decode step found a key/value cache without room "
+                               "for the new row (or a negative length); nothing was appended and that sequence's output is zero")
         raise RuntimeError(f"libfat_b200: device {idx} status word 0x{v:08x} "
-                           f"(code {(v >> 24) & 0x1f}: a bounded wait inside a kernel ran out, detail {v & 0xffffff})")
+                           f"(code {(v >> 24) & 0xf}: a bounded wait inside a kernel ran out, detail {v & 0xffffff})")
 
 
 class device_guard:

@@ -19,6 +19,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
+from . import ops
 from .backward import RationalAttentionPackedFunction
 from .forward import compute_alibi_slopes
 from .fused_ops import (EPS, RationalSwiGLUPacked, add_mean_error_norm, head_shifted_cross_entropy, mean_error_norm,
@@ -53,6 +54,31 @@ class RationalSwiGLU(nn.Module):
         return self.dropout(self.w_out(RationalSwiGLUPacked.apply(gv)))
 
 
+class KVCache:
+    """Keys and values of the tokens a model has seen, for ``generate``: one [B, H, capacity, D] pair per layer and the
+    number of cached tokens per sequence as an int32 tensor on the device (the decode kernel reads it there, so a step
+    looks the same to the GPU whatever the length).  The reference has no cache: its generate() runs the whole prefix
+    through forward() for every new token (algebraic_model.py:239-265)."""
+
+    DECODE_HEAD_SIZES = (32, 64, 128)
+    DECODE_DTYPES = (torch.float32, torch.bfloat16, torch.float16)
+
+    def __init__(self, n_layers: int, batch: int, n_head: int, capacity: int, d_head: int, dtype: torch.dtype, device):
+        self.capacity = capacity
+        self.k = [torch.empty(batch, n_head, capacity, d_head, dtype=dtype, device=device) for _ in range(n_layers)]
+        self.v = [torch.empty(batch, n_head, capacity, d_head, dtype=dtype, device=device) for _ in range(n_layers)]
+        self.lengths = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.seen = 0                                   # host copy of the (common) length
+
+    def layer(self, i: int):
+        return self.k[i], self.v[i], self
+
+    def advance(self, n_tokens: int) -> None:
+        """Called once per model step, after every layer has appended its rows."""
+        self.lengths += n_tokens
+        self.seen += n_tokens
+
+
 class AlgebraicAttention(nn.Module):
     """Multi-head causal attention with rational softmax and ALiBi (reference algebraic_model.py:65-110).
 
@@ -71,12 +97,29 @@ class AlgebraicAttention(nn.Module):
         self.dropout = nn.Dropout(dropout)
         self.register_buffer("alibi_slopes", compute_alibi_slopes(n_head))
 
-    def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None, cache=None) -> torch.Tensor:
+        """``cache`` (an extension): ``KVCache.layer(i)``.  An empty cache is filled with this call's keys and values (the
+        prompt); afterwards ``x`` must hold one new token per sequence, which is appended and attends over the cache."""
         B, T, C = x.shape
         qkv = self.qkv(x).view(B, T, 3, self.n_head, self.d_head)
         if not qkv.is_cuda:
             raise RuntimeError("AlgebraicAttention: CUDA tensor required — this build has no CPU fallback")
+        if cache is not None and cache[2].seen > 0:
+            k_cache, v_cache, state = cache
+            if T != 1:
+                raise ValueError("a filled key/value cache takes one new token per sequence and step")
+            if state.seen >= state.capacity:
+                raise RuntimeError(f"key/value cache is full ({state.capacity} tokens)")
+            out = ops.attn_decode(qkv[:, 0, 0], qkv[:, 0, 1], qkv[:, 0, 2], k_cache, v_cache, state.lengths, self.alibi_slopes,
+                                  float(self.scale), float(EPS)).view(B, 1, C)
+            return self.dropout(self.out(out))
         out = RationalAttentionPackedFunction.apply(qkv, self.alibi_slopes, self.scale, EPS)     # [B,T,C]
+        if cache is not None:
+            k_cache, v_cache, state = cache
+            if T > state.capacity:
+                raise RuntimeError(f"the prompt ({T} tokens) does not fit the key/value cache ({state.capacity})")
+            k_cache[:, :, :T].copy_(qkv[:, :, 1].permute(0, 2, 1, 3))
+            v_cache[:, :, :T].copy_(qkv[:, :, 2].permute(0, 2, 1, 3))
         return self.dropout(self.out(out))
 
 
@@ -90,12 +133,12 @@ class AlgebraicBlock(nn.Module):
         self.norm1 = RationalMR(d_model)
         self.norm2 = RationalMR(d_model)
 
-    def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-        x = x + self.attn(self.norm1(x), mask)
+    def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None, cache=None) -> torch.Tensor:
+        x = x + self.attn(self.norm1(x), mask, cache)
         return x + self.ffn(self.norm2(x))
 
     def forward_deferred(self, x: torch.Tensor, pending: Optional[torch.Tensor],
-                         mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                         mask: Optional[torch.Tensor] = None, cache=None) -> Tuple[torch.Tensor, torch.Tensor]:
         """The same block with every residual addition fused into the normalisation that follows it.  ``pending`` is
         the previous block's feed-forward output that has not been added to ``x`` yet (None for the first block);
         returns (x, pending) in the same convention: the caller adds the last pending term (or fuses it into the
@@ -104,7 +147,7 @@ class AlgebraicBlock(nn.Module):
             y = self.norm1(x)
         else:
             x, y = add_mean_error_norm(x, pending, self.norm1.weight, self.norm1.eps)
-        x, y = add_mean_error_norm(x, self.attn(y, mask), self.norm2.weight, self.norm2.eps)
+        x, y = add_mean_error_norm(x, self.attn(y, mask, cache), self.norm2.weight, self.norm2.eps)
         return x, self.ffn(y)
 
 
@@ -175,20 +218,61 @@ class AlgebraicTransformerLM(nn.Module):
                                        ignore_index=-100)
         return (logits if return_logits else None), loss
 
+    def new_cache(self, batch: int, capacity: int) -> KVCache:
+        """An empty key/value cache for ``batch`` sequences of up to ``capacity`` tokens, in the model's dtype and device."""
+        attn = self.blocks[0].attn
+        w = self.head.weight
+        return KVCache(len(self.blocks), batch, attn.n_head, capacity, attn.d_head, w.dtype, w.device)
+
+    def cache_supported(self) -> bool:
+        """Whether the decode kernel covers this model's head size and dtype (else ``generate`` recomputes the prefix)."""
+        w = self.head.weight
+        return w.is_cuda and self.blocks[0].attn.d_head in KVCache.DECODE_HEAD_SIZES and w.dtype in KVCache.DECODE_DTYPES
+
+    @torch.no_grad()
+    def forward_cached(self, input_ids: torch.Tensor, cache: KVCache) -> torch.Tensor:
+        """Logits [B, V] of the LAST position of ``input_ids`` given the tokens already in ``cache``.  With an empty cache
+        ``input_ids`` is the prompt (any length); afterwards it is the one token per sequence that was sampled last.
+        Same arithmetic as ``forward`` on the concatenated sequence: keys and values of earlier positions do not
+        depend on later tokens (causal attention, relative bias), so they are kept instead of recomputed."""
+        x = self.embed(input_ids)
+        pending = None
+        for i, block in enumerate(self.blocks):
+            x, pending = block.forward_deferred(x, pending, None, cache.layer(i))
+        x, pending = x[:, -1:], pending[:, -1:]
+        _, y = add_mean_error_norm(x.contiguous(), pending.contiguous(), self.norm.weight, self.norm.eps)
+        cache.advance(input_ids.size(1))
+        return self.head(y)[:, -1, :]
+
     @torch.no_grad()
     def generate(self, idx: torch.Tensor, max_new_tokens: int, temperature: float = 1.0,
-                 top_k: Optional[int] = None) -> torch.Tensor:
-        """Sampling loop (reference algebraic_model.py:239-265): re-runs the forward per token, no KV cache."""
-        for _ in range(max_new_tokens):
-            idx_cond = idx if idx.size(1) <= self.block_size else idx[:, -self.block_size:]
-            logits, _ = self.forward(idx_cond)
-            logits = logits[:, -1, :]
+                 top_k: Optional[int] = None, use_cache: bool = True) -> torch.Tensor:
+        """Sampling loop (reference algebraic_model.py:239-265).  The reference re-runs the forward over the whole prefix
+        for every token; here (``use_cache``, an extension) the prompt runs once, its keys and values are kept, and each
+        new token costs one decode step.  The two agree as long as the reference would not crop the prefix to
+        ``block_size``; when it would (or the decode kernel does not cover the model), the reference's loop runs."""
+        def sample(logits):
             if temperature != 1.0:
                 logits = logits / temperature
             if top_k is not None:
                 kth, _ = torch.topk(logits, min(top_k, logits.size(-1)))
                 logits[logits < kth[:, [-1]]] = float("-inf")
-            idx = torch.cat((idx, torch.multinomial(F.softmax(logits, dim=-1), num_samples=1)), dim=1)
+            return torch.multinomial(F.softmax(logits, dim=-1), num_samples=1)
+
+        longest = idx.size(1) + max_new_tokens - 1          # the longest prefix a forward pass will see
+        if use_cache and max_new_tokens > 0 and idx.size(1) > 0 and longest <= self.block_size and self.cache_supported():
+            cache = self.new_cache(idx.size(0), longest)
+            logits = self.forward_cached(idx, cache)
+            for step in range(max_new_tokens):
+                nxt = sample(logits)
+                idx = torch.cat((idx, nxt), dim=1)
+                if step + 1 < max_new_tokens:
+                    logits = self.forward_cached(nxt, cache)
+            return idx
+        for _ in range(max_new_tokens):
+            idx_cond = idx if idx.size(1) <= self.block_size else idx[:, -self.block_size:]
+            logits, _ = self.forward(idx_cond)
+            idx = torch.cat((idx, sample(logits[:, -1, :])), dim=1)
         return idx
 
 

@@ -365,6 +365,37 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q_in, const Tensor& k_
   return {d_q, d_k, d_v};
 }
 
+// One decode step over a key/value cache: appends (k_new, v_new) at row n_cached[b] of the caches and returns the
+// attention of the new token over rows 0..n_cached[b].  q, k_new, v_new [B,H,D]; caches [B,H,capacity,D].
+Tensor attn_decode(const Tensor& q_in, const Tensor& k_new_in, const Tensor& v_new_in, Tensor& k_cache, Tensor& v_cache,
+                   const Tensor& n_cached, const Tensor& slopes, double scale, double eps) {
+  cuda_check({&q_in, &k_new_in, &v_new_in, &k_cache, &v_cache, &n_cached, &slopes});
+  TORCH_CHECK(q_in.dim() == 3 && q_in.sizes() == k_new_in.sizes() && q_in.sizes() == v_new_in.sizes(), "q, k_new, v_new must be [B,H,D] of one shape");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.sizes() == v_cache.sizes() && k_cache.size(0) == q_in.size(0) && k_cache.size(1) == q_in.size(1) &&
+              k_cache.size(3) == q_in.size(2), "the caches must be [B,H,capacity,D]");
+  TORCH_CHECK(q_in.scalar_type() == k_new_in.scalar_type() && q_in.scalar_type() == v_new_in.scalar_type() &&
+              q_in.scalar_type() == k_cache.scalar_type() && q_in.scalar_type() == v_cache.scalar_type(), "q, the new rows and the caches must share one dtype");
+  TORCH_CHECK(k_cache.stride(3) == 1 && v_cache.stride(3) == 1, "the caches need unit stride along the head dimension");
+  TORCH_CHECK(n_cached.scalar_type() == at::kInt && n_cached.dim() == 1 && n_cached.size(0) == q_in.size(0) && n_cached.is_contiguous(),
+              "n_cached must be a dense int32 tensor of one length per sequence");
+  auto unit = [](const Tensor& t) { return t.stride(-1) == 1 ? t : t.contiguous(); };
+  const Tensor q = unit(q_in), k_new = unit(k_new_in), v_new = unit(v_new_in);
+  const int64_t B = q.size(0), H = q.size(1), D = q.size(2);
+  const Tensor sl = slopes.to(at::kFloat).contiguous();
+  TORCH_CHECK(sl.numel() == H, "alibi_slopes must hold one slope per head");
+  Tensor out = at::empty({B, H, D}, q.options());
+  if (q.numel()) {
+    c10::cuda::CUDAGuard guard(q.device());
+    const std::array<int64_t, 2> qs{q.stride(0), q.stride(1)}, kns{k_new.stride(0), k_new.stride(1)}, vns{v_new.stride(0), v_new.stride(1)},
+        os{out.stride(0), out.stride(1)};
+    const auto kcs = strides3(k_cache), vcs = strides3(v_cache);
+    check(fat_attn_decode(q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), n_cached.data_ptr<int>(),
+                          sl.data_ptr<float>(), out.data_ptr(), int(B), int(H), int(k_cache.size(2)), int(D), qs.data(), kns.data(), vns.data(),
+                          os.data(), kcs.data(), vcs.data(), scale, eps, dtype_tag(q), status_word(q.get_device()).data_ptr<int>(), stream_of(q)));
+  }
+  return out;
+}
+
 }  // namespace
 
 TORCH_LIBRARY(algebraic, m) {
@@ -383,6 +414,8 @@ TORCH_LIBRARY(algebraic, m) {
         "bool token_major_out) -> (Tensor, Tensor, Tensor)");
   m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor out_lo, Tensor L, Tensor d_out, Tensor slopes, "
         "float scale, bool causal, float eps, int path) -> (Tensor, Tensor, Tensor)");
+  m.def("attn_decode(Tensor q, Tensor k_new, Tensor v_new, Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor n_cached, Tensor slopes, "
+        "float scale, float eps) -> Tensor");
   m.def("device_status(int device) -> Tensor", &device_status);
 }
 
@@ -400,4 +433,5 @@ TORCH_LIBRARY_IMPL(algebraic, CUDA, m) {
   m.impl("softmax_bwd", &softmax_bwd);
   m.impl("attn_fwd", &attn_fwd);
   m.impl("attn_bwd", &attn_bwd);
+  m.impl("attn_decode", &attn_decode);
 }

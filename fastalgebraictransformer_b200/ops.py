@@ -58,6 +58,13 @@ def attn_fwd(q: Tensor, k: Tensor, v: Tensor, slopes: Tensor, scale: float, caus
     return _alg.attn_fwd(q, k, v, slopes, float(scale), bool(causal), float(eps), int(path), bool(token_major_out))
 
 
+def attn_decode(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, v_cache: Tensor, n_cached: Tensor, slopes: Tensor,
+                scale: float, eps: float) -> Tensor:
+    """One decode step: appends the new key/value rows [B,H,D] at row n_cached[b] of the caches [B,H,capacity,D] and
+    returns the new token's attention [B,H,D] over rows 0..n_cached[b]; see include/fat_b200.h, fat_attn_decode."""
+    return _alg.attn_decode(q, k_new, v_new, k_cache, v_cache, n_cached, slopes, float(scale), float(eps))
+
+
 def attn_bwd_packed(qkv: Tensor, out: Tensor, out_lo: Tensor, L: Tensor, d_out: Tensor, slopes: Tensor,
                     scale: float, causal: bool, eps: float, path: int) -> Tensor:
     """Gradient of a packed [B,T,3,H,D] projection: d_q, d_k, d_v written side by side into one buffer."""
@@ -142,6 +149,11 @@ def _(q, k, v, slopes, scale, causal, eps, path, token_major_out):
 @torch.library.register_fake(f"{_NS}::attn_bwd")
 def _(q, k, v, out, out_lo, L, d_out, slopes, scale, causal, eps, path):
     return tuple(q.new_empty(q.shape) for _ in range(3))
+
+
+@torch.library.register_fake(f"{_NS}::attn_decode")
+def _(q, k_new, v_new, k_cache, v_cache, n_cached, slopes, scale, eps):
+    return q.new_empty(q.shape)
 
 
 # ----------------------------------------------------------------------------- autograd formulas

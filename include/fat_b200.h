@@ -57,13 +57,15 @@ enum fat_attn_path {
 /* Device-side status word.  The caller allocates one int32 per device, zeroes it, passes it to the
  * attention entry points and reads it back when it wants to know (reading needs a synchronise, so it
  * is left to the caller).  0 = nothing to report.  Otherwise:
- *   bits 24..28 = FAT_DEV_WAIT_TIMEOUT with a detail in bits 0..23: a bounded wait inside a kernel ran
+ *   bits 24..27 = FAT_DEV_WAIT_TIMEOUT with a detail in bits 0..23: a bounded wait inside a kernel ran
  *                 out and the kernel gave up (its outputs are undefined, the context stays usable);
+ *   bit 28      = fat_attn_decode found a sequence whose key/value cache has no room for the new row
+ *                 (or a negative length): nothing was appended and that sequence's output is zero;
  *   bit 29      = the tensor-core backward found |q| or |k| >= 65536 in a bfloat16 tensor.  It forms
  *                 d_q and d_k from float16 copies of q and k (see fat_attn_bwd), which were clamped to
  *                 65504: those two gradients are wrong for this call; use FAT_PATH_SIMT for such data;
  *   bit 30      = the fused backward found its shared memory misaligned and did nothing. */
-enum fat_device_status { FAT_DEV_OK = 0, FAT_DEV_WAIT_TIMEOUT = 1, FAT_DEV_F16_RANGE = 0x20000000,
+enum fat_device_status { FAT_DEV_OK = 0, FAT_DEV_WAIT_TIMEOUT = 1, FAT_DEV_CACHE_FULL = 0x10000000, FAT_DEV_F16_RANGE = 0x20000000,
                          FAT_DEV_SMEM_ALIGN = 0x40000000 };
 
 FAT_API int fat_version(void);
@@ -252,6 +254,28 @@ FAT_API int fat_attn_bwd(const void* q, const void* k, const void* v, const void
                  const int64_t* d_q_strides, const int64_t* d_k_strides, const int64_t* d_v_strides,
                  double scale, double eps, int causal, int dtype, int path,
                  int* status, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Decode step: rational attention of ONE new token per sequence over a key/value cache.
+ *     out[b,h,:] = sum_j f_j v_j / (sum_j f_j + eps),  f_j = sigma(q . k_j scale - slope_h (n_b - j))^4,  j = 0..n_b
+ * where n_b = n_cached[b] rows are already in the cache and the new token's key/value rows (k_new, v_new) are first
+ * appended at row n_b by the same launch (n_cached itself is not changed: the caller advances it once per model step,
+ * after all layers).  It equals row n_b of the causal forward over the n_b + 1 tokens, which is what the reference's
+ * generate() recomputes from scratch for every new token (algebraic_model.py:239-265: the whole prefix runs through
+ * forward() again; there is no cache in the reference).
+ *   q, k_new, v_new, out: [B, H, D] with element strides {batch, head} and unit stride along D;
+ *   k_cache, v_cache:     [B, H, capacity, D] with element strides {batch, head, token};
+ *   n_cached:             int32 [B] on the device (a CUDA graph of the step can be replayed as it grows).
+ * A sequence with n_cached[b] < 0 or >= capacity gets zeros, nothing is appended and bit 28 of the status word is set.
+ * Bit-reproducible from run to run (the partial sums of a key range meet in one fixed order).  Pointers 16-byte aligned,
+ * strides multiples of 16 bytes.  dtypes: F32, BF16, F16.  D in {32, 64, 128}.
+ * ---------------------------------------------------------------------------------- */
+FAT_API int fat_attn_decode(const void* q, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                 const int32_t* n_cached, const float* slopes, void* out,
+                 int B, int H, int capacity, int D,
+                 const int64_t* q_strides, const int64_t* k_new_strides, const int64_t* v_new_strides,
+                 const int64_t* out_strides, const int64_t* k_cache_strides, const int64_t* v_cache_strides,
+                 double scale, double eps, int dtype, int* status, void* stream);
 
 /* Which kernel family FAT_PATH_AUTO would pick for these arguments (FAT_PATH_SIMT or
  * FAT_PATH_TENSOR), for the forward (backward = 0) or the backward (backward = 1) launch.

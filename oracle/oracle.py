@@ -116,6 +116,18 @@ def rational_attention(q, k, v, slopes, scale, eps: float = EPS, causal: bool = 
     return torch.matmul(rational_softmax(_scores(q, k, slopes, scale, causal), eps), v)
 
 
+def rational_attention_last_row(q, k, v, slopes, scale, eps: float = EPS):
+    """Row T-1 of ``rational_attention`` computed on its own: q [B,H,D] is the query of the newest token, k, v [B,H,T,D]
+    hold every token including it.  The same arithmetic as tests.py:44-65 restricted to the last query row (nothing is
+    masked for it), i.e. what one step of a key/value-cached generate() needs; the reference itself recomputes all rows
+    (algebraic_model.py:239-265)."""
+    B, H, T, D = k.shape
+    s = torch.einsum("bhd,bhtd->bht", q, k) * scale
+    dist = (T - 1 - torch.arange(T)).to(torch.float32)
+    s = s + (-dist[None, None] * slopes.view(1, H, 1).to(torch.float32)).to(s.dtype)
+    return torch.einsum("bht,bhtd->bhd", rational_softmax(s, eps), v)
+
+
 def rational_attention_rowsum(q, k, slopes, scale, causal: bool = True):
     """L_i = sum_j sigma(s_ij)^4 without eps — the statistic the forward launcher returns
     next to the output (forward.py:150-159)."""

@@ -80,6 +80,9 @@ def test_attention(tag):
         assert norm_max_err(got, g[key]) < 1e-5, key
     L = oracle.rational_attention_rowsum(g["q"], g["k"], g["slopes"], g["scale"])
     assert L.shape == g["q"].shape[:3] and (L > 0).all()
+    # the last query row on its own (what a key/value-cached decode step computes) is the reference's last row
+    last = oracle.rational_attention_last_row(g["q"][:, :, -1], g["k"], g["v"], g["slopes"], g["scale"])
+    assert norm_max_err(last, g["out"][:, :, -1]) < TOL
 
 
 def test_lm_tiny():
