@@ -66,6 +66,35 @@ __device__ __forceinline__ void unpack(const uint4& raw, float (&f)[W]) {
   for (int i = 0; i < W; ++i) f[i] = Elem<T>::to_c(e[i]);
 }
 
+// Two neighbouring float32 values as one 64-bit register pair: fma.rn.f32x2 works on both at once.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void upk2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+
+// A 16-byte pack as W/2 float32 pairs.
+template <typename T> struct Pairs;
+template <> struct Pairs<__nv_bfloat16> {
+  static __device__ __forceinline__ void get(const uint4& raw, f32x2 (&o)[4]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = pk2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+  }
+};
+template <> struct Pairs<__half> {
+  static __device__ __forceinline__ void get(const uint4& raw, f32x2 (&o)[4]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); o[i] = pk2(f.x, f.y); }
+  }
+};
+template <> struct Pairs<float> {
+  static __device__ __forceinline__ void get(const uint4& raw, f32x2 (&o)[2]) {
+    o[0] = pk2(__uint_as_float(raw.x), __uint_as_float(raw.y));
+    o[1] = pk2(__uint_as_float(raw.z), __uint_as_float(raw.w));
+  }
+};
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kDecThreads, FAT_DEC_MINB)
 attn_decode_kernel(const DecodeParams p) {
@@ -103,17 +132,21 @@ attn_decode_kernel(const DecodeParams p) {
   }
   __syncthreads();                             // the row is read back below by threads of this CTA only
 
-  float qf[W];
+  static_assert(kUnroll == 4 && LPR >= 4, "the four-row transpose reduction below needs four rows and four lanes per row");
+  constexpr int P = W / 2;                     // float32 pairs per pack
+  f32x2 q2[P];
   {
     const uint4 raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1]) + c);
+    float qf[W];
     unpack<T, W>(raw, qf);
 #pragma unroll
-    for (int i = 0; i < W; ++i) qf[i] *= p.scale;
+    for (int i = 0; i < P; ++i) q2[i] = pk2(qf[2 * i] * p.scale, qf[2 * i + 1] * p.scale);
   }
   const float slope = p.slopes[h];
-  float acc[W], l = 0.f;
+  f32x2 acc2[P];
+  float l = 0.f;
 #pragma unroll
-  for (int i = 0; i < W; ++i) acc[i] = 0.f;
+  for (int i = 0; i < P; ++i) acc2[i] = pk2(0.f, 0.f);
 
   // Every thread moves the 16-byte pieces it will use itself from the caches into its own slots of a shared-memory ring
   // with asynchronous copies, kStages - 1 steps ahead of their use: the loads of several steps are in flight while one
@@ -121,51 +154,87 @@ attn_decode_kernel(const DecodeParams p) {
   // zeros without touching memory (source size 0) and weigh nothing.
   extern __shared__ uint4 ring[];              // [kStages][kUnroll][2][kDecThreads]
   constexpr int kRows = kStep * kUnroll;       // key rows a CTA handles per step
-  const int j_first = lo + warp * RPW + g;     // (lo + warp * RPW is the same for the whole warp, and so are the trip counts)
-  const int n_steps = hi > lo + warp * RPW ? (hi - (lo + warp * RPW) + kRows - 1) / kRows : 0;
+  const int w_first = lo + warp * RPW;         // the same for the whole warp, and so are the trip counts
+  const int j_first = w_first + g;
+  const int n_steps = hi > w_first ? (hi - w_first + kRows - 1) / kRows : 0;
+  const T* k_src = kc + j_first * p.kcs[2] + c * W;          // this thread's piece of the next step to be requested
+  const T* v_src = vc + j_first * p.vcs[2] + c * W;
+  const int64_t k_row = int64_t(kStep) * p.kcs[2], v_row = int64_t(kStep) * p.vcs[2];
+  const uint32_t ring0 = uint32_t(__cvta_generic_to_shared(ring + tid));
+  constexpr uint32_t kStageBytes = kUnroll * 2 * kDecThreads * 16, kPieceBytes = kDecThreads * 16;
   auto issue = [&](int step) {
     if (step < n_steps) {
-      uint4* slot = ring + size_t(step % kStages) * (kUnroll * 2 * kDecThreads) + tid;
+      const uint32_t dst = ring0 + uint32_t(step % kStages) * kStageBytes;
+      const bool whole = w_first + (step + 1) * kRows <= hi;                 // every row of the step is in range (warp-uniform)
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const int j = j_first + step * kRows + u * kStep;
-        const bool in = j < hi;
-        const T* ks = in ? kc + j * p.kcs[2] + c * W : kc;
-        const T* vs = in ? vc + j * p.vcs[2] + c * W : vc;
+        const bool in = whole || j_first + step * kRows + u * kStep < hi;
+        const T* ks = in ? k_src + u * k_row : kc;
+        const T* vs = in ? v_src + u * v_row : vc;
         const uint32_t bytes = in ? 16u : 0u;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(uint32_t(__cvta_generic_to_shared(slot + (2 * u) * kDecThreads))), "l"(ks), "r"(bytes) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(uint32_t(__cvta_generic_to_shared(slot + (2 * u + 1) * kDecThreads))), "l"(vs), "r"(bytes) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (2 * u) * kPieceBytes), "l"(ks), "r"(bytes) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (2 * u + 1) * kPieceBytes), "l"(vs), "r"(bytes) : "memory");
       }
+      k_src += kUnroll * k_row;
+      v_src += kUnroll * v_row;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");       // one group per step, empty or not: the waits count groups
   };
+  // After the transpose reduction lane c of a row group holds the score of row `my_u` of the step's four rows.
+  const bool up_a = (c & (LPR / 2)) != 0, up_b = (c & (LPR / 4)) != 0;
+  const int my_u = 2 * int(up_a) + int(up_b);
+  const int group0 = lane & ~(LPR - 1);
 #pragma unroll
   for (int s0 = 0; s0 < kStages - 1; ++s0) issue(s0);
   for (int step = 0; step < n_steps; ++step) {
     issue(step + kStages - 1);
     asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 1) : "memory");     // this step's pieces have landed
     const uint4* slot = ring + size_t(step % kStages) * (kUnroll * 2 * kDecThreads) + tid;
+    float d[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {        // this lane's share of the four dot products
+      f32x2 k2[P];
+      Pairs<T>::get(slot[(2 * u) * kDecThreads], k2);
+      f32x2 t = pk2(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < P; ++i) t = fma2(q2[i], k2[i], t);
+      float t0, t1;
+      upk2(t, t0, t1);
+      d[u] = t0 + t1;
+    }
+    // four sums over LPR lanes at the price of little more than one: halve the rows while doubling the lanes summed
+    const float a0 = (up_a ? d[2] : d[0]) + __shfl_xor_sync(0xffffffffu, up_a ? d[0] : d[2], LPR / 2);
+    const float a1 = (up_a ? d[3] : d[1]) + __shfl_xor_sync(0xffffffffu, up_a ? d[1] : d[3], LPR / 2);
+    float x = (up_b ? a1 : a0) + __shfl_xor_sync(0xffffffffu, up_b ? a0 : a1, LPR / 4);
+#pragma unroll
+    for (int o = LPR / 8; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    const int j = j_first + step * kRows + my_u * kStep;
+    const float s = x - slope * float(n - j);
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fabsf(s) + 1.0f));
+    const float sig = fmaf(s * r, 0.5f, 0.5f);
+    const float sg2 = sig * sig;
+    const float f = j < hi ? sg2 * sg2 : 0.f;
+    l += f;                                    // (every row is counted by LPR/4 lanes; undone after the loop)
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int j = j_first + step * kRows + u * kStep;
-      float kf[W], vf[W];
-      unpack<T, W>(slot[(2 * u) * kDecThreads], kf);
-      unpack<T, W>(slot[(2 * u + 1) * kDecThreads], vf);
-      float dot = 0.f;
+      const float fu = __shfl_sync(0xffffffffu, f, group0 + (u >> 1) * (LPR / 2) + (u & 1) * (LPR / 4));
+      const f32x2 f2 = pk2(fu, fu);
+      f32x2 v2[P];
+      Pairs<T>::get(slot[(2 * u + 1) * kDecThreads], v2);
 #pragma unroll
-      for (int i = 0; i < W; ++i) dot = fmaf(qf[i], kf[i], dot);
-#pragma unroll
-      for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float s = dot - slope * float(n - j);
-      const float sig = 0.5f * (s / (fabsf(s) + 1.0f) + 1.0f);
-      const float s2 = sig * sig;
-      const float f = j < hi ? s2 * s2 : 0.f;
-      l += f;
-#pragma unroll
-      for (int i = 0; i < W; ++i) acc[i] = fmaf(f, vf[i], acc[i]);
+      for (int i = 0; i < P; ++i) acc2[i] = fma2(f2, v2[i], acc2[i]);
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  float acc[W];
+#pragma unroll
+  for (int i = 0; i < P; ++i) upk2(acc2[i], acc[2 * i], acc[2 * i + 1]);
+#pragma unroll
+  for (int o = LPR / 8; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);   // lanes that hold the other rows' weights
+  l += __shfl_xor_sync(0xffffffffu, l, LPR / 4);
+  l += __shfl_xor_sync(0xffffffffu, l, LPR / 2);
+  l *= 4.0f / float(LPR);
   // rows of one warp -> one row
 #pragma unroll
   for (int o = LPR; o < 32; o <<= 1) {
