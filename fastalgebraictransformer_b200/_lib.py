@@ -47,6 +47,10 @@ PROTOTYPES = {
     "fat_attn_bwd_workspace_bytes": (_sz, [_int] * 6),
     "fat_attn_bwd": (_int, [_ptr] * 12 + [_sz] + [_int] * 4 + [_p64] * 8 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
     "fat_attn_select_path": (_int, [_int] * 6),
+    "fat_key_mask_words": (_int, [_int]),
+    "fat_pack_key_mask": (_int, [_ptr, _ptr, _int, _int, _i64, _i64, _ptr]),
+    "fat_attn_fwd_masked": (_int, [_ptr] * 8 + [_int] * 4 + [_p64] * 4 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
+    "fat_attn_bwd_masked": (_int, [_ptr] * 13 + [_sz] + [_int] * 4 + [_p64] * 8 + [_dbl, _dbl, _int, _int, _int, _ptr, _ptr]),
     "fat_attn_decode": (_int, [_ptr] * 8 + [_int] * 4 + [_p64] * 6 + [_dbl, _dbl, _int, _ptr, _ptr]),
 }
 

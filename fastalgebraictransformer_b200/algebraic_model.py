@@ -82,8 +82,9 @@ class KVCache:
 class AlgebraicAttention(nn.Module):
     """Multi-head causal attention with rational softmax and ALiBi (reference algebraic_model.py:65-110).
 
-    ``mask`` is accepted for signature parity and ignored, as the reference's CUDA path does
-    (algebraic_model.py:93-104)."""
+    ``mask`` [B, T] (0 = padding) takes the padded keys out of every query's sum, as the reference's PyTorch path does
+    (algebraic_model.py:128-131: their scores are filled with -1e4); the reference's Triton path drops the argument
+    (algebraic_model.py:93-104), so on CUDA this is where the two differ: here the mask counts."""
 
     def __init__(self, d_model: int, n_head: int, dropout: float = 0.1):
         super().__init__()
@@ -113,7 +114,9 @@ class AlgebraicAttention(nn.Module):
             out = ops.attn_decode(qkv[:, 0, 0], qkv[:, 0, 1], qkv[:, 0, 2], k_cache, v_cache, state.lengths, self.alibi_slopes,
                                   float(self.scale), float(EPS)).view(B, 1, C)
             return self.dropout(self.out(out))
-        out = RationalAttentionPackedFunction.apply(qkv, self.alibi_slopes, self.scale, EPS)     # [B,T,C]
+        if mask is not None and cache is not None:
+            raise ValueError("the key/value cache takes no padding mask")
+        out = RationalAttentionPackedFunction.apply(qkv, self.alibi_slopes, self.scale, EPS, mask)     # [B,T,C]
         if cache is not None:
             k_cache, v_cache, state = cache
             if T > state.capacity:
@@ -187,6 +190,8 @@ class AlgebraicTransformerLM(nn.Module):
         extension; needs ``labels``) is for training loops that only use the loss: the head GEMM and the loss then run one
         sequence at a time and neither the [B, T, V] logits nor their gradient are ever materialised; ``logits`` is None."""
         x = self.embed(input_ids)
+        if attention_mask is not None and not isinstance(attention_mask, ops.PackedKeyMask):
+            attention_mask = ops.PackedKeyMask(attention_mask)          # packed to bits once for all layers
         if self.gradient_checkpointing and self.training:
             for block in self.blocks:
                 x = checkpoint(block, x, attention_mask, use_reentrant=False)

@@ -20,7 +20,16 @@ struct AttnParams {
   int causal;
   int deterministic;                          // tensor path backward: two kernels without atomics instead of the fused one
   int* status;
+  // optional padding mask over the keys: bit (j & 31) of key_mask[b * mask_words + (j >> 5)] set = key j of batch
+  // element b takes part; mask_words = 4 * ceil(T / 128), bits from T on are clear.  Null: every key takes part.
+  const uint32_t* key_mask;
+  int mask_words;
 };
+
+// Whether key `col` (< T) of batch element b takes part.
+__device__ __forceinline__ bool key_kept(const AttnParams& p, int b, int col) {
+  return !p.key_mask || ((__ldg(p.key_mask + int64_t(b) * p.mask_words + (col >> 5)) >> (col & 31)) & 1u);
+}
 
 // SIMT family (attn_simt.cu)
 int attn_fwd_simt(const AttnParams& p, int dtype, cudaStream_t st);

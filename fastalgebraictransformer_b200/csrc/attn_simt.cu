@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(NT) attn_fwd_simt_kernel(AttnParams p, bool ve
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int col = k0 + tx + 16 * j;
-        const bool live = col < p.T && row < p.T && (!p.causal || col <= row);
+        const bool live = col < p.T && row < p.T && (!p.causal || col <= row) && key_kept(p, b, col);
         const float f = live ? score_terms(acc[i][j], p.scale, slope, row, col).f : 0.f;
         l[i] += f;
         Ps[(ty + 16 * i) * LDP + tx + 16 * j] = f;
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(NT) attn_bwd_dq_simt_kernel(AttnParams p, bool
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int col = k0 + tx + 16 * j;
-        const bool live = col < p.T && row < p.T && (!p.causal || col <= row);
+        const bool live = col < p.T && row < p.T && (!p.causal || col <= row) && key_kept(p, b, col);
         dSs[rl * LDP + tx + 16 * j] =
             live ? score_terms(s[i][j], p.scale, slope, row, col).k * (dp[i][j] - dlt) * inv : 0.f;
       }
@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(NT) attn_bwd_dkv_simt_kernel(AttnParams p, boo
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int cl = tx + 16 * j, col = k0 + cl;
-        const bool live = col < p.T && row < p.T && (!p.causal || col <= row);
+        const bool live = col < p.T && row < p.T && (!p.causal || col <= row) && key_kept(p, b, col);
         Score sc = score_terms(s[i][j], p.scale, slope, row, col);
         PsT[cl * LDP + rl] = live ? sc.f * inv : 0.f;
         dSsT[cl * LDP + rl] = live ? sc.k * (dp[i][j] - dlt) * inv : 0.f;

@@ -44,6 +44,16 @@ constexpr float kOpScale = 256.0f;
 constexpr float kDsScale = 4.0f;         // fused and key-major kernels: dS_stored = 4 kDsScale c dS
 constexpr float kDsScaleQ = 64.0f;       // query-major d_q kernel: dS_stored = 4 kDsScaleQ c (L+eps) dS (1/(L+eps) is applied to the rows of d_q afterwards)
 constexpr int kStatusF16Range = 0x20000000;
+// Bias of a key that the padding mask takes out, in the kernels where a thread owns a key: sigma(-1e6) = 2.5e-7, so its
+// sigma^4 and its gradient factor vanish against every kept key's (the reference fills such scores with -1e4).
+constexpr float kMaskedKeyBias = -1.0e6f;
+// With a padding mask hundreds of queries can share a handful of keys with nearly equal weights; rounded to bfloat16's 8
+// significand bits those weights leave d_v = P^T dO a few elements in 10^5 outside the 16-bit bar (the errors of one key's
+// column no longer average out).  Masked bfloat16 launches therefore hand P^T to the d_v product as value + residual.
+template <typename T> constexpr bool kMaskedHiLo = std::is_same<T, __nv_bfloat16>::value;
+__device__ __forceinline__ uint32_t pack_residual(float p0, float p1, uint32_t packed_bf16) {
+  return Pack16<__nv_bfloat16>::pack(p0 - __uint_as_float(packed_bf16 << 16), p1 - __uint_as_float(packed_bf16 & 0xffff0000u));
+}
 
 // c and 1/c from the bits of max|dO| (a float32 with the sign cleared)
 __device__ __forceinline__ void dout_scale(uint32_t max_bits, float& c, float& rc) {
@@ -336,13 +346,17 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
       const float sl = (!p.causal && j > qt) ? -slope : slope;
       const float base = sl * float(j * BLK - row);
       const f32x2 step2 = pk2(2.f * sl, 2.f * sl);
-      auto phase_a = [&](auto ABS) {
+      // KM: a padding mask over the keys is in force (one 32-bit word per chunk, bit set = the key takes part)
+      const uint32_t* keep_words = p.key_mask ? p.key_mask + int64_t(b) * p.mask_words + j * (BLK / 32) : nullptr;
+      auto phase_a = [&](auto ABS, auto KM) {
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
           uint32_t sreg[32];
           tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
-          tmem_wait_ld_regs(sreg);
           const int col0 = kColsPerGroup * w + 32 * c;
+          uint32_t keep = 0xffffffffu;
+          if constexpr (decltype(KM)::value) keep = __ldg(keep_words + (col0 >> 5));
+          tmem_wait_ld_regs(sreg);
           f32x2 bias2 = pk2(fmaf(sl, float(col0), base), fmaf(sl, float(col0 + 1), base));
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -356,11 +370,20 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ DqMaps maps, const AttnParams p) {
             if (rcp_shared(i, FAT_RCP_SHARE_BWD)) score_fg2<false, true>(acc2, scale2, b2, half2, F2, g2);
             else            score_fg2<false, false>(acc2, scale2, b2, half2, F2, g2);
             bias2 = add2(bias2, step2);
+            if constexpr (decltype(KM)::value) {
+              float g0, g1;
+              upk2(g2, g0, g1);
+              if (!(keep & (1u << (2 * i)))) g0 = 0.f;
+              if (!(keep & (2u << (2 * i)))) g1 = 0.f;
+              g2 = pk2(g0, g1);
+            }
             gq[16 * c + i] = g2;
           }
         }
       };
-      if (!p.causal && j == qt) phase_a(std::true_type{}); else phase_a(std::false_type{});
+      const bool abs_tile = !p.causal && j == qt;
+      if (keep_words) { if (abs_tile) phase_a(std::true_type{}, std::true_type{}); else phase_a(std::false_type{}, std::true_type{}); }
+      else            { if (abs_tile) phase_a(std::true_type{}, std::false_type{}); else phase_a(std::false_type{}, std::false_type{}); }
       tc_fence_before();
       mbar_arrive(&sm.s_free);
       // ---- phase B: dS = g (dP - Delta), packed over dP
@@ -440,7 +463,9 @@ struct DkvSmem {
 struct DkvMaps { CUtensorMap q, dout, k, v, dk, dv; };
 
 // TMEM columns: S^T / packed P^T [0,128)   dP'^T / packed dS^T [128,256)   dV [256,256+D)   dK [256+D,256+2D)
-template <typename T, int D>
+// MASKED: a padding mask over the keys is in force (p.key_mask is set).  A separate instantiation, so that the kernel of
+// the unmasked case carries none of it.
+template <typename T, int D, bool MASKED>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -513,7 +538,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
         const uint32_t ph1 = ((it + 1) / kBwdStages) & 1;
         if (!(ok = g.wait(&sm.p_full, it & 1, 83))) break;
         tc_fence_after();
-        issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn[st], idesc_dv, it > 0);      // dV += P^T dO
+        if constexpr (MASKED && kMaskedHiLo<T>) issue_gemm_tn_hilo(tV, tS, dod_mn[st], idesc_dv, it > 0);
+        else issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn[st], idesc_dv, it > 0);      // dV += P^T dO
         mma_commit(&sm.do_empty[st]);
         if (it + 1 < n) {
           if (!(ok = g.wait(&sm.q_full[st1], ph1, 84))) break;
@@ -538,6 +564,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
     const int w = warp >> 2;                                 // query-column slice of this warpgroup
     const int r = tid & (BLK - 1);                           // key row inside the tile == TMEM lane
     const int key = kt * BLK + r;
+    const bool kept = !MASKED || key >= p.T || key_kept(p, b, key);     // a key the padding mask takes out gets a bias that zeroes it
+    constexpr bool hilo = MASKED && kMaskedHiLo<T>;
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
     const float slope = p.slopes[h], scale = p.scale;
     const f32x2 scale2 = pk2(scale, scale), half2 = pk2(1.0f, 1.0f);
@@ -556,14 +584,15 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
       // -slope for queries before it (non-causal only); MODE 1: causal diagonal tile (queries before the key are masked),
       // MODE 2: non-causal diagonal tile (absolute value element by element, nothing masked)
       const float sl = (!p.causal && qi < kt) ? -slope : slope;
-      const float base = sl * float(key - qi * BLK);
+      const float base = (!MASKED || kept) ? sl * float(key - qi * BLK) : kMaskedKeyBias;
       const f32x2 step2 = pk2(-2.f * sl, -2.f * sl);
       const float* iv = sm.inv[st];
-      auto phase_a = [&](auto MODE) {          // the diagonal tile gets its own copy (no run-time test in the unrolled body)
+      auto phase_a = [&](auto MODE, auto HL) { // the diagonal tile gets its own copy (no run-time test in the unrolled body)
         constexpr int kMode = decltype(MODE)::value;
+        constexpr bool kHiLo = decltype(HL)::value && std::is_same<T, __nv_bfloat16>::value;
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
-          uint32_t sreg[32], preg[16];
+          uint32_t sreg[32], preg[16], lreg[kHiLo ? 16 : 1];
           tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
           tmem_wait_ld_regs(sreg);
           const int col0 = kColsPerGroup * w + 32 * c;
@@ -595,13 +624,19 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ DkvMaps maps, const AttnParams p)
             }
             gq[16 * c + i] = g2;
             preg[i] = Pack16<T>::pack(p0, p1);
+            if constexpr (kHiLo) lreg[i] = pack_residual(p0, p1, preg[i]);
           }
-          tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
+          if constexpr (kHiLo) {
+            tmem_st16(tmem_addr(tS, lane_base, col0), preg);
+            tmem_st16(tmem_addr(tS, lane_base, col0 + 16), lreg);
+          } else {
+            tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
+          }
         }
       };
-      if (!diag)         phase_a(std::integral_constant<int, 0>{});
-      else if (p.causal) phase_a(std::integral_constant<int, 1>{});
-      else               phase_a(std::integral_constant<int, 2>{});
+      if (!diag)         phase_a(std::integral_constant<int, 0>{}, std::integral_constant<bool, hilo>{});
+      else if (p.causal) phase_a(std::integral_constant<int, 1>{}, std::integral_constant<bool, hilo>{});
+      else               phase_a(std::integral_constant<int, 2>{}, std::integral_constant<bool, hilo>{});
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full);
@@ -700,7 +735,9 @@ struct FusedSmem {
 
 struct FusedMaps { CUtensorMap q, dout, k, v, dk, dv, dq_acc; };    // dq_acc: float32, 32-row boxes
 
-template <typename T, int D>
+// MASKED: a padding mask over the keys is in force (p.key_mask is set).  A separate instantiation, so that the kernel of
+// the unmasked case carries none of it.
+template <typename T, int D, bool MASKED>
 __global__ void __launch_bounds__(kFusedThreads, 1)
 attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParams p) {
   static_assert((D == 128 || D == 64) && kEwGroups == 2, "laid out for D = 64 or 128 and two element-wise warpgroups");
@@ -812,7 +849,8 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
             if (i + 1 < n && !(ok = g.wait_polling(&sm.q_full[st1], ((i + 1) >> 1) & 1, 154))) break;
             if (!(ok = g.wait_polling(&sm.p_full, i & 1, 152))) break;
             tc_fence_after();
-            issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn, idesc_dv, i > 0);               // dV += P^T dO
+            if constexpr (MASKED && kMaskedHiLo<T>) issue_gemm_tn_hilo(tV, tS, dod_mn, idesc_dv, i > 0);
+            else issue_gemm_tn<kColsPerGroup>(tV, tS, dod_mn, idesc_dv, i > 0);               // dV += P^T dO
             mma_commit(&sm.do_empty);                                                // X's share of releasing dO(i)
             if (i + 1 < n) {
               issue_gemm_nt<D>(tS, kd, qd[st1], idesc_s);                                // S^T of the next query tile
@@ -928,6 +966,8 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
     const int w = warp >> 2;                                 // query columns [64w, 64w+64) of each step
     const int r = tid & (BLK - 1);                           // key row inside the tile == TMEM lane
     const int key = kt * BLK + r;
+    const bool kept = !MASKED || key >= p.T || key_kept(p, b, key);     // a key the padding mask takes out gets a bias that zeroes it
+    constexpr bool hilo = MASKED && kMaskedHiLo<T>;
     const uint32_t lane_base = uint32_t(warp & 3) * 32;
     const float slope = p.slopes[h], scale = p.scale;
     const f32x2 scale2 = pk2(scale, scale), one2 = pk2(1.0f, 1.0f);
@@ -946,14 +986,15 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
       // -slope for queries before it (non-causal only); MODE 1: causal diagonal tile (queries before the key are masked),
       // MODE 2: non-causal diagonal tile (absolute value element by element, nothing masked)
       const float sl = (!p.causal && qi < kt) ? -slope : slope;
-      const float base = sl * float(key - qi * BLK);
+      const float base = (!MASKED || kept) ? sl * float(key - qi * BLK) : kMaskedKeyBias;
       const f32x2 step2 = pk2(-2.f * sl, -2.f * sl);
       const float* iv = sm.inv[st];
-      auto phase_a = [&](auto MODE) {          // the diagonal tile gets its own copy (no run-time test in the unrolled body)
+      auto phase_a = [&](auto MODE, auto HL) { // the diagonal tile gets its own copy (no run-time test in the unrolled body)
         constexpr int kMode = decltype(MODE)::value;
+        constexpr bool kHiLo = decltype(HL)::value && std::is_same<T, __nv_bfloat16>::value;
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
-          uint32_t sreg[32], preg[16];
+          uint32_t sreg[32], preg[16], lreg[kHiLo ? 16 : 1];
           tmem_ld32(tmem_addr(tS, lane_base, kColsPerGroup * w + 32 * c), sreg);
           tmem_wait_ld_regs(sreg);
           const int col0 = kColsPerGroup * w + 32 * c;
@@ -986,13 +1027,19 @@ attn_bwd_fused_tc_kernel(const __grid_constant__ FusedMaps maps, const AttnParam
             }
             gq[16 * c + e] = g2;
             preg[e] = Pack16<T>::pack(p0, p1);
+            if constexpr (kHiLo) lreg[e] = pack_residual(p0, p1, preg[e]);
           }
-          tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
+          if constexpr (kHiLo) {
+            tmem_st16(tmem_addr(tS, lane_base, col0), preg);
+            tmem_st16(tmem_addr(tS, lane_base, col0 + 16), lreg);
+          } else {
+            tmem_st16(tmem_addr(tS, lane_base, packed_col(w, c)), preg);
+          }
         }
       };
-      if (!diag)         phase_a(std::integral_constant<int, 0>{});
-      else if (p.causal) phase_a(std::integral_constant<int, 1>{});
-      else               phase_a(std::integral_constant<int, 2>{});
+      if (!diag)         phase_a(std::integral_constant<int, 0>{}, std::integral_constant<bool, hilo>{});
+      else if (p.causal) phase_a(std::integral_constant<int, 1>{}, std::integral_constant<bool, hilo>{});
+      else               phase_a(std::integral_constant<int, 2>{}, std::integral_constant<bool, hilo>{});
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_full);
@@ -1155,14 +1202,15 @@ int launch_bwd_split(const AttnParams& p, cudaStream_t st) {
   mk.q = mq.q; mk.dout = mq.dout; mk.k = mq.k; mk.v = mq.v;
   if (int rc = launch_prepare<T, D>(p, st, nullptr, true)) return rc;
   if (int rc = launch_main(attn_bwd_dq_tc_kernel<T, D>, mq, p, sizeof(DqSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dq_tc")) return rc;
-  return launch_main(attn_bwd_dkv_tc_kernel<T, D>, mk, p, sizeof(DkvSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dkv_tc");
+  if (p.key_mask) return launch_main(attn_bwd_dkv_tc_kernel<T, D, true>, mk, p, sizeof(DkvSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dkv_tc");
+  return launch_main(attn_bwd_dkv_tc_kernel<T, D, false>, mk, p, sizeof(DkvSmem<D>) + 1024, kBwdThreads, st, "attn_bwd_dkv_tc");
 }
 
 // Fused backward: prepare (which also clears the float32 d_q accumulator), fused kernel, convert d_q.
 template <typename T, int D>
 int launch_bwd_fused(const AttnParams& p, cudaStream_t st) {
   float* dq_acc = ws_dq_acc(p);
-  auto kern = attn_bwd_fused_tc_kernel<T, D>;
+  auto kern = p.key_mask ? attn_bwd_fused_tc_kernel<T, D, true> : attn_bwd_fused_tc_kernel<T, D, false>;
   cudaFuncAttributes fa;
   if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
       fa.numRegs * kFusedThreads < 256 * kFusedRegsEw + 128 * kFusedRegsDrain + 128 * kFusedRegsAux) {

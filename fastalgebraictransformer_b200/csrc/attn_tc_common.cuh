@@ -119,6 +119,19 @@ __device__ __forceinline__ void issue_gemm_tn(uint32_t d_tmem, uint32_t a_tmem, 
   }
 }
 
+// The same product with the packed A kept as a bfloat16 value plus its rounding residual (two 16-bit pieces, 16 more
+// significand bits for eight more MMAs).  Layout: the 32 elements of score chunk j (elements [32 j, 32 j + 32)) occupy
+// the chunk's own 32 columns, values in the first 16, residuals in the last 16, so that a thread can store both as soon
+// as it has read that chunk.
+__device__ __forceinline__ void issue_gemm_tn_hilo(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int s = 0; s < BLK / 16; ++s) {
+    const uint32_t acol = uint32_t(32 * (s / 2) + 8 * (s % 2));
+    mma_ts(d_tmem, a_tmem + acol, bdesc + ((s * 2048) >> 4), idesc, accumulate || s > 0);
+    mma_ts(d_tmem, a_tmem + acol + 16, bdesc + ((s * 2048) >> 4), idesc, true);
+  }
+}
+
 // ------------------------------------------------------------------ packed fp32 pairs (sm_100 FFMA2 / FMUL2 / FADD2)
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 pk2(float lo, float hi) {

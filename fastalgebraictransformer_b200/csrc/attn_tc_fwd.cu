@@ -75,9 +75,9 @@ struct FwdMaps { CUtensorMap q, k, v, out, out_lo; };
 // on its side of the diagonal).  MASK: keys with column index > lim get no weight (causal: the diagonal tile, lim = the
 // thread's row; non-causal: the last key tile of a ragged sequence, lim = its last valid column).  ABS: the tile
 // straddles the diagonal of a non-causal problem, the bias is -|slope * c + base|.
-template <bool MASK, bool ABS>
-__device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32_t (&preg)[16], int c, int lim, f32x2 scale2,
-                                              f32x2 four2, f32x2 step2, float slope, float base, f32x2& l2) {
+template <bool MASK, bool ABS, bool KM>
+__device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32_t (&preg)[16], int c, int lim, uint32_t keep,
+                                              f32x2 scale2, f32x2 four2, f32x2 step2, float slope, float base, f32x2& l2) {
   f32x2 bias2 = pk2(fmaf(slope, float(c * 32), base), fmaf(slope, float(c * 32 + 1), base));
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
@@ -98,7 +98,11 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32
     f32x2 f2 = mul2(q2, q2);                               // (8 sigma)^4 = 4096 sigma^4
     float f0, f1;
     upk2(f2, f0, f1);
-    if (MASK) {
+    if (KM) {                                              // `keep` already holds the limit, if there is one
+      if (!(keep & (1u << (2 * i)))) f0 = 0.f;
+      if (!(keep & (2u << (2 * i)))) f1 = 0.f;
+      f2 = pk2(f0, f1);
+    } else if (MASK) {
       if (c * 32 + 2 * i > lim) f0 = 0.f;
       if (c * 32 + 2 * i + 1 > lim) f1 = 0.f;
       f2 = pk2(f0, f1);
@@ -112,16 +116,26 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&sreg)[32], uint32
 // index c0).  The packed P of chunk c lands on columns [16 c, 16 c + 16) counted from `trow`, i.e. over scores
 // this thread has already taken into registers.  The chunk loop is kept rolled (the body is ~400 instructions;
 // unrolled four times it no longer fits the instruction cache).
-template <bool MASK, bool ABS>
+// KM: a padding mask over the keys is in force; `keep_words` points at the four 32-bit words of this key tile (bit set =
+// the key takes part) and MASK's limit, if any, is folded into the word of each chunk.
+template <bool MASK, bool ABS, bool KM = false>
 __device__ __forceinline__ void softmax_tile(uint32_t trow, int c0, int lim, f32x2 scale2, f32x2 four2, f32x2 step2,
-                                             float slope, float base, f32x2& l2) {
+                                             float slope, float base, f32x2& l2, const uint32_t* keep_words = nullptr) {
   uint32_t sreg[32];
   tmem_ld32(trow, sreg);
 #pragma unroll 1
   for (int c = 0; c < kChunks; ++c) {
+    uint32_t keep = 0xffffffffu;
+    if (KM) {
+      keep = __ldg(keep_words + c0 + c);
+      if (MASK) {
+        const int rel = lim - (c0 + c) * 32;                 // last column of this chunk that may be seen
+        keep &= rel >= 31 ? 0xffffffffu : (rel < 0 ? 0u : (2u << rel) - 1u);
+      }
+    }
     tmem_wait_ld_regs(sreg);
     uint32_t preg[16];
-    softmax_chunk<MASK, ABS>(sreg, preg, c0 + c, lim, scale2, four2, step2, slope, base, l2);
+    softmax_chunk<MASK, ABS, KM>(sreg, preg, c0 + c, lim, keep, scale2, four2, step2, slope, base, l2);
     if (c + 1 < kChunks) tmem_ld32(trow + (c + 1) * 32, sreg);      // next chunk in flight while this one is stored
     tmem_st16(trow + c * 16, preg);
   }
@@ -301,7 +315,13 @@ attn_fwd_tc_kernel(const __grid_constant__ FwdMaps maps, const AttnParams p) {
       const float base = sl * float(j * BLK - row);
       const f32x2 step2 = pk2(2.f * sl, 2.f * sl);
       const uint32_t trow = tmem_addr(tmem, lane_base, t * BLK + part * kColsPerWg);
-      if (p.causal) {
+      if (p.key_mask) {
+        // (bits of keys beyond T are clear, so a ragged last tile needs no limit of its own)
+        const uint32_t* kw = p.key_mask + int64_t(b) * p.mask_words + j * (BLK / 32);
+        if (p.causal && diag) softmax_tile<true, false, true>(trow, part * kChunks, r, scale2, four2, step2, sl, base, l2, kw);
+        else if (diag)        softmax_tile<false, true, true>(trow, part * kChunks, 0, scale2, four2, step2, sl, base, l2, kw);
+        else                  softmax_tile<false, false, true>(trow, part * kChunks, 0, scale2, four2, step2, sl, base, l2, kw);
+      } else if (p.causal) {
         if (diag) softmax_tile<true, false>(trow, part * kChunks, r, scale2, four2, step2, sl, base, l2);
         else      softmax_tile<false, false>(trow, part * kChunks, r, scale2, four2, step2, sl, base, l2);
       } else {

@@ -117,6 +117,14 @@ int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slope
                  int B, int H, int T, int D,
                  const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os,
                  double scale, double eps, int causal, int dtype, int path, int* status, void* stream) {
+  return fat_attn_fwd_masked(q, k, v, slopes, nullptr, out, out_lo, L, B, H, T, D, qs, ks, vs, os, scale, eps, causal, dtype, path,
+                             status, stream);
+}
+
+int fat_attn_fwd_masked(const void* q, const void* k, const void* v, const float* slopes, const uint32_t* key_mask_bits,
+                        void* out, void* out_lo, float* L, int B, int H, int T, int D,
+                        const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os,
+                        double scale, double eps, int causal, int dtype, int path, int* status, void* stream) {
   if (int rc = check_attn_shape("attn_fwd", B, H, T, D)) return rc;
   if (dtype != FAT_F32 && dtype != FAT_BF16 && dtype != FAT_F16) { set_error("attn_fwd: unsupported dtype tag %d", dtype); return FAT_ERR_DTYPE; }
   if (B == 0 || T == 0) return FAT_OK;
@@ -131,6 +139,7 @@ int fat_attn_fwd(const void* q, const void* k, const void* v, const float* slope
   p.B = B; p.H = H; p.T = T; p.D = D;
   copy3(p.qs, qs); copy3(p.ks, ks); copy3(p.vs, vs); copy3(p.os, os);
   p.scale = float(scale); p.eps = float(eps); p.causal = causal != 0; p.status = status;
+  p.key_mask = key_mask_bits; p.mask_words = fat_key_mask_words(T);
   return sel == FAT_PATH_TENSOR ? attn_fwd_tc(p, dtype, (cudaStream_t)stream) : attn_fwd_simt(p, dtype, (cudaStream_t)stream);
 }
 
@@ -147,6 +156,16 @@ int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, c
                  const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, const int64_t* dos,
                  const int64_t* dqs, const int64_t* dks, const int64_t* dvs,
                  double scale, double eps, int causal, int dtype, int path, int* status, void* stream) {
+  return fat_attn_bwd_masked(q, k, v, out, out_lo, L, d_out, slopes, nullptr, d_q, d_k, d_v, workspace, workspace_bytes, B, H, T, D,
+                             qs, ks, vs, os, dos, dqs, dks, dvs, scale, eps, causal, dtype, path, status, stream);
+}
+
+int fat_attn_bwd_masked(const void* q, const void* k, const void* v, const void* out, const void* out_lo, const float* L,
+                        const void* d_out, const float* slopes, const uint32_t* key_mask_bits, void* d_q, void* d_k, void* d_v,
+                        void* workspace, size_t workspace_bytes, int B, int H, int T, int D,
+                        const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, const int64_t* dos,
+                        const int64_t* dqs, const int64_t* dks, const int64_t* dvs,
+                        double scale, double eps, int causal, int dtype, int path, int* status, void* stream) {
   if (int rc = check_attn_shape("attn_bwd", B, H, T, D)) return rc;
   if (dtype != FAT_F32 && dtype != FAT_BF16 && dtype != FAT_F16) { set_error("attn_bwd: unsupported dtype tag %d", dtype); return FAT_ERR_DTYPE; }
   if (B == 0 || T == 0) return FAT_OK;
@@ -174,6 +193,7 @@ int fat_attn_bwd(const void* q, const void* k, const void* v, const void* out, c
   copy3(p.dqs, dqs); copy3(p.dks, dks); copy3(p.dvs, dvs);
   p.scale = float(scale); p.eps = float(eps); p.causal = causal != 0; p.status = status;
   p.deterministic = path == FAT_PATH_TENSOR_DETERMINISTIC;
+  p.key_mask = key_mask_bits; p.mask_words = fat_key_mask_words(T);
   return sel == FAT_PATH_TENSOR ? attn_bwd_tc(p, dtype, (cudaStream_t)stream) : attn_bwd_simt(p, dtype, (cudaStream_t)stream);
 }
 

@@ -297,8 +297,34 @@ Tensor alloc_bhtd(const Tensor& like, bool token_major) {
   return at::empty({B, H, T, D}, like.options());
 }
 
+// The packed padding mask of a launch (see fat_pack_key_mask), or null when there is none.
+const uint32_t* mask_bits(const c10::optional<Tensor>& key_mask, const Tensor& q) {
+  if (!key_mask.has_value() || !key_mask->defined()) return nullptr;
+  const Tensor& m = *key_mask;
+  TORCH_CHECK(m.is_cuda() && m.device() == q.device() && m.scalar_type() == at::kInt && m.is_contiguous() && m.dim() == 2 &&
+              m.size(0) == q.size(0) && m.size(1) == fat_key_mask_words(int(q.size(2))),
+              "key_mask must be the int32 [B, 4*ceil(T/128)] tensor that algebraic::pack_key_mask returns for these shapes");
+  return reinterpret_cast<const uint32_t*>(m.data_ptr<int>());
+}
+
+// [B, T] mask (non-zero = the key takes part) -> int32 [B, 4*ceil(T/128)] bits for the attention operators.
+Tensor pack_key_mask(const Tensor& mask) {
+  cuda_check({&mask});
+  TORCH_CHECK(mask.dim() == 2, "attention mask must be [B, T]");
+  const Tensor m = mask.scalar_type() == at::kBool ? mask : mask.ne(0);
+  const int64_t B = m.size(0), T = m.size(1);
+  Tensor bits = at::empty({B, int64_t(fat_key_mask_words(int(T)))}, m.options().dtype(at::kInt));
+  if (bits.numel()) {
+    c10::cuda::CUDAGuard guard(m.device());
+    check(fat_pack_key_mask(reinterpret_cast<const uint8_t*>(m.data_ptr<bool>()), reinterpret_cast<uint32_t*>(bits.data_ptr<int>()), int(B), int(T),
+                            m.stride(0), m.stride(1), stream_of(m)));
+  }
+  return bits;
+}
+
 std::tuple<Tensor, Tensor, Tensor> attn_fwd(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in, const Tensor& slopes, double scale,
-                                            bool causal, double eps, int64_t path, bool token_major_out) {
+                                            bool causal, double eps, int64_t path, bool token_major_out,
+                                            const c10::optional<Tensor>& key_mask) {
   cuda_check({&q_in, &k_in, &v_in, &slopes});
   TORCH_CHECK(q_in.dim() == 4 && q_in.sizes() == k_in.sizes() && q_in.sizes() == v_in.sizes() &&
               q_in.scalar_type() == k_in.scalar_type() && q_in.scalar_type() == v_in.scalar_type(), "q, k, v must be [B,H,T,D] of one shape and dtype");
@@ -313,7 +339,7 @@ std::tuple<Tensor, Tensor, Tensor> attn_fwd(const Tensor& q_in, const Tensor& k_
   if (q.numel()) {
     c10::cuda::CUDAGuard guard(q.device());
     const auto qs = strides3(q), ks = strides3(k), vs = strides3(v), os = strides3(out);
-    check(fat_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), sl.data_ptr<float>(), out.data_ptr(),
+    check(fat_attn_fwd_masked(q.data_ptr(), k.data_ptr(), v.data_ptr(), sl.data_ptr<float>(), mask_bits(key_mask, q), out.data_ptr(),
                        out_lo.numel() ? out_lo.data_ptr() : nullptr, L.data_ptr<float>(), int(B), int(H), int(T), int(D), qs.data(), ks.data(),
                        vs.data(), os.data(), scale, eps, int(causal), dtype_tag(q), int(path),
                        status_word(q.get_device()).data_ptr<int>(), stream_of(q)));
@@ -323,7 +349,7 @@ std::tuple<Tensor, Tensor, Tensor> attn_fwd(const Tensor& q_in, const Tensor& k_
 
 std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in, const Tensor& out_in,
                                             const Tensor& out_lo_in, const Tensor& L, const Tensor& d_out_in, const Tensor& slopes,
-                                            double scale, bool causal, double eps, int64_t path) {
+                                            double scale, bool causal, double eps, int64_t path, const c10::optional<Tensor>& key_mask) {
   cuda_check({&q_in, &k_in, &v_in, &out_in, &L, &d_out_in, &slopes});
   const Tensor q = unit_d(q_in), k = unit_d(k_in), v = unit_d(v_in), d_out = unit_d(d_out_in);
   Tensor out = unit_d(out_in), out_lo = out_lo_in;
@@ -357,8 +383,8 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q_in, const Tensor& k_
     Tensor ws = at::empty({int64_t(ws_bytes)}, q.options().dtype(at::kByte));
     const auto qs = strides3(q), ks = strides3(k), vs = strides3(v), os = strides3(out), dos = strides3(d_out), dqs = strides3(d_q),
                dks = strides3(d_k), dvs = strides3(d_v);
-    check(fat_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lo_ptr, Lc.data_ptr<float>(), d_out.data_ptr(),
-                       sl.data_ptr<float>(), d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), ws.data_ptr(), ws_bytes, int(B), int(H), int(T),
+    check(fat_attn_bwd_masked(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lo_ptr, Lc.data_ptr<float>(), d_out.data_ptr(),
+                       sl.data_ptr<float>(), mask_bits(key_mask, q), d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), ws.data_ptr(), ws_bytes, int(B), int(H), int(T),
                        int(D), qs.data(), ks.data(), vs.data(), os.data(), dos.data(), dqs.data(), dks.data(), dvs.data(), scale, eps,
                        int(causal), tag, int(path), status_word(q.get_device()).data_ptr<int>(), stream_of(q)));
   }
@@ -411,9 +437,10 @@ TORCH_LIBRARY(algebraic, m) {
   m.def("softmax_fwd(Tensor x, float eps) -> Tensor");
   m.def("softmax_bwd(Tensor d_out, Tensor x, float eps) -> Tensor");
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor slopes, float scale, bool causal, float eps, int path, "
-        "bool token_major_out) -> (Tensor, Tensor, Tensor)");
+        "bool token_major_out, Tensor? key_mask=None) -> (Tensor, Tensor, Tensor)");
   m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor out_lo, Tensor L, Tensor d_out, Tensor slopes, "
-        "float scale, bool causal, float eps, int path) -> (Tensor, Tensor, Tensor)");
+        "float scale, bool causal, float eps, int path, Tensor? key_mask=None) -> (Tensor, Tensor, Tensor)");
+  m.def("pack_key_mask(Tensor mask) -> Tensor");
   m.def("attn_decode(Tensor q, Tensor k_new, Tensor v_new, Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor n_cached, Tensor slopes, "
         "float scale, float eps) -> Tensor");
   m.def("device_status(int device) -> Tensor", &device_status);
@@ -434,4 +461,5 @@ TORCH_LIBRARY_IMPL(algebraic, CUDA, m) {
   m.impl("attn_fwd", &attn_fwd);
   m.impl("attn_bwd", &attn_bwd);
   m.impl("attn_decode", &attn_decode);
+  m.impl("pack_key_mask", &pack_key_mask);
 }

@@ -52,10 +52,38 @@ def head_shifted_ce(y: Tensor, weight: Tensor, labels: Tensor, ignore_index: int
     return (loss, d_y, d_w) if want_grads else (loss, None, None)
 
 
+def pack_key_mask(mask: Tensor) -> Tensor:
+    """Padding mask [B, T] (non-zero = the key takes part; the reference's ``attention_mask``, algebraic_model.py:128-131)
+    as the int32 [B, 4*ceil(T/128)] bit tensor the attention operators take; see include/fat_b200.h, fat_pack_key_mask."""
+    return _alg.pack_key_mask(mask)
+
+
+class PackedKeyMask:
+    """A padding mask that has already been packed to bits (``bits``: int32 [B, 4*ceil(T/128)]), so that the layers of a
+    model pack it once per step instead of once each."""
+
+    def __init__(self, mask: Tensor):
+        if mask.dim() != 2:
+            raise ValueError("a padding mask must be [B, T]")
+        self.n_tokens = mask.shape[1]
+        self.bits = pack_key_mask(mask)
+
+
+def as_key_mask_bits(key_mask, n_tokens: int) -> Optional[Tensor]:
+    """None, a [B, T] padding mask (0 = padding) or a PackedKeyMask -> the bit tensor the attention operators take."""
+    if key_mask is None:
+        return None
+    if not isinstance(key_mask, PackedKeyMask):
+        key_mask = PackedKeyMask(key_mask)
+    if key_mask.n_tokens != n_tokens:
+        raise ValueError(f"the padding mask covers {key_mask.n_tokens} tokens, the sequence has {n_tokens}")
+    return key_mask.bits
+
+
 def attn_fwd(q: Tensor, k: Tensor, v: Tensor, slopes: Tensor, scale: float, causal: bool, eps: float,
-             path: int, token_major_out: bool) -> Tuple[Tensor, Tensor, Tensor]:
-    """(out, L, out_lo) of rational attention; see include/fat_b200.h, fat_attn_fwd."""
-    return _alg.attn_fwd(q, k, v, slopes, float(scale), bool(causal), float(eps), int(path), bool(token_major_out))
+             path: int, token_major_out: bool, key_mask: Optional[Tensor] = None) -> Tuple[Tensor, Tensor, Tensor]:
+    """(out, L, out_lo) of rational attention; see include/fat_b200.h, fat_attn_fwd.  ``key_mask``: packed bits or None."""
+    return _alg.attn_fwd(q, k, v, slopes, float(scale), bool(causal), float(eps), int(path), bool(token_major_out), key_mask)
 
 
 def attn_decode(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, v_cache: Tensor, n_cached: Tensor, slopes: Tensor,
@@ -66,10 +94,10 @@ def attn_decode(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, v_cach
 
 
 def attn_bwd_packed(qkv: Tensor, out: Tensor, out_lo: Tensor, L: Tensor, d_out: Tensor, slopes: Tensor,
-                    scale: float, causal: bool, eps: float, path: int) -> Tensor:
+                    scale: float, causal: bool, eps: float, path: int, key_mask: Optional[Tensor] = None) -> Tensor:
     """Gradient of a packed [B,T,3,H,D] projection: d_q, d_k, d_v written side by side into one buffer."""
     q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
-    d_q, d_k, d_v = _alg.attn_bwd(q, k, v, out, out_lo, L, d_out, slopes, float(scale), bool(causal), float(eps), int(path))
+    d_q, d_k, d_v = _alg.attn_bwd(q, k, v, out, out_lo, L, d_out, slopes, float(scale), bool(causal), float(eps), int(path), key_mask)
     base = d_q._base
     while base is not None and base._base is not None:
         base = base._base
@@ -138,8 +166,13 @@ def _(d_out, x, eps):
     return torch.empty_like(x, memory_format=torch.contiguous_format)
 
 
+@torch.library.register_fake(f"{_NS}::pack_key_mask")
+def _(mask):
+    return mask.new_empty((mask.shape[0], 4 * ((mask.shape[1] + 127) // 128)), dtype=torch.int32)
+
+
 @torch.library.register_fake(f"{_NS}::attn_fwd")
-def _(q, k, v, slopes, scale, causal, eps, path, token_major_out):
+def _(q, k, v, slopes, scale, causal, eps, path, token_major_out, key_mask=None):
     B, H, T, D = q.shape
     out = q.new_empty((B, T, H, D)).permute(0, 2, 1, 3) if token_major_out else q.new_empty((B, H, T, D))
     lo = torch.empty_like(out) if q.element_size() == 2 else q.new_empty(0)
@@ -147,7 +180,7 @@ def _(q, k, v, slopes, scale, causal, eps, path, token_major_out):
 
 
 @torch.library.register_fake(f"{_NS}::attn_bwd")
-def _(q, k, v, out, out_lo, L, d_out, slopes, scale, causal, eps, path):
+def _(q, k, v, out, out_lo, L, d_out, slopes, scale, causal, eps, path, key_mask=None):
     return tuple(q.new_empty(q.shape) for _ in range(3))
 
 
@@ -203,15 +236,16 @@ def _softmax_backward(ctx, d_out):
 
 
 def _attn_setup(ctx, inputs, output):
-    q, k, v, slopes, scale, causal, eps, path, _ = inputs
+    q, k, v, slopes, scale, causal, eps, path, _, key_mask = inputs
     ctx.save_for_backward(q, k, v, output[0], output[1], output[2], slopes)
     ctx.args = (scale, causal, eps, path)
+    ctx.key_mask = key_mask                                  # (an int32 tensor: nothing to differentiate)
 
 
 def _attn_backward(ctx, d_out, d_L, d_lo):
     q, k, v, out, L, out_lo, slopes = ctx.saved_tensors
-    d_q, d_k, d_v = torch.ops.algebraic.attn_bwd(q, k, v, out, out_lo, L, d_out, slopes, *ctx.args)
-    return d_q, d_k, d_v, None, None, None, None, None, None
+    d_q, d_k, d_v = torch.ops.algebraic.attn_bwd(q, k, v, out, out_lo, L, d_out, slopes, *ctx.args, ctx.key_mask)
+    return d_q, d_k, d_v, None, None, None, None, None, None, None
 
 
 torch.library.register_autograd(f"{_NS}::swiglu_fwd", _swiglu_backward, setup_context=_swiglu_setup)

@@ -256,6 +256,33 @@ FAT_API int fat_attn_bwd(const void* q, const void* k, const void* v, const void
                  int* status, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Padding mask over the keys.  The reference's model takes attention_mask [B, T] (0 = padding) and, on its PyTorch path
+ * only, fills the scores of padded keys with -1e4 before the rational softmax (algebraic_model.py:128-131:
+ * scores.masked_fill_(mask[:, None, None, :] == 0, -1e4)); its Triton path never sees the mask (algebraic_model.py:93-104).
+ * Here the attention kernels of both families honour it: a masked key gets weight zero for every query (the reference's
+ * -1e4 leaves sigma^4 = 6e-18), its d_k and d_v rows come out as zero, and a query that sees no key at all gets a zero
+ * output row.  The kernels read the mask as bits: fat_key_mask_words(T) = 4 * ceil(T / 128) 32-bit words per batch element,
+ * bit (j & 31) of word (j >> 5) set = key j takes part, bits from T on clear.  fat_pack_key_mask builds them from a
+ * byte mask [B, T] (non-zero = the key takes part; element strides given).  fat_attn_fwd_masked / fat_attn_bwd_masked are
+ * fat_attn_fwd / fat_attn_bwd with the packed mask as one more argument (null = no mask: the same call as the plain entry
+ * point); the backward must be given the mask its forward was given.
+ * ---------------------------------------------------------------------------------- */
+FAT_API int fat_key_mask_words(int T);
+FAT_API int fat_pack_key_mask(const uint8_t* mask, uint32_t* bits, int B, int T, int64_t mask_batch_stride,
+                 int64_t mask_token_stride, void* stream);
+FAT_API int fat_attn_fwd_masked(const void* q, const void* k, const void* v, const float* slopes, const uint32_t* key_mask_bits,
+                 void* out, void* out_lo, float* L, int B, int H, int T, int D,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides, const int64_t* out_strides,
+                 double scale, double eps, int causal, int dtype, int path, int* status, void* stream);
+FAT_API int fat_attn_bwd_masked(const void* q, const void* k, const void* v, const void* out, const void* out_lo, const float* L,
+                 const void* d_out, const float* slopes, const uint32_t* key_mask_bits, void* d_q, void* d_k, void* d_v,
+                 void* workspace, size_t workspace_bytes, int B, int H, int T, int D,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const int64_t* out_strides, const int64_t* d_out_strides,
+                 const int64_t* d_q_strides, const int64_t* d_k_strides, const int64_t* d_v_strides,
+                 double scale, double eps, int causal, int dtype, int path, int* status, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Decode step: rational attention of ONE new token per sequence over a key/value cache.
  *     out[b,h,:] = sum_j f_j v_j / (sum_j f_j + eps),  f_j = sigma(q . k_j scale - slope_h (n_b - j))^4,  j = 0..n_b
  * where n_b = n_cached[b] rows are already in the cache and the new token's key/value rows (k_new, v_new) are first

@@ -94,8 +94,10 @@ def compute_alibi_slopes(n_heads: int) -> torch.Tensor:
 # attention
 # --------------------------------------------------------------------------------------
 
-def _scores(q, k, slopes, scale, causal=True):
-    """scores = q k^T * scale - slope_h |i-j|, masked entries set to -1e4 (tests.py:48-59)."""
+def _scores(q, k, slopes, scale, causal=True, key_mask=None):
+    """scores = q k^T * scale - slope_h |i-j|, masked entries set to -1e4 (tests.py:48-59).  ``key_mask`` [B, T]: keys
+    whose entry is 0 are padding and are filled the same way, as the reference's model does on its PyTorch path
+    (algebraic_model.py:128-131)."""
     B, H, T, D = q.shape
     s = torch.matmul(q, k.transpose(-2, -1)) * scale
     pos = torch.arange(T)
@@ -104,16 +106,18 @@ def _scores(q, k, slopes, scale, causal=True):
     if causal:
         future = torch.triu(torch.ones(T, T, dtype=torch.bool), diagonal=1)
         s = s.masked_fill(future[None, None], MASK_FILL)
+    if key_mask is not None:
+        s = s.masked_fill(key_mask[:, None, None, :] == 0, MASK_FILL)
     return s
 
 
-def rational_attention(q, k, v, slopes, scale, eps: float = EPS, causal: bool = True):
+def rational_attention(q, k, v, slopes, scale, eps: float = EPS, causal: bool = True, key_mask=None):
     """Causal rational attention with ALiBi (tests.py:44-65).
 
     ``causal=False`` is this oracle's natural extension (mask line removed); the
     reference never defines it (its kernels and its own oracle are always causal).
     """
-    return torch.matmul(rational_softmax(_scores(q, k, slopes, scale, causal), eps), v)
+    return torch.matmul(rational_softmax(_scores(q, k, slopes, scale, causal, key_mask), eps), v)
 
 
 def rational_attention_last_row(q, k, v, slopes, scale, eps: float = EPS):
@@ -134,13 +138,13 @@ def rational_attention_rowsum(q, k, slopes, scale, causal: bool = True):
     return rational_sigmoid(_scores(q, k, slopes, scale, causal)).pow(4).sum(-1)
 
 
-def rational_attention_grads(q, k, v, d_out, slopes, scale, eps: float = EPS, causal: bool = True):
+def rational_attention_grads(q, k, v, d_out, slopes, scale, eps: float = EPS, causal: bool = True, key_mask=None):
     """(out, dq, dk, dv) via autograd through the forward restatement, one batch element at
     a time so that S=4096 fits in host memory."""
     outs, dqs, dks, dvs = [], [], [], []
     for b in range(q.shape[0]):
         qb, kb, vb = (t[b:b + 1].detach().clone().requires_grad_(True) for t in (q, k, v))
-        o = rational_attention(qb, kb, vb, slopes, scale, eps, causal)
+        o = rational_attention(qb, kb, vb, slopes, scale, eps, causal, None if key_mask is None else key_mask[b:b + 1])
         o.backward(d_out[b:b + 1])
         outs.append(o.detach()); dqs.append(qb.grad); dks.append(kb.grad); dvs.append(vb.grad)
     return tuple(torch.cat(t, 0) for t in (outs, dqs, dks, dvs))

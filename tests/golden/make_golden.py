@@ -110,6 +110,20 @@ def main():
         save(f"attention_{tag}", q=q, k=k, v=v, d_out=go, slopes=slopes, scale=np.float32(scale),
              out=out, dq=dq, dk=dk, dv=dv)
 
+    # --- attention with a padding mask: the only place the reference applies one is the PyTorch path of its attention
+    #     module (algebraic_model.py:112-136), so that method is what is recorded (scale 1/sqrt(D), the module's slopes)
+    g = torch.Generator().manual_seed(107)
+    for tag, (B, H, T, D), pads in (("a", (2, 4, 48, 32), ((40, 48), (0, 5))),              # right padding, left padding
+                                    ("b", (3, 1, 136, 64), ((100, 136), (0, 0), (60, 131)))):  # ... none, and a hole
+        q, k, v, go = (torch.randn(B, H, T, D, generator=g) for _ in range(4))
+        mask = torch.ones(B, T, dtype=torch.int64)
+        for b, (lo, hi) in enumerate(pads):
+            mask[b, lo:hi] = 0
+        attn = ref_model.AlgebraicAttention(d_model=H * D, n_head=H, dropout=0.0)
+        out, (dq, dk, dv) = grads(lambda a, b, c: attn._cpu_attention(a, b, c, mask), [q, k, v], go)
+        save(f"attention_masked_{tag}", q=q, k=k, v=v, d_out=go, mask=mask, slopes=attn.alibi_slopes, scale=np.float32(attn.scale),
+             out=out, dq=dq, dk=dk, dv=dv)
+
     # --- language model: a shrunken version of the reference smoke test (tests.py:281-290), dropout 0
     torch.manual_seed(105)
     cfg = dict(vocab_size=128, d_model=64, n_head=4, n_layers=2)
@@ -124,6 +138,16 @@ def main():
     save("lm_tiny", input_ids=ids, labels=labels, loss=loss.detach(), logits=logits.detach(),
          n_head=np.int64(cfg["n_head"]),
          **{"w__" + n.replace(".", "__"): p.detach() for n, p in named},
+         **{"g__" + n.replace(".", "__"): p.grad for n, p in named})
+
+    # --- the same model and inputs with a padding mask (weights as in lm_tiny; right padding and left padding)
+    model.zero_grad()
+    mask = torch.ones(2, 32, dtype=torch.int64)
+    mask[0, 25:] = 0
+    mask[1, :3] = 0
+    logits, loss = model(ids, labels=labels, attention_mask=mask)
+    loss.backward()
+    save("lm_tiny_masked", attention_mask=mask, loss=loss.detach(), logits=logits.detach(),
          **{"g__" + n.replace(".", "__"): p.grad for n, p in named})
 
 

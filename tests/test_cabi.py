@@ -57,6 +57,17 @@ def test_host_side_argument_errors_need_no_gpu(libpath):
                             _lib.F64, 0, None, None) == 1
     assert lib.fat_norm_bwd_workspace_bytes(10, 4096, _lib.BF16) == 2 * 148 * 4096 * 4   # 2 blocks per SM, 148 SMs (a B200; also assumed when no device answers)
     assert lib.fat_attn_bwd_workspace_bytes(2, 3, 5, 64, _lib.F32, _lib.PATH_SIMT) == 2 * 3 * 5 * 4
+    # padding-mask and decode entry points: sizes and argument errors are decided on the host
+    assert [lib.fat_key_mask_words(t) for t in (0, 1, 128, 129, 4096)] == [0, 4, 4, 8, 128]
+    assert lib.fat_pack_key_mask(None, None, 2, 16, 16, 1, None) == 7
+    assert lib.fat_pack_key_mask(None, None, 0, 16, 16, 1, None) == 0
+    assert lib.fat_attn_fwd_masked(None, None, None, None, None, None, None, None, 1, 0, 4, 8, s3, s3, s3, s3, 1.0, 1e-6, 1,
+                                   _lib.F32, 0, None, None) == 2
+    s2 = (ctypes.c_int64 * 2)(1, 1)
+    assert lib.fat_attn_decode(None, None, None, None, None, None, None, None, 1, 2, 0, 64, s2, s2, s2, s2, s3, s3, 1.0, 1e-6,
+                               _lib.F32, None, None) == 2
+    assert lib.fat_attn_decode(None, None, None, None, None, None, None, None, 1, 2, 16, 64, s2, s2, s2, s2, s3, s3, 1.0, 1e-6,
+                               _lib.F32, None, None) == 7
 
 
 def test_cpu_tensors_are_rejected_not_emulated(libpath):

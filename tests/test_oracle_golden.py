@@ -85,6 +85,25 @@ def test_attention(tag):
     assert norm_max_err(last, g["out"][:, :, -1]) < TOL
 
 
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_attention_with_padding_mask(tag):
+    """The oracle's key mask against the reference's masked attention (its model's PyTorch path)."""
+    g = load_golden(f"attention_masked_{tag}")
+    out, dq, dk, dv = oracle.rational_attention_grads(g["q"], g["k"], g["v"], g["d_out"], g["slopes"], g["scale"],
+                                                       key_mask=g["mask"])
+    for got, key in ((out, "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert norm_max_err(got, g[key]) < TOL, key
+
+
+def test_lm_tiny_with_padding_mask():
+    g, m = load_golden("lm_tiny"), load_golden("lm_tiny_masked")
+    state = {k[3:].replace("__", "."): v for k, v in g.items() if k.startswith("w__")}
+    state["head.weight"] = state.pop("embed.weight")
+    logits, loss = oracle.lm_forward(state, g["input_ids"], g["n_head"], g["labels"], attention_mask=m["attention_mask"])
+    assert norm_max_err(logits, m["logits"]) < 1e-5
+    assert abs(loss.item() - m["loss"]) < 1e-5
+
+
 def test_lm_tiny():
     g = load_golden("lm_tiny")
     state = {k[3:].replace("__", "."): v for k, v in g.items() if k.startswith("w__")}
