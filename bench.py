@@ -339,7 +339,8 @@ FUSED = {
     "loss_head": dict(rows=8 * 1024, cols=32000, bytes=2 * 8 * 1024 * 32000 * 2, traffic=None),
     # one decode step of a key/value-cached generate(): every (batch, head) pair reads its 4096 cached key rows and value
     # rows once (the query, the appended rows and the output are KBs); shape of the headline attention configuration
-    "decode": dict(rows=8 * 16 * 4096, cols=128, bytes=2 * 8 * 16 * 4096 * 128 * 2, traffic=None, B=8, H=16, cap=4096),
+    # (traffic: profiles/attention_decode_bf16_B8_H16_T4096_D128.md)
+    "decode": dict(rows=8 * 16 * 4096, cols=128, bytes=2 * 8 * 16 * 4096 * 128 * 2, traffic=272.7e6, B=8, H=16, cap=4096),
 }
 FUSED_TRAFFIC_SOURCE = "profiles/fused_ops_bf16_config3.md"
 
@@ -441,7 +442,8 @@ def run_fused(name, steps, warmup, rank, world, device, with_e2e=True):
         "gpu_launches_how": "fat_launch_count() of libfat_b200.so around the capture of one step, times the replays of the timed region",
         "roofline": {"bound": "hbm", "kernel": f"{name} fwd+bwd" if name != "decode" else "attn_decode_kernel", "achieved": gbs / world, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": gbs / world / peaks["hbm_gbs"], "traffic": cfg["traffic"],
-                     "traffic_source": FUSED_TRAFFIC_SOURCE if cfg["traffic"] else None,
+                     "traffic_source": (("profiles/attention_decode_bf16_B8_H16_T4096_D128.md" if name == "decode" else FUSED_TRAFFIC_SOURCE)
+                                        if cfg["traffic"] else None),
                      "peak_source": peaks["source"] + " (copy bandwidth)"},
         "clocks": clocks.summary(),
     }
