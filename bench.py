@@ -599,6 +599,89 @@ def run_lm(name, steps, warmup, rank, world, device, graph=True, eager_steps=0, 
     return res
 
 
+def run_generate(steps, warmup, rank, world, device):
+    """Decode steps of the small LM over a key/value cache: every sequence gets one new token per step.  The prompt
+    (512 tokens per sequence) is run once, untimed; the timed region replays the captured decode step (all layers: norms,
+    projections, cache append + attention, feed-forward, head).  Next to it: the same step issued launch by launch, and what
+    the reference's generate() does for one token at this length, a full forward over the prefix (algebraic_model.py:239-265)."""
+    from fastalgebraictransformer_b200 import AlgebraicTransformerLM, ops  # noqa: F401
+    cfg = LM["lm_small"]
+    batch, prompt = 8, 512
+    capacity = prompt + warmup + 2 * steps + 64
+    torch.manual_seed(1234 + 3)
+    model = AlgebraicTransformerLM(cfg["vocab_size"], cfg["d_model"], cfg["n_head"], cfg["n_layers"], d_ffn=cfg["d_ffn"],
+                                   block_size=capacity, dropout=0.0).to(device).to(torch.bfloat16).eval()
+    g = torch.Generator(device=device).manual_seed(1234 + 3 + rank)
+    ids = torch.randint(0, cfg["vocab_size"], (batch, prompt), generator=g, device=device)
+    token = torch.randint(0, cfg["vocab_size"], (batch, 1), generator=g, device=device)
+    with torch.no_grad():
+        cache = model.new_cache(batch, capacity)
+        model.forward_cached(ids, cache)
+        n0 = launch_count()
+        model.forward_cached(token, cache)                           # one step launch by launch (also the warm-up of the capture)
+        launches_per_step = launch_count() - n0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(device)
+        e0.record()
+        for _ in range(8):
+            model.forward_cached(token, cache)
+        e1.record()
+        torch.cuda.synchronize(device)
+        eager_ms = e0.elapsed_time(e1) / 8
+        seen = cache.seen
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = model.forward_cached(token, cache)
+        cache.seen = seen
+
+        def step():
+            graph.replay()
+            cache.seen += 1
+
+        with ClockSampler(device.index) as clocks:
+            ms = time_steps(step, steps, warmup, world, device)
+        n_ctx = cache.seen
+        # the reference's way: one forward over the whole prefix per new token
+        full = torch.randint(0, cfg["vocab_size"], (batch, n_ctx), generator=g, device=device)
+        ms_recompute = time_steps(lambda: model(full), 5, 2, world, device)
+        # end to end: prompt up, generate(), tokens down
+        host_prompt = ids.cpu().pin_memory()
+        new_tokens = 64
+
+        def e2e_step():
+            out = model.generate(host_prompt.to(device, non_blocking=True), new_tokens, top_k=1)
+            return out.cpu()
+
+        ms_e2e = time_steps(e2e_step, 2, 1, world, device)
+    peaks = measured_peaks()
+    params = sum(p.numel() for n, p in model.named_parameters())
+    kv_bytes = 2 * cfg["n_layers"] * batch * cfg["d_model"] * n_ctx * 2            # keys and values of every layer, read once
+    step_bytes = params * 2 + kv_bytes                                              # plus every weight, read once
+    tok_s = batch * world / (ms * 1e-3)
+    gbs = step_bytes / (ms * 1e-3) / 1e9
+    res = {
+        "metric": "lm_generate_tokens_per_s", "value": tok_s, "unit": "tokens/s", "ms_per_step": ms, "dtype": "bf16", "scaling": "weak",
+        "config": {"workload": f"lm_small decode: {batch} sequences per GPU, one new token each per step, {prompt}-token prompts, "
+                               f"context {n_ctx - steps}..{n_ctx} tokens during the timed steps",
+                   "params": params, "launch": "decode step replayed from a CUDA graph (cached lengths live on the device)",
+                   "eager_ms": eager_ms, "reference_way_ms_per_token": ms_recompute,
+                   "reference_way": "a forward over the whole prefix for every new token (what generate() does without a cache), same model and kernels",
+                   "algorithmic_bytes_per_step": step_bytes},
+        "e2e": {"value": batch * new_tokens * world / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": host_prompt.numel() * 8, "d2h_bytes_per_step": batch * (prompt + new_tokens) * 8,
+                "what": f"model.generate(prompt from pinned host memory, {new_tokens} new tokens, greedy), prompt pass included, tokens read back"},
+        "gpu_launches": launches_per_step * steps,
+        "gpu_launches_how": "fat_launch_count() of libfat_b200.so around one decode step, times the replays of the timed region",
+        "roofline": {"bound": "hbm", "kernel": "decode step (all launches: this library's and the cuBLAS projections)", "achieved": gbs,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": peaks["source"] + " (copy bandwidth)"},
+        "clocks": clocks.summary(),
+    }
+    del model, cache, graph, logits
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_extras(args, rank, world, device):
     """Compact records of the other configurations at the same N, for the default workload's line: the small LM's
     training step, the three bandwidth-sweep operators and the decode step over a key/value cache.  A failure in one is recorded, not raised."""
@@ -688,6 +771,20 @@ def cpu_sample(workload: str):
             x = logits.detach().clone().requires_grad_(True)
             oracle.shifted_cross_entropy(x, labels).backward()
         return (run, cfg["bytes"] / 8 / 1e9, "GB/s", "8 sequences of 128 of the 1024 positions, float32")
+    if workload == "generate":
+        from fastalgebraictransformer_b200 import AlgebraicTransformerLM
+        cfg = LM["lm_small"]
+        torch.manual_seed(1234 + 3)
+        model = AlgebraicTransformerLM(cfg["vocab_size"], cfg["d_model"], cfg["n_head"], cfg["n_layers"], d_ffn=cfg["d_ffn"],
+                                       block_size=1024, dropout=0.0)
+        state = {k: v.detach().float() for k, v in model.state_dict().items()}
+        ids = torch.randint(0, cfg["vocab_size"], (1, 512), generator=torch.Generator().manual_seed(1234 + 3))
+
+        def run():
+            with torch.no_grad():
+                oracle.lm_forward(state, ids, cfg["n_head"])
+        return (run, 1.0, "tokens/s", "one new token of ONE sequence the reference's way: a float32 forward over its 512-token prefix "
+                "(algebraic_model.py:239-265; the GPU arm advances 8 sequences per step)")
     if workload in LM:
         from fastalgebraictransformer_b200 import AlgebraicTransformerLM
         cfg = LM[workload]
@@ -705,7 +802,8 @@ def cpu_sample(workload: str):
     raise SystemExit(f"no CPU sample for workload {workload}")
 
 
-REF_METRIC = {"attn": "rational_attention_fwd_bwd_tflops", "lm_small": "lm_train_tokens_per_s", "lm_xl": "lm_train_tokens_per_s"}
+REF_METRIC = {"attn": "rational_attention_fwd_bwd_tflops", "lm_small": "lm_train_tokens_per_s", "lm_xl": "lm_train_tokens_per_s",
+              "decode": "rational_attention_decode_gbs", "generate": "lm_generate_tokens_per_s"}
 
 
 def cpu_baseline(workload: str, budget_s: float = 10.0, max_passes: int = 64):
@@ -761,7 +859,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "add_norm", "loss_head", "decode", "lm_small", "lm_xl"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "swiglu", "norm", "softmax", "add_norm", "loss_head", "decode", "generate", "lm_small", "lm_xl"])
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="attn workload on N > 1 ranks: split the 128 (batch, head) units over the ranks (strong, default) "
                          "or give every rank all of them (weak)")
@@ -802,6 +900,8 @@ def main():
             res["extra"] = run_extras(args, rank, world, device)
     elif args.workload in FUSED:
         res = run_fused(args.workload, args.steps, args.warmup, rank, world, device)
+    elif args.workload == "generate":
+        res = run_generate(args.steps, args.warmup, rank, world, device)
     else:
         res = run_lm(args.workload, args.steps, args.warmup, rank, world, device, graph=not args.no_graph,
                      eager_steps=0 if args.no_graph else max(3, args.steps // 2), keep_logits=not args.no_logits)

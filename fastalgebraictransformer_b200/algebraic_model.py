@@ -251,11 +251,13 @@ class AlgebraicTransformerLM(nn.Module):
 
     @torch.no_grad()
     def generate(self, idx: torch.Tensor, max_new_tokens: int, temperature: float = 1.0,
-                 top_k: Optional[int] = None, use_cache: bool = True) -> torch.Tensor:
+                 top_k: Optional[int] = None, use_cache: bool = True, cuda_graph: bool = True) -> torch.Tensor:
         """Sampling loop (reference algebraic_model.py:239-265).  The reference re-runs the forward over the whole prefix
         for every token; here (``use_cache``, an extension) the prompt runs once, its keys and values are kept, and each
         new token costs one decode step.  The two agree as long as the reference would not crop the prefix to
-        ``block_size``; when it would (or the decode kernel does not cover the model), the reference's loop runs."""
+        ``block_size``; when it would (or the decode kernel does not cover the model), the reference's loop runs.
+        ``cuda_graph``: a decode step is a hundred small launches whatever the length (the cached lengths live on the
+        device), so after one step issued launch by launch it is captured once and replayed for the remaining tokens."""
         def sample(logits):
             if temperature != 1.0:
                 logits = logits / temperature
@@ -268,10 +270,25 @@ class AlgebraicTransformerLM(nn.Module):
         if use_cache and max_new_tokens > 0 and idx.size(1) > 0 and longest <= self.block_size and self.cache_supported():
             cache = self.new_cache(idx.size(0), longest)
             logits = self.forward_cached(idx, cache)
+            graph = token = None
             for step in range(max_new_tokens):
                 nxt = sample(logits)
                 idx = torch.cat((idx, nxt), dim=1)
-                if step + 1 < max_new_tokens:
+                if step + 1 == max_new_tokens:
+                    break
+                if graph is not None:
+                    token.copy_(nxt)
+                    graph.replay()
+                    cache.seen += 1                         # (the device-side lengths advance inside the graph)
+                elif cuda_graph and step == 1 and max_new_tokens - step > 4:
+                    token, seen = nxt.clone(), cache.seen
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        logits = self.forward_cached(token, cache)
+                    cache.seen = seen                       # capturing ran the host bookkeeping without running the step
+                    graph.replay()
+                    cache.seen += 1
+                else:
                     logits = self.forward_cached(nxt, cache)
             return idx
         for _ in range(max_new_tokens):

@@ -164,9 +164,12 @@ def test_generate_with_cache_equals_the_reference_loop():
     """Greedy sampling (top_k=1 leaves one candidate) through the cache and through the reference's recompute loop."""
     model = _tiny(torch.float32, block_size=48)
     prompt = torch.randint(0, 128, (2, 9), device=DEV)
-    a = model.generate(prompt.clone(), 24, top_k=1, use_cache=True)
+    a = model.generate(prompt.clone(), 24, top_k=1, use_cache=True)                      # decode steps replayed from a CUDA graph
     b = model.generate(prompt.clone(), 24, top_k=1, use_cache=False)
-    assert a.shape == (2, 33) and torch.equal(a, b)
+    e = model.generate(prompt.clone(), 24, top_k=1, use_cache=True, cuda_graph=False)    # every decode step launch by launch
+    assert a.shape == (2, 33) and torch.equal(a, b) and torch.equal(e, b)
+    fat_status = __import__("fastalgebraictransformer_b200").check_device_status
+    fat_status()                                                                         # no cache overflow was reported
     # a run that would outgrow block_size falls back to the reference's loop (the window slides, positions shift)
     c = model.generate(prompt.clone(), 48, top_k=1, use_cache=True)
     d = model.generate(prompt.clone(), 48, top_k=1, use_cache=False)
