@@ -13,12 +13,21 @@
 
 #include "../../include/fat_b200.h"
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace fat {
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kCePacks = 16;                       // 16-byte packs of one row a thread keeps in registers
+#ifndef FAT_CE_STAGED
+#define FAT_CE_STAGED 1
+#endif
+#ifndef FAT_CE_STAGED_THREADS
+#define FAT_CE_STAGED_THREADS 512
+#endif
+constexpr int kCeStagedThreads = FAT_CE_STAGED_THREADS;
+constexpr size_t kCeSmemBytes = 200 * 1024;        // shared memory the staged kernel may ask for
 
 __device__ __forceinline__ float fast_exp2(float x) {      // x <= 0 here: flushing tiny results to zero is harmless
   float y;
@@ -136,6 +145,220 @@ shifted_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labe
   }
 }
 
+// Two neighbouring float32 values as one 64-bit register pair (fma.rn.f32x2 and mul.rn.f32x2 work on both at once), and a
+// 16-byte pack of the tensor dtype as such pairs.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void upk2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+
+template <typename T> struct Pairs;
+template <> struct Pairs<__nv_bfloat16> {
+  static __device__ __forceinline__ void get(const uint4& raw, f32x2 (&o)[4]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = pk2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
+  static __device__ __forceinline__ void store(uint4* dst, const uint32_t (&w)[4]) { *dst = make_uint4(w[0], w[1], w[2], w[3]); }
+  static __device__ __forceinline__ void stream(__nv_bfloat16* dst, const uint32_t (&w)[4]) { __stcs(reinterpret_cast<uint4*>(dst), make_uint4(w[0], w[1], w[2], w[3])); }
+};
+template <> struct Pairs<__half> {
+  static __device__ __forceinline__ void get(const uint4& raw, f32x2 (&o)[4]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); o[i] = pk2(f.x, f.y); }
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
+  static __device__ __forceinline__ void store(uint4* dst, const uint32_t (&w)[4]) { *dst = make_uint4(w[0], w[1], w[2], w[3]); }
+  static __device__ __forceinline__ void stream(__half* dst, const uint32_t (&w)[4]) { __stcs(reinterpret_cast<uint4*>(dst), make_uint4(w[0], w[1], w[2], w[3])); }
+};
+// Largest element of the packs tid, tid + nt, ... of a 16-bit row in shared memory, compared two elements at a time
+// without unpacking them.
+template <typename T> struct RowMax;
+template <> struct RowMax<__nv_bfloat16> {
+  static __device__ __forceinline__ float of(const uint4* row, int tid, int npk, int nt) {
+    __nv_bfloat162 m2 = __float2bfloat162_rn(-INFINITY);
+#pragma unroll 4
+    for (int pk = tid; pk < npk; pk += nt) {
+      const uint4 raw = row[pk];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      m2 = __hmax2(__hmax2(m2, h[0]), __hmax2(__hmax2(h[1], h[2]), h[3]));
+    }
+    return fmaxf(__low2float(m2), __high2float(m2));
+  }
+};
+template <> struct RowMax<__half> {
+  static __device__ __forceinline__ float of(const uint4* row, int tid, int npk, int nt) {
+    __half2 m2 = __float2half2_rn(-INFINITY);
+#pragma unroll 4
+    for (int pk = tid; pk < npk; pk += nt) {
+      const uint4 raw = row[pk];
+      const __half2* h = reinterpret_cast<const __half2*>(&raw);
+      m2 = __hmax2(__hmax2(m2, h[0]), __hmax2(__hmax2(h[1], h[2]), h[3]));
+    }
+    return fmaxf(__low2float(m2), __high2float(m2));
+  }
+};
+
+// The same computation with the rows staged in shared memory.  One persistent CTA per SM owns every gridDim.x-th row; a
+// ring of whole rows (64 KB each for 32000 bfloat16 logits, three of them) is filled by bulk asynchronous copies that
+// complete on mbarriers, so the next rows are on their way from HBM while the current one is swept three times out of
+// shared memory (max, sum of exponentials, gradient) and its gradient streams out.  The register-resident kernel above
+// has nothing in flight while a block reduces and exponentiates; this one keeps the memory system busy throughout.
+// Rows that do not count are never loaded.  Every wait is bounded: when one runs out the block marks the rows it has
+// not finished with a NaN loss (which makes the mean loss NaN), lets its outstanding copies land (bounded too) and returns.
+template <typename T, int NT>
+__global__ void __launch_bounds__(NT, 1)
+shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels, const float* __restrict__ n_valid,
+                         float* __restrict__ row_loss, T* d_logits, int B, int Tn, int V,
+                         int64_t ls_b, int64_t ls_t, int64_t lab_b, int64_t lab_t, int64_t ignore_index,
+                         int n_stages, uint32_t stage_bytes) {
+  using namespace tc;
+  constexpr int W = 16 / sizeof(T);
+  extern __shared__ __align__(128) unsigned char ce_smem[];
+  __shared__ float buf[2 * (NT / 32)];
+  __shared__ int abort_flag;
+  uint64_t* full = reinterpret_cast<uint64_t*>(ce_smem + size_t(n_stages) * stage_bytes);
+  const int tid = threadIdx.x;
+  const float scale = 1.0f / fmaxf(n_valid[0], 1.0f);
+  const int n_rows = B * Tn, npk = V / W;
+  const uint32_t row_bytes = uint32_t(V) * sizeof(T);
+  const int n_mine = int(blockIdx.x) < n_rows ? (n_rows - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < n_stages; ++i) mbar_init(&full[i], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  Guard g{&abort_flag, nullptr};
+  auto target_of = [&](int i) -> int64_t {               // target of my i-th row, or -1 when the row does not count
+    const int row = int(blockIdx.x) + i * int(gridDim.x);
+    const int b = row / Tn, t = row - b * Tn;
+    if (t + 1 >= Tn) return -1;
+    const int64_t target = labels[b * lab_b + (t + 1) * lab_t];
+    return (target != ignore_index && target >= 0 && target < V) ? target : -1;
+  };
+  // producer side (thread 0 only): the next row that counts goes into the next stage of the ring
+  int p_i = 0, p_k = 0;
+  auto request_next = [&]() {
+    while (p_i < n_mine && target_of(p_i) < 0) ++p_i;
+    if (p_i >= n_mine) return;
+    const int row = int(blockIdx.x) + p_i * int(gridDim.x);
+    const int b = row / Tn, t = row - b * Tn;
+    const int st = p_k % n_stages;
+    mbar_expect_tx(&full[st], row_bytes);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(ce_smem + size_t(st) * stage_bytes)), "l"(reinterpret_cast<uint64_t>(logits + b * ls_b + t * ls_t)),
+                   "r"(row_bytes), "r"(smem_u32(&full[st])) : "memory");
+    ++p_i; ++p_k;
+  };
+  if (tid == 0) for (int i = 0; i + 1 < n_stages; ++i) request_next();
+
+  int k = 0;                                             // rows that count, seen so far (they use the stages in turn)
+  bool ok = true;
+  int phase = 0;                                         // which half of `buf` the next reduction uses
+  // One barrier per block-wide reduction: consecutive reductions alternate between the two halves of `buf`, and a half
+  // is not written again before a later barrier has been passed by every thread that read it.
+  auto reduce = [&](float v, bool is_max) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float w = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, w) : v + w;
+    }
+    float* half = buf + phase * (NT / 32);
+    phase ^= 1;
+    if ((tid & 31) == 0) half[tid >> 5] = v;
+    __syncthreads();
+    float r = half[0];
+#pragma unroll
+    for (int w = 1; w < NT / 32; ++w) r = is_max ? fmaxf(r, half[w]) : r + half[w];
+    return r;
+  };
+  for (int i = 0; i < n_mine; ++i) {
+    const int row = int(blockIdx.x) + i * int(gridDim.x);
+    T* dx = d_logits ? d_logits + int64_t(row) * V : nullptr;
+    const int64_t target = target_of(i);
+    if (target < 0) {                                    // uniform over the block
+      if (dx) for (int pk = tid; pk < npk; pk += NT) reinterpret_cast<uint4*>(dx)[pk] = make_uint4(0u, 0u, 0u, 0u);
+      if (tid == 0) row_loss[row] = 0.f;
+      continue;
+    }
+    const int st = k % n_stages;
+    fence_async_smem();
+    __syncthreads();                                     // everyone is done with the previous row: its stage may be refilled
+    if (tid == 0) request_next();
+    // (a wait that runs out does not leave the loop: every thread keeps passing the same barriers, the abort flag makes
+    //  all later waits return at once, and the rows are marked after the loop)
+    ok = g.wait(&full[st], (k / n_stages) & 1, 200) && ok;
+    uint4* srow = reinterpret_cast<uint4*>(ce_smem + size_t(st) * stage_bytes);
+    const int tgt = int(target);
+    const float x_target = tid == 0 ? Elem<T>::to_c(reinterpret_cast<const T*>(srow)[tgt]) : 0.f;
+    float m = RowMax<T>::of(srow, tid, npk, NT);
+    m = reduce(m, true);
+    const float off = m * kLog2e;
+    // the exponentials are summed in float32 and put back over the row in the tensor dtype (values in [0, 1]): the
+    // gradient sweep then needs no second exponential per element, at the price of one more rounding of the gradient
+    // (2^-9 relative for bfloat16 against a bar of 2e-2)
+    const f32x2 l2e2 = pk2(kLog2e, kLog2e), noff2 = pk2(-off, -off);
+    float sum = 0.f;
+#pragma unroll 4
+    for (int pk = tid; pk < npk; pk += NT) {
+      f32x2 x2[W / 2];
+      Pairs<T>::get(srow[pk], x2);
+      uint32_t back[W / 2];
+#pragma unroll
+      for (int j = 0; j < W / 2; ++j) {
+        float a0, a1;
+        upk2(fma2(x2[j], l2e2, noff2), a0, a1);
+        const float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
+        sum += e0 + e1;
+        back[j] = Pairs<T>::pack(e0, e1);
+      }
+      if (dx) Pairs<T>::store(srow + pk, back);          // (each thread rewrites only the packs it reads)
+    }
+    sum = reduce(sum, false);
+    if (dx) {
+      const float inv = scale / sum;                     // softmax normaliser and 1/n_valid in one factor
+      const f32x2 inv2 = pk2(inv, inv);
+#pragma unroll 4
+      for (int pk = tid; pk < npk; pk += NT) {
+        f32x2 e2[W / 2];
+        Pairs<T>::get(srow[pk], e2);
+        uint32_t o[W / 2];
+#pragma unroll
+        for (int j = 0; j < W / 2; ++j) {
+          float o0, o1;
+          upk2(mul2(e2[j], inv2), o0, o1);
+          o[j] = Pairs<T>::pack(o0, o1);
+        }
+        Pairs<T>::stream(dx + int64_t(pk) * W, o);
+      }
+      // the target's element, by the thread that has just stored its pack (so this store lands after that one)
+      if (tid == (tgt / W) % NT) dx[tgt] = Elem<T>::from_c(Elem<T>::to_c(reinterpret_cast<const T*>(srow)[tgt]) * inv - scale);
+    }
+    if (tid == 0) row_loss[row] = m + logf(sum) - x_target;
+    ++k;
+  }
+  if (__syncthreads_or(!ok)) {
+    // a copy never arrived: say so through the losses, then let what was requested land before the block goes away
+    if (tid == 0) {
+      for (int r = 0; r < n_mine; ++r) row_loss[int(blockIdx.x) + r * int(gridDim.x)] = __int_as_float(0x7fc00000);
+      for (int kk = 0; kk < p_k; ++kk)
+        for (uint32_t spin = 0; spin < 64 && !mbar_try_wait(&full[kk % n_stages], (kk / n_stages) & 1); ++spin) {}
+    }
+  }
+}
+
 // x *= s[0] unless s[0] == 1 (the usual case: loss.backward() with no loss scaling), in which case nothing is touched
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -159,6 +382,21 @@ int shifted_ce_t(const void* logits, const int64_t* labels, const float* n_valid
     kern<<<grid, threads, 0, st>>>((const T*)logits, labels, n_valid, row_loss, (T*)d_logits, B, Tn, V, ls_b, ls_t, lab_b, lab_t,
                                    ignore_index);
   };
+  // rows staged in shared memory when at least two of them fit next to each other
+  const uint32_t stage_bytes = (uint32_t(V) * sizeof(T) + 127u) & ~127u;
+  const int n_stages = int((kCeSmemBytes - 256) / stage_bytes) < 4 ? int((kCeSmemBytes - 256) / stage_bytes) : 4;
+  if constexpr (sizeof(T) == 2) if (FAT_CE_STAGED && aligned && n_stages >= 2 && rows >= 2 * int64_t(num_sms())) {
+    const size_t smem = size_t(n_stages) * stage_bytes + 64;
+    auto kern = shifted_ce_staged_kernel<T, kCeStagedThreads>;
+    static bool configured = false;              // (per instantiation; racing threads set the same value)
+    if (!configured) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kCeSmemBytes));
+      configured = true;
+    }
+    kern<<<unsigned(num_sms()), kCeStagedThreads, smem, st>>>((const T*)logits, labels, n_valid, row_loss, (T*)d_logits, B, Tn, V, ls_b, ls_t,
+                                                             lab_b, lab_t, ignore_index, n_stages, stage_bytes);
+    return check_launch("shifted_ce_staged");
+  }
   if (aligned && V / W <= 256 * kCePacks) go(shifted_ce_kernel<T, 256, true>, 256);
   else if (aligned && V / W <= 512 * kCePacks) go(shifted_ce_kernel<T, 512, true>, 512);
   else go(shifted_ce_kernel<T, 512, false>, 512);
