@@ -212,8 +212,9 @@ template <> struct RowMax<__half> {
 
 // The same computation with the rows staged in shared memory.  One persistent CTA per SM owns every gridDim.x-th row; a
 // ring of whole rows (64 KB each for 32000 bfloat16 logits, three of them) is filled by bulk asynchronous copies that
-// complete on mbarriers, so the next rows are on their way from HBM while the current one is swept three times out of
-// shared memory (max, sum of exponentials, gradient) and its gradient streams out.  The register-resident kernel above
+// complete on mbarriers, so the next row is on its way from HBM while the two halves of the CTA sweep one row each, three
+// times out of shared memory (max, sum of exponentials, gradient), and the gradients stream out.  Two rows at once because
+// one row's sweeps are chains of shared-memory, special-function and barrier latencies that a single set of warps cannot fill.  The register-resident kernel above
 // has nothing in flight while a block reduces and exponentiates; this one keeps the memory system busy throughout.
 // Rows that do not count are never loaded.  Every wait is bounded: when one runs out the block marks the rows it has
 // not finished with a NaN loss (which makes the mean loss NaN), lets its outstanding copies land (bounded too) and returns.
@@ -225,11 +226,12 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
                          int n_stages, uint32_t stage_bytes) {
   using namespace tc;
   constexpr int W = 16 / sizeof(T);
+  constexpr int kGroups = 2, GT = NT / kGroups;          // the two halves of the CTA sweep two rows at the same time
   extern __shared__ __align__(128) unsigned char ce_smem[];
-  __shared__ float buf[2 * (NT / 32)];
+  __shared__ float buf[kGroups][2][GT / 32];
   __shared__ int abort_flag;
   uint64_t* full = reinterpret_cast<uint64_t*>(ce_smem + size_t(n_stages) * stage_bytes);
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, gid = tid / GT, gt = tid % GT;
   const float scale = 1.0f / fmaxf(n_valid[0], 1.0f);
   const int n_rows = B * Tn, npk = V / W;
   const uint32_t row_bytes = uint32_t(V) * sizeof(T);
@@ -248,26 +250,35 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
     const int64_t target = labels[b * lab_b + (t + 1) * lab_t];
     return (target != ignore_index && target >= 0 && target < V) ? target : -1;
   };
-  // producer side (thread 0 only): the next row that counts goes into the next stage of the ring
-  int p_i = 0, p_k = 0;
-  auto request_next = [&]() {
-    while (p_i < n_mine && target_of(p_i) < 0) ++p_i;
-    if (p_i >= n_mine) return;
-    const int row = int(blockIdx.x) + p_i * int(gridDim.x);
+  // Rows that count use the stages of the ring in turn: the k-th of them goes through stage k % n_stages, and the group
+  // that has finished with row k asks for row k + n_stages.  A group leader walks its own cursor over the rows to find it.
+  int c_i = 0, c_k = 0;                                  // (leaders only) c_i: first row not yet passed, c_k: rows that count before it
+  auto request = [&](int kk) {                           // copy the kk-th row that counts into its stage, if there is one
+    while (c_i < n_mine) {
+      if (target_of(c_i) >= 0) {
+        if (c_k == kk) break;
+        ++c_k;
+      }
+      ++c_i;
+    }
+    if (c_i >= n_mine) return;
+    const int row = int(blockIdx.x) + c_i * int(gridDim.x);
     const int b = row / Tn, t = row - b * Tn;
-    const int st = p_k % n_stages;
+    const int st = kk % n_stages;
     mbar_expect_tx(&full[st], row_bytes);
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(ce_smem + size_t(st) * stage_bytes)), "l"(reinterpret_cast<uint64_t>(logits + b * ls_b + t * ls_t)),
                    "r"(row_bytes), "r"(smem_u32(&full[st])) : "memory");
-    ++p_i; ++p_k;
   };
-  if (tid == 0) for (int i = 0; i + 1 < n_stages; ++i) request_next();
+  if (tid == 0) {
+    for (int kk = 0; kk < n_stages; ++kk) request(kk);
+    c_i = 0; c_k = 0;                                    // the walk for this group's own requests starts over
+  }
 
-  int k = 0;                                             // rows that count, seen so far (they use the stages in turn)
   bool ok = true;
-  int phase = 0;                                         // which half of `buf` the next reduction uses
-  // One barrier per block-wide reduction: consecutive reductions alternate between the two halves of `buf`, and a half
+  int phase = 0;                                         // which half of this group's `buf` the next reduction uses
+  auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + gid), "r"(GT) : "memory"); };
+  // One barrier per group-wide reduction: consecutive reductions alternate between the two halves of `buf`, and a half
   // is not written again before a later barrier has been passed by every thread that read it.
   auto reduce = [&](float v, bool is_max) {
 #pragma unroll
@@ -275,35 +286,37 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
       const float w = __shfl_xor_sync(0xffffffffu, v, o);
       v = is_max ? fmaxf(v, w) : v + w;
     }
-    float* half = buf + phase * (NT / 32);
+    float* half = buf[gid][phase];
     phase ^= 1;
-    if ((tid & 31) == 0) half[tid >> 5] = v;
-    __syncthreads();
+    if ((gt & 31) == 0) half[gt >> 5] = v;
+    group_sync();
     float r = half[0];
 #pragma unroll
-    for (int w = 1; w < NT / 32; ++w) r = is_max ? fmaxf(r, half[w]) : r + half[w];
+    for (int w = 1; w < GT / 32; ++w) r = is_max ? fmaxf(r, half[w]) : r + half[w];
     return r;
   };
+  int k = 0;                                             // rows that count, seen so far
   for (int i = 0; i < n_mine; ++i) {
     const int row = int(blockIdx.x) + i * int(gridDim.x);
     T* dx = d_logits ? d_logits + int64_t(row) * V : nullptr;
     const int64_t target = target_of(i);
-    if (target < 0) {                                    // uniform over the block
-      if (dx) for (int pk = tid; pk < npk; pk += NT) reinterpret_cast<uint4*>(dx)[pk] = make_uint4(0u, 0u, 0u, 0u);
-      if (tid == 0) row_loss[row] = 0.f;
+    if (target < 0) {                                    // the groups take turns with the rows that only need zeros
+      if ((i & 1) == gid) {
+        if (dx) for (int pk = gt; pk < npk; pk += GT) reinterpret_cast<uint4*>(dx)[pk] = make_uint4(0u, 0u, 0u, 0u);
+        if (gt == 0) row_loss[row] = 0.f;
+      }
       continue;
     }
-    const int st = k % n_stages;
-    fence_async_smem();
-    __syncthreads();                                     // everyone is done with the previous row: its stage may be refilled
-    if (tid == 0) request_next();
+    const int my_k = k++;
+    if ((my_k & 1) != gid) continue;                     // the other group's row
+    const int st = my_k % n_stages;
     // (a wait that runs out does not leave the loop: every thread keeps passing the same barriers, the abort flag makes
     //  all later waits return at once, and the rows are marked after the loop)
-    ok = g.wait(&full[st], (k / n_stages) & 1, 200) && ok;
+    ok = g.wait(&full[st], (my_k / n_stages) & 1, 200) && ok;
     uint4* srow = reinterpret_cast<uint4*>(ce_smem + size_t(st) * stage_bytes);
     const int tgt = int(target);
-    const float x_target = tid == 0 ? Elem<T>::to_c(reinterpret_cast<const T*>(srow)[tgt]) : 0.f;
-    float m = RowMax<T>::of(srow, tid, npk, NT);
+    const float x_target = gt == 0 ? Elem<T>::to_c(reinterpret_cast<const T*>(srow)[tgt]) : 0.f;
+    float m = RowMax<T>::of(srow, gt, npk, GT);
     m = reduce(m, true);
     const float off = m * kLog2e;
     // the exponentials are summed in float32 and put back over the row in the tensor dtype (values in [0, 1]): the
@@ -312,7 +325,7 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
     const f32x2 l2e2 = pk2(kLog2e, kLog2e), noff2 = pk2(-off, -off);
     float sum = 0.f;
 #pragma unroll 4
-    for (int pk = tid; pk < npk; pk += NT) {
+    for (int pk = gt; pk < npk; pk += GT) {
       f32x2 x2[W / 2];
       Pairs<T>::get(srow[pk], x2);
       uint32_t back[W / 2];
@@ -331,7 +344,7 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
       const float inv = scale / sum;                     // softmax normaliser and 1/n_valid in one factor
       const f32x2 inv2 = pk2(inv, inv);
 #pragma unroll 4
-      for (int pk = tid; pk < npk; pk += NT) {
+      for (int pk = gt; pk < npk; pk += GT) {
         f32x2 e2[W / 2];
         Pairs<T>::get(srow[pk], e2);
         uint32_t o[W / 2];
@@ -344,17 +357,19 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
         Pairs<T>::stream(dx + int64_t(pk) * W, o);
       }
       // the target's element, by the thread that has just stored its pack (so this store lands after that one)
-      if (tid == (tgt / W) % NT) dx[tgt] = Elem<T>::from_c(Elem<T>::to_c(reinterpret_cast<const T*>(srow)[tgt]) * inv - scale);
+      if (gt == (tgt / W) % GT) dx[tgt] = Elem<T>::from_c(Elem<T>::to_c(reinterpret_cast<const T*>(srow)[tgt]) * inv - scale);
     }
-    if (tid == 0) row_loss[row] = m + logf(sum) - x_target;
-    ++k;
+    if (gt == 0) row_loss[row] = m + logf(sum) - x_target;
+    fence_async_smem();
+    group_sync();                                        // the group is done with the row: its stage may be refilled
+    if (gt == 0) request(my_k + n_stages);
   }
   if (__syncthreads_or(!ok)) {
     // a copy never arrived: say so through the losses, then let what was requested land before the block goes away
     if (tid == 0) {
       for (int r = 0; r < n_mine; ++r) row_loss[int(blockIdx.x) + r * int(gridDim.x)] = __int_as_float(0x7fc00000);
-      for (int kk = 0; kk < p_k; ++kk)
-        for (uint32_t spin = 0; spin < 64 && !mbar_try_wait(&full[kk % n_stages], (kk / n_stages) & 1); ++spin) {}
+      for (int st = 0; st < n_stages; ++st)
+        for (uint32_t spin = 0; spin < 64 && !mbar_try_wait(&full[st], 0) && !mbar_try_wait(&full[st], 1); ++spin) {}
     }
   }
 }
