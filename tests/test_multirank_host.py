@@ -43,7 +43,7 @@ def test_two_ranks_agree_on_the_slowest_time_and_the_aggregate():
     assert (res[0][2], res[0][3]) == (0, 4) and (res[1][2], res[1][3]) == (4, 4)  # contiguous blocks that tile the batch
 
 
-def test_flop_convention_matches_the_survey():
+def test_flop_convention_of_the_headline_configurations():
     sys.path.insert(0, ROOT)
     import bench
     fwd, bwd = bench.attn_flops(B=8, H=16, S=4096, D=128)
