@@ -81,26 +81,29 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 WAIT_TEST_LIB = os.path.join(PKG, "..", "tests", "_build", "libfat_b200_waittest.so")
-WAIT_TEST_FLAGS = ["-DFAT_TEST_WITHHOLD_V_TILE=0", "-DFAT_WAIT_HINT_NS=100000", "-DFAT_WAIT_SPINS=30"]
+WAIT_TEST_FLAGS = ["-DFAT_TEST_WITHHOLD_V_TILE=0", "-DFAT_TEST_CE_WITHHOLD_ROW=4", "-DFAT_WAIT_HINT_NS=100000", "-DFAT_WAIT_SPINS=30"]
+WAIT_TEST_SOURCES = ("attn_tc_fwd.cu", "loss.cu")
 
 
 def build_wait_test(force: bool = False, verbose: bool = False) -> str:
     """A TEST-ONLY variant of the library (tests/_build/, never loaded by the package): the attention forward is compiled
-    so that its producer leaves out one V tile and every bounded wait gives up after ~3 ms.  tests/test_wait_timeout.py
-    uses it to run the give-up path once (status word, teardown, TMEM release).  Only attn_tc_fwd.cu is recompiled; the
-    other objects are the shipped ones."""
-    src = os.path.join(CSRC, "attn_tc_fwd.cu")
+    so that its producer leaves out one V tile, the staged loss kernel so that its first block never requests the copy of
+    one row, and every bounded wait gives up after ~3 ms.  tests/test_wait_timeout.py uses it to run the give-up paths
+    once (status word or NaN losses, teardown, TMEM release).  Only those two sources are recompiled; the other objects
+    are the shipped ones."""
+    srcs = [os.path.join(CSRC, n) for n in WAIT_TEST_SOURCES]
     headers = sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + sorted(glob.glob(os.path.join(PKG, "..", "include", "*.h")))
     out_dir = os.path.dirname(WAIT_TEST_LIB)
     os.makedirs(out_dir, exist_ok=True)
-    obj = os.path.join(out_dir, "attn_tc_fwd_waittest.o")
+    objs = [os.path.join(out_dir, n[:-3] + "_waittest.o") for n in WAIT_TEST_SOURCES]
     others = [os.path.join(OBJ, os.path.basename(s)[:-3] + ".o") for s in sorted(glob.glob(os.path.join(CSRC, "*.cu")))
-              if os.path.basename(s) != "attn_tc_fwd.cu"]
-    if not (force or _stale(WAIT_TEST_LIB, [src] + headers + others)):
+              if os.path.basename(s) not in WAIT_TEST_SOURCES]
+    if not (force or _stale(WAIT_TEST_LIB, srcs + headers + others)):
         return WAIT_TEST_LIB
     nvcc = _nvcc()
-    for cmd in ([nvcc, *NVCC_FLAGS, *WAIT_TEST_FLAGS, "-c", src, "-o", obj],
-                [nvcc, "-shared", "-o", WAIT_TEST_LIB, obj, *others, "-gencode", "arch=compute_100a,code=sm_100a"]):
+    cmds = [[nvcc, *NVCC_FLAGS, *WAIT_TEST_FLAGS, "-c", src, "-o", obj] for src, obj in zip(srcs, objs)]
+    cmds.append([nvcc, "-shared", "-o", WAIT_TEST_LIB, *objs, *others, "-gencode", "arch=compute_100a,code=sm_100a"])
+    for cmd in cmds:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or r.returncode:
             sys.stderr.write(r.stdout + r.stderr)

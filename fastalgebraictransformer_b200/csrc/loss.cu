@@ -230,6 +230,7 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
   extern __shared__ __align__(128) unsigned char ce_smem[];
   __shared__ float buf[kGroups][2][GT / 32];
   __shared__ int abort_flag;
+  __shared__ int last_req[4];                            // per stage: the last row that counts whose copy was requested
   uint64_t* full = reinterpret_cast<uint64_t*>(ce_smem + size_t(n_stages) * stage_bytes);
   const int tid = threadIdx.x, gid = tid / GT, gt = tid % GT;
   const float scale = 1.0f / fmaxf(n_valid[0], 1.0f);
@@ -238,7 +239,7 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
   const int n_mine = int(blockIdx.x) < n_rows ? (n_rows - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
   if (tid == 0) {
     abort_flag = 0;
-    for (int i = 0; i < n_stages; ++i) mbar_init(&full[i], 1);
+    for (int i = 0; i < n_stages; ++i) { mbar_init(&full[i], 1); last_req[i] = -1; }
     mbar_fence_init();
   }
   __syncthreads();
@@ -261,10 +262,14 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
       }
       ++c_i;
     }
-    if (c_i >= n_mine) return;
+    if (c_i >= n_mine || g.aborted()) return;           // (after a wait has run out nothing new is requested)
+#ifdef FAT_TEST_CE_WITHHOLD_ROW
+    if (kk == FAT_TEST_CE_WITHHOLD_ROW && blockIdx.x == 0) return;      // test builds: this copy never happens
+#endif
     const int row = int(blockIdx.x) + c_i * int(gridDim.x);
     const int b = row / Tn, t = row - b * Tn;
     const int st = kk % n_stages;
+    last_req[st] = kk;
     mbar_expect_tx(&full[st], row_bytes);
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(ce_smem + size_t(st) * stage_bytes)), "l"(reinterpret_cast<uint64_t>(logits + b * ls_b + t * ls_t)),
@@ -368,8 +373,9 @@ shifted_ce_staged_kernel(const T* __restrict__ logits, const int64_t* __restrict
     // a copy never arrived: say so through the losses, then let what was requested land before the block goes away
     if (tid == 0) {
       for (int r = 0; r < n_mine; ++r) row_loss[int(blockIdx.x) + r * int(gridDim.x)] = __int_as_float(0x7fc00000);
-      for (int st = 0; st < n_stages; ++st)
-        for (uint32_t spin = 0; spin < 64 && !mbar_try_wait(&full[st], 0) && !mbar_try_wait(&full[st], 1); ++spin) {}
+      for (int st = 0; st < n_stages; ++st)            // copies that were requested may still be on their way into this CTA
+        if (last_req[st] >= 0)
+          for (uint32_t spin = 0; spin < 16 && !mbar_try_wait(&full[st], (last_req[st] / n_stages) & 1); ++spin) {}
     }
   }
 }
