@@ -39,6 +39,9 @@ namespace {
 #ifndef FAT_DEC_FILL
 #define FAT_DEC_FILL 3            // the key range of a (batch, head) pair is split until there are this many CTAs per SM
 #endif
+#ifndef FAT_DEC_MIN_ROWS
+#define FAT_DEC_MIN_ROWS 256      // ... but no CTA gets fewer rows of a full cache than this (more, smaller clusters measured slower)
+#endif
 #ifndef FAT_DEC_MINB
 #define FAT_DEC_MINB 4            // CTAs per SM the register budget is cut for
 #endif
@@ -340,9 +343,9 @@ extern "C" int fat_attn_decode(const void* q, const void* k_new, const void* v_n
   for (int i = 0; i < 2; ++i) { p.qs[i] = q_strides[i]; p.kns[i] = k_new_strides[i]; p.vns[i] = v_new_strides[i]; p.os[i] = out_strides[i]; }
   for (int i = 0; i < 3; ++i) { p.kcs[i] = k_cache_strides[i]; p.vcs[i] = v_cache_strides[i]; }
   p.scale = float(scale); p.eps = float(eps); p.status = status;
-  // enough CTAs to fill the GPU twice over, but no CTA with less than a few hundred rows of a full cache
+  // enough CTAs to fill the GPU (FAT_DEC_FILL per SM), but no CTA with less than FAT_DEC_MIN_ROWS rows of a full cache
   int n_split = 1;
-  while (n_split < 8 && int64_t(B) * H * n_split < FAT_DEC_FILL * int64_t(num_sms()) && capacity / (2 * n_split) >= 256) n_split *= 2;
+  while (n_split < 8 && int64_t(B) * H * n_split < FAT_DEC_FILL * int64_t(num_sms()) && capacity / (2 * n_split) >= FAT_DEC_MIN_ROWS) n_split *= 2;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case FAT_F32: return decode_t<float>(p, D, n_split, st);
