@@ -46,7 +46,8 @@ class RationalAttentionFunction(torch.autograd.Function):
         assert q.shape == k.shape == v.shape
         bits = as_key_mask_bits(key_mask, q.shape[2])
         output, L, output_lo = torch.ops.algebraic.attn_fwd(q, k, v, alibi_slopes, float(scale), bool(causal),
-                                                            float(eps), int(path), bool(token_major_out), bits)
+                                                            float(eps), int(path), bool(token_major_out), bits,
+                                                            any(ctx.needs_input_grad[:3]))
         ctx.save_for_backward(q, k, v, output, L, output_lo, alibi_slopes)
         ctx.scale, ctx.causal, ctx.eps, ctx.path, ctx.bits = float(scale), bool(causal), float(eps), int(path), bits
         return output
@@ -72,7 +73,8 @@ class RationalAttentionPackedFunction(torch.autograd.Function):
         B, T, _, H, D = qkv.shape
         q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
         bits = as_key_mask_bits(key_mask, T)
-        out, L, out_lo = ops.attn_fwd(q, k, v, alibi_slopes, float(scale), True, float(eps), _lib.PATH_AUTO, True, bits)
+        out, L, out_lo = ops.attn_fwd(q, k, v, alibi_slopes, float(scale), True, float(eps), _lib.PATH_AUTO, True, bits,
+                                      ctx.needs_input_grad[0])
         ctx.save_for_backward(qkv, out, L, out_lo, alibi_slopes)
         ctx.scale, ctx.eps, ctx.bits = float(scale), float(eps), bits
         return out.permute(0, 2, 1, 3).reshape(B, T, H * D)        # a view: the memory order already is [B,T,H,D]

@@ -46,5 +46,5 @@ def rational_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     assert q.shape == k.shape == v.shape
     out, L, _ = torch.ops.algebraic.attn_fwd(q.detach(), k.detach(), v.detach(), alibi_slopes, float(scale),
                                              bool(causal), float(eps), int(path), False,
-                                             ops.as_key_mask_bits(key_mask, q.shape[2]))
+                                             ops.as_key_mask_bits(key_mask, q.shape[2]), False)
     return out, L

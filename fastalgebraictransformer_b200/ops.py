@@ -81,9 +81,11 @@ def as_key_mask_bits(key_mask, n_tokens: int) -> Optional[Tensor]:
 
 
 def attn_fwd(q: Tensor, k: Tensor, v: Tensor, slopes: Tensor, scale: float, causal: bool, eps: float,
-             path: int, token_major_out: bool, key_mask: Optional[Tensor] = None) -> Tuple[Tensor, Tensor, Tensor]:
-    """(out, L, out_lo) of rational attention; see include/fat_b200.h, fat_attn_fwd.  ``key_mask``: packed bits or None."""
-    return _alg.attn_fwd(q, k, v, slopes, float(scale), bool(causal), float(eps), int(path), bool(token_major_out), key_mask)
+             path: int, token_major_out: bool, key_mask: Optional[Tensor] = None, residual: bool = True) -> Tuple[Tensor, Tensor, Tensor]:
+    """(out, L, out_lo) of rational attention; see include/fat_b200.h, fat_attn_fwd.  ``key_mask``: packed bits or None.
+    ``residual=False``: no backward will follow, so the rounding residual of a 16-bit output is not written (out_lo is empty)."""
+    return _alg.attn_fwd(q, k, v, slopes, float(scale), bool(causal), float(eps), int(path), bool(token_major_out), key_mask,
+                         bool(residual))
 
 
 def attn_decode(q: Tensor, k_new: Tensor, v_new: Tensor, k_cache: Tensor, v_cache: Tensor, n_cached: Tensor, slopes: Tensor,
@@ -172,10 +174,10 @@ def _(mask):
 
 
 @torch.library.register_fake(f"{_NS}::attn_fwd")
-def _(q, k, v, slopes, scale, causal, eps, path, token_major_out, key_mask=None):
+def _(q, k, v, slopes, scale, causal, eps, path, token_major_out, key_mask=None, residual=True):
     B, H, T, D = q.shape
     out = q.new_empty((B, T, H, D)).permute(0, 2, 1, 3) if token_major_out else q.new_empty((B, H, T, D))
-    lo = torch.empty_like(out) if q.element_size() == 2 else q.new_empty(0)
+    lo = torch.empty_like(out) if q.element_size() == 2 and residual else q.new_empty(0)
     return out, q.new_empty((B, H, T), dtype=torch.float32), lo
 
 
@@ -236,7 +238,7 @@ def _softmax_backward(ctx, d_out):
 
 
 def _attn_setup(ctx, inputs, output):
-    q, k, v, slopes, scale, causal, eps, path, _, key_mask = inputs
+    q, k, v, slopes, scale, causal, eps, path, _, key_mask, _residual = inputs
     ctx.save_for_backward(q, k, v, output[0], output[1], output[2], slopes)
     ctx.args = (scale, causal, eps, path)
     ctx.key_mask = key_mask                                  # (an int32 tensor: nothing to differentiate)
@@ -245,7 +247,7 @@ def _attn_setup(ctx, inputs, output):
 def _attn_backward(ctx, d_out, d_L, d_lo):
     q, k, v, out, L, out_lo, slopes = ctx.saved_tensors
     d_q, d_k, d_v = torch.ops.algebraic.attn_bwd(q, k, v, out, out_lo, L, d_out, slopes, *ctx.args, ctx.key_mask)
-    return d_q, d_k, d_v, None, None, None, None, None, None, None
+    return d_q, d_k, d_v, None, None, None, None, None, None, None, None
 
 
 torch.library.register_autograd(f"{_NS}::swiglu_fwd", _swiglu_backward, setup_context=_swiglu_setup)
