@@ -174,3 +174,24 @@ def test_generate_with_cache_equals_the_reference_loop():
     c = model.generate(prompt.clone(), 48, top_k=1, use_cache=True)
     d = model.generate(prompt.clone(), 48, top_k=1, use_cache=False)
     assert c.shape == (2, 57) and torch.equal(c, d)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_decode_first_token_of_an_empty_cache(dtype):
+    """n_cached = 0 everywhere and a cache of one row: the token attends to itself only, out = v * f / (f + eps)."""
+    from fastalgebraictransformer_b200 import ops
+    B, H, D = 2, 3, 32
+    g = torch.Generator().manual_seed(2)
+    q, k_new, v_new = (torch.randn(B, H, D, generator=g).to(dtype) for _ in range(3))
+    kc = torch.full((B, H, 1, D), float("nan"), dtype=dtype)
+    vc = torch.full((B, H, 1, D), float("nan"), dtype=dtype)
+    slopes = oracle.compute_alibi_slopes(H)
+    want = oracle.rational_attention_last_row(q.float(), k_new.float()[:, :, None], v_new.float()[:, :, None], slopes, 0.2)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    got = ops.attn_decode(q.to(DEV), k_new.to(DEV), v_new.to(DEV), kd, vd, torch.zeros(B, dtype=torch.int32, device=DEV),
+                          slopes.to(DEV), 0.2, 1e-6)
+    if dtype == torch.float32:
+        assert norm_max_err(got, want) < 1e-5
+    else:
+        assert bf16_violations(got, want)[0] == 0.0
+    assert torch.equal(kd[:, :, 0].cpu(), k_new) and torch.equal(vd[:, :, 0].cpu(), v_new)

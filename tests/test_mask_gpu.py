@@ -178,3 +178,27 @@ def test_lm_bf16_with_padding_mask_close_to_oracle():
         plain, _ = model(ids.to(DEV))
     assert norm_max_err(got, want) < 3e-2
     assert norm_max_err(plain, want) > 3e-2          # the mask matters for this input
+
+
+@pytest.mark.parametrize("dtype,path", [(torch.float32, 1), (torch.bfloat16, 0), (torch.bfloat16, 3), (torch.float16, 0)])
+@pytest.mark.parametrize("T", [1, 129])
+def test_edge_masks(dtype, path, T):
+    """A sequence whose every key is padding (zero output, zero gradients), one that loses only its last key, one that
+    keeps everything; a single token, and a second tile that holds one key."""
+    B, H, D = 3, 2, 64
+    g = torch.Generator().manual_seed(12 + T)
+    q, k, v, go = (torch.randn(B, H, T, D, generator=g).to(dtype) for _ in range(4))
+    slopes = oracle.compute_alibi_slopes(H)
+    mask = torch.ones(B, T, dtype=torch.int64)
+    mask[0] = 0
+    mask[1, T - 1] = 0
+    got = run_masked(q, k, v, go, slopes, 0.125, mask, path=path)
+    want = oracle.rational_attention_grads(q.float(), k.float(), v.float(), go.float(), slopes, 0.125, key_mask=mask)
+    for t, w, name in zip(got, want, ("out", "dq", "dk", "dv")):
+        assert torch.isfinite(t).all(), name
+        if dtype == torch.float32:
+            # single-key rows have gradients that are differences of equal numbers (size eps): compared absolutely
+            assert (t.cpu().double() - w.double()).abs().max() < 1e-5, name
+        else:
+            assert bf16_violations(t, w)[0] == 0.0, name
+    assert got[0][0].abs().max().item() < 1e-6 and got[2][0].abs().max().item() < 1e-6 and got[3][0].abs().max().item() < 1e-6
