@@ -3,8 +3,10 @@
 // The reference computes  F.cross_entropy(logits[..., :-1, :].contiguous().view(-1, V), labels[..., 1:].view(-1),
 // ignore_index=-100)  (algebraic_model.py:229-235): a copy of the logits, a log-softmax pass that writes a tensor of the
 // same size, and in the backward a log-softmax-backward pass and a zero-padded slice gradient.  Here one kernel reads
-// every logits row once, keeps it in registers, and writes the row's loss and the row of d(loss)/d(logits) (already
-// divided by the number of valid targets; zero for the last position of a sequence and for ignored targets).  The
+// every logits row once and writes the row's loss and the row of d(loss)/d(logits) (already divided by the number of
+// valid targets; zero for the last position of a sequence and for ignored targets).  Two kernels: 16-bit rows that fit
+// shared memory at least twice go through persistent CTAs that stage whole rows with bulk asynchronous copies
+// (shifted_ce_staged_kernel); everything else keeps the row in registers, one block per row (shifted_ce_kernel).  The
 // backward only multiplies by the incoming scalar gradient, and skips even that when the scalar is 1.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
