@@ -225,6 +225,64 @@ def test_shifted_cross_entropy_vs_oracle(shape, dtype):
     assert float(leaf.grad[:, -1].abs().max()) == 0.0                       # the last position is never scored
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(4, 100, 32000), (2, 160, 50000), (8, 64, 1000), (3, 128, 8)])
+def test_shifted_cross_entropy_many_rows_vs_oracle(shape, dtype):
+    """Enough rows (at least two per SM) for the kernel that stages whole rows in shared memory: three, two and four rows
+    in flight per CTA (64 KB, 100 KB and short rows), targets that are ignored, rows that only get zeros, a non-unit
+    incoming gradient.  Loss and every element of the gradient against the float32 oracle on the rounded logits."""
+    B, T, V = shape
+    g = torch.Generator().manual_seed(53)
+    logits = (torch.randn(B, T, V, generator=g) * 3).to(dtype)
+    labels = torch.randint(0, V, (B, T), generator=g)
+    labels[torch.rand(B, T, generator=g) < 0.2] = -100
+    leaf = logits.to(DEV).requires_grad_(True)
+    loss = fat().shifted_cross_entropy(leaf, labels.to(DEV), -100)
+    (loss.float() * 3.0).backward()
+    ref = logits.float().requires_grad_(True)
+    want = oracle.shifted_cross_entropy(ref, labels, -100)
+    (want * 3.0).backward()
+    assert abs(float(loss.detach()) - float(want.detach())) <= 1e-2 * max(1.0, abs(float(want.detach())))
+    got = leaf.grad.float().cpu()
+    # per element: rel 2e-2 of the value plus an absolute floor far below the largest gradients (1/n_valid ~ 1e-3)
+    assert ((got - ref.grad).abs() <= 2e-2 * ref.grad.abs() + 2e-2 * ref.grad.abs().max()).all()
+    assert ((got - ref.grad).abs().max() / ref.grad.abs().max()).item() < 1e-2
+    assert float(leaf.grad[:, -1].abs().max()) == 0.0                       # the last position is never scored
+    ignored = labels[:, 1:] == -100
+    assert float(leaf.grad[:, :-1][ignored.to(DEV)].abs().max()) == 0.0     # nor are ignored targets
+
+
+def test_shifted_cross_entropy_in_place_and_strided_on_the_staged_kernel():
+    """Through the C ABI, with enough rows for the staged kernel: the gradient written over the logits themselves gives
+    the same bits as a separate gradient buffer, and so do logits read through a token stride."""
+    from fastalgebraictransformer_b200 import _lib
+    lib = _lib.lib()
+    B, T, V = 4, 96, 32000
+    g = torch.Generator().manual_seed(54)
+    logits = (torch.randn(B, T, V, generator=g) * 2).to(torch.bfloat16).to(DEV)
+    labels = torch.randint(0, V, (B, T), generator=g).to(DEV)
+    n_valid = torch.tensor([float(B * (T - 1))], device=DEV)
+
+    def run(src, ls_b, ls_t, dst):
+        row_loss = torch.empty(B * T, device=DEV)
+        rc = lib.fat_shifted_ce_fwd(src.data_ptr(), labels.data_ptr(), n_valid.data_ptr(), row_loss.data_ptr(), dst.data_ptr(), B, T, V,
+                                    ls_b, ls_t, labels.stride(0), labels.stride(1), -100, _lib.BF16, _lib.stream_ptr(logits.device))
+        assert rc == 0, lib.fat_last_error().decode()
+        torch.cuda.synchronize()
+        return row_loss
+
+    grad = torch.empty_like(logits)
+    loss_a = run(logits, T * V, V, grad)
+    over = logits.clone()
+    loss_b = run(over, T * V, V, over)                                      # gradient over the logits
+    assert torch.equal(loss_a, loss_b) and torch.equal(grad, over)
+    wide = torch.zeros(B, T, 2, V, dtype=torch.bfloat16, device=DEV)        # every second row of a wider buffer
+    wide[:, :, 0] = logits
+    grad_c = torch.empty_like(logits)
+    loss_c = run(wide, T * 2 * V, 2 * V, grad_c)
+    assert torch.equal(loss_a, loss_c) and torch.equal(grad, grad_c)
+
+
 def test_shifted_cross_entropy_strided_logits_and_unit_gradient():
     """Logits that are a view with a token stride (as a head applied to a padded buffer would give) and the plain
     loss.backward() path, where the gradient is used exactly as the forward wrote it."""
